@@ -1,0 +1,373 @@
+// Split-context paged attention for single decoded tokens, bfloat16 keys and values, float32
+// scores, softmax and accumulation.
+//
+// The decode step is bound by reading the cache, so the kernel is built around the copy: each CTA
+// owns one (request, key/value head, split of the context) and streams its keys and values
+// through a three-stage ring of shared-memory tiles filled by 16-byte asynchronous copies, so that
+// many tiles are in flight per SM.  All query heads of the group share each tile; the two small
+// products (scores, and probabilities times values) run on tensor cores with the group's heads
+// padded to the 16 rows of an m16n8k16 tile.  A split covers a fixed number of positions, so how
+// a row is cut depends on its own length only, never on what else is in the batch.  A second
+// kernel merges the splits.
+//
+// Math as in attention_simt.cu (reference: src/attention/paged_decode.cu:169-352 for the split
+// scheme), except where that kernel is not exact: no epsilon is added to the denominator, and
+// partial results stay float32.  Probabilities are rounded to bfloat16 for the second product, as
+// the reference does (paged_decode.cu:289).
+#include "common.cuh"
+
+namespace zb {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE = 64;            // keys per shared-memory tile; 16 per warp
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_MAX_GROUP = 16;       // query heads per key/value head that fit one MMA tile
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;        // [T, nh*hd]
+  const __nv_bfloat16* kv_cache; // [num_pages][2][nkv][page_size][hd]
+  const int* block_table;        // [R, max_blocks]
+  const int* rows;               // [n_rows] request rows that decode one token
+  const int* row_q_start;        // [R]
+  const int* row_ctx;            // [R] tokens in the cache before this step (the new token's position)
+  float* part_o;                 // [n_rows, nh, max_splits, hd]
+  float* part_ml;                // [n_rows, nh, max_splits, 2]
+  int max_blocks, page_size, num_pages, num_rows;
+  int nh, nkv, window, split_size, max_splits;
+  float scale_log2;              // scale * log2(e)
+  int* status;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;       // 0 bytes read: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+
+// Which positions split `s` of a row covers: [begin, end), empty if begin >= end.
+__device__ __forceinline__ void split_range(int ctx_total, int window, int split_size, int s, int& begin, int& end) {
+  const int lo = window > 0 ? max(0, ctx_total - window) : 0;   // the query sits at ctx_total - 1
+  begin = max(s * split_size, lo);
+  end = min((s + 1) * split_size, ctx_total);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+paged_decode_split_kernel(const DecodeArgs a) {
+  static_assert(HD % 32 == 0 && HD <= 128, "head sizes 32, 64, 96, 128");
+  constexpr int KROW = HD + 8;                     // padded row: ldmatrix reads without bank conflicts
+  constexpr int STAGE = 2 * DEC_TILE * KROW;       // elements of one stage (keys, then values)
+  constexpr int CHUNKS = HD / 8;                   // 16-byte chunks per row
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+  const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  const int row = a.rows[r];
+  if (row < 0 || row >= a.num_rows) {
+    if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, r);
+    return;
+  }
+  const int ctx_total = a.row_ctx[row] + 1;
+  int begin, end;
+  split_range(ctx_total, a.window, a.split_size, split, begin, end);
+  if (begin >= end) return;
+
+  const int g = a.nh / a.nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
+  const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
+
+  // The group's queries as the A operand (heads on the 16 rows; rows past the group are zero).
+  unsigned qa[HD / 16][4];
+  {
+    const __nv_bfloat16* qrow = a.q + (static_cast<size_t>(a.row_q_start[row]) * a.nh + static_cast<size_t>(kvh) * g) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int c = ks * 16 + quad_col;
+      const unsigned* lo_row = reinterpret_cast<const unsigned*>(qrow + static_cast<size_t>(quad_row) * HD + c);
+      const unsigned* hi_row = reinterpret_cast<const unsigned*>(qrow + static_cast<size_t>(quad_row + 8) * HD + c);
+      qa[ks][0] = quad_row < g ? lo_row[0] : 0u;
+      qa[ks][1] = quad_row + 8 < g ? hi_row[0] : 0u;
+      qa[ks][2] = quad_row < g ? lo_row[4] : 0u;       // columns + 8
+      qa[ks][3] = quad_row + 8 < g ? hi_row[4] : 0u;
+    }
+  }
+
+  const int first_tile = begin / DEC_TILE * DEC_TILE;
+  const int n_tiles = (end - first_tile + DEC_TILE - 1) / DEC_TILE;
+
+  auto load_tile = [&](int t) {
+    __nv_bfloat16* ks = tiles + (t % DEC_STAGES) * STAGE;
+    __nv_bfloat16* vs = ks + DEC_TILE * KROW;
+    const int k0 = first_tile + t * DEC_TILE;
+    for (int e = threadIdx.x; e < DEC_TILE * CHUNKS; e += DEC_WARPS * 32) {
+      const int j = e / CHUNKS, c = (e - j * CHUNKS) * 8;
+      const int pos = k0 + j;
+      bool ok = pos >= begin && pos < end;
+      const __nv_bfloat16* src = a.kv_cache;
+      if (ok) {
+        const int block = pos / a.page_size;
+        const int page = block < a.max_blocks ? table[block] : -1;
+        if (page <= 0 || page >= a.num_pages) {
+          report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, row);
+          ok = false;
+        } else {
+          src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD + c;
+        }
+      }
+      cp_async_16(ks + j * KROW + c, src, ok);
+      cp_async_16(vs + j * KROW + c, ok ? src + static_cast<long long>(a.nkv) * a.page_size * HD : src, ok);
+    }
+  };
+
+#pragma unroll
+  for (int t = 0; t < DEC_STAGES - 1; ++t) {
+    if (t < n_tiles) load_tile(t);
+    cp_async_commit();
+  }
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();              // tile t has landed for every thread; tile t-1 is no longer read
+    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1);
+    cp_async_commit();
+
+    const __nv_bfloat16* ks = tiles + (t % DEC_STAGES) * STAGE;
+    const __nv_bfloat16* vs = ks + DEC_TILE * KROW;
+    const int key0 = first_tile + t * DEC_TILE + warp * 16;   // this warp's 16 keys
+    if (key0 >= end || key0 + 16 <= begin) continue;          // uniform over the warp
+
+    // Scores: two n-tiles of 8 keys.
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < HD / 32; ++kk) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        unsigned b[4];
+        ldmatrix_x4(b, ks + (warp * 16 + nt * 8 + (lane & 7)) * KROW + kk * 32 + (lane >> 3) * 8);
+        mma_bf16_16816(s[nt], qa[2 * kk], b[0], b[1]);
+        mma_bf16_16816(s[nt], qa[2 * kk + 1], b[2], b[3]);
+      }
+    }
+
+    // Mask, running maximum, probabilities.
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int pos = key0 + nt * 8 + quad_col + (c & 1);
+        const bool valid = pos >= begin && pos < end;
+        s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
+        tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+      const float new_m = fmaxf(m_run[h], tile_max[h]);       // finite: the warp's keys hold a visible one
+      corr[h] = exp2f(m_run[h] - new_m);
+      m_run[h] = new_m;
+    }
+    float row_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        s[nt][c] = exp2f(s[nt][c] - m_run[c >> 1]);          // exp2(-inf) = 0 for masked keys
+        row_sum[c >> 1] += s[nt][c];
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+      l_run[h] = l_run[h] * corr[h] + row_sum[h];
+    }
+    unsigned pa[4];
+    pa[0] = pack_bf16(s[0][0], s[0][1]);
+    pa[1] = pack_bf16(s[0][2], s[0][3]);
+    pa[2] = pack_bf16(s[1][0], s[1][1]);
+    pa[3] = pack_bf16(s[1][2], s[1][3]);
+
+    // O = O * corr + P V over this warp's 16 keys.
+#pragma unroll
+    for (int n2 = 0; n2 < HD / 16; ++n2) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, vs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float (&acc)[4] = o[2 * n2 + half];
+        acc[0] *= corr[0]; acc[1] *= corr[0]; acc[2] *= corr[1]; acc[3] *= corr[1];
+        mma_bf16_16816(acc, pa, b[2 * half], b[2 * half + 1]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();              // every warp is done with the tiles; reuse them for the merge
+
+  // Merge the four warps (each saw its own keys) and write the split's partial result.
+  float* merge_o = reinterpret_cast<float*>(smem_raw);               // [DEC_WARPS][16][HD]
+  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                   // [DEC_WARPS][16][2]
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    float* base = merge_o + (warp * 16 + quad_row) * HD + n * 8 + quad_col;
+    base[0] = o[n][0]; base[1] = o[n][1];
+    base[8 * HD] = o[n][2]; base[8 * HD + 1] = o[n][3];
+  }
+  if ((lane & 3) == 0) {
+    merge_ml[(warp * 16 + quad_row) * 2] = m_run[0];
+    merge_ml[(warp * 16 + quad_row) * 2 + 1] = l_run[0];
+    merge_ml[(warp * 16 + quad_row + 8) * 2] = m_run[1];
+    merge_ml[(warp * 16 + quad_row + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < g * HD; e += DEC_WARPS * 32) {
+    const int h = e / HD, d = e - h * HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, merge_ml[(w * 16 + h) * 2]);
+    float acc = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float mw = merge_ml[(w * 16 + h) * 2];
+      const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mx);
+      acc += merge_o[(w * 16 + h) * HD + d] * f;
+      l += merge_ml[(w * 16 + h) * 2 + 1] * f;
+    }
+    const size_t slot = (static_cast<size_t>(r) * a.nh + static_cast<size_t>(kvh) * g + h) * a.max_splits + split;
+    a.part_o[slot * HD + d] = acc;
+    if (d == 0) {
+      a.part_ml[slot * 2] = mx;
+      a.part_ml[slot * 2 + 1] = l;
+    }
+  }
+}
+
+// out[token of row, head, :] = sum over the row's splits, weighted by their maxima.
+__global__ void paged_decode_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                            const float* __restrict__ part_ml, const int* __restrict__ rows,
+                                            const int* __restrict__ row_q_start, const int* __restrict__ row_ctx,
+                                            int num_rows, int nh, int hd, int window, int split_size, int max_splits) {
+  const int r = blockIdx.x, head = blockIdx.y;
+  const int row = rows[r];
+  if (row < 0 || row >= num_rows) return;
+  const int ctx_total = row_ctx[row] + 1;
+  const size_t base = (static_cast<size_t>(r) * nh + head) * max_splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < max_splits; ++s) {
+    int begin, end;
+    split_range(ctx_total, window, split_size, s, begin, end);
+    if (begin < end) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+  }
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.0f, l = 0.0f;
+    for (int s = 0; s < max_splits; ++s) {
+      int begin, end;
+      split_range(ctx_total, window, split_size, s, begin, end);
+      if (begin >= end) continue;
+      const float f = exp2f(part_ml[(base + s) * 2] - mx);
+      acc += part_o[(base + s) * hd + d] * f;
+      l += part_ml[(base + s) * 2 + 1] * f;
+    }
+    out[(static_cast<size_t>(row_q_start[row]) * nh + head) * hd + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+  }
+}
+
+template <int HD> size_t decode_smem_bytes() {
+  const size_t ring = static_cast<size_t>(DEC_STAGES) * 2 * DEC_TILE * (HD + 8) * sizeof(__nv_bfloat16);
+  const size_t merge = static_cast<size_t>(DEC_WARPS) * 16 * (HD + 2) * sizeof(float);
+  return ring > merge ? ring : merge;
+}
+
+template <int HD>
+int decode_launch(const DecodeArgs& a, int n_rows, cudaStream_t stream) {
+  const size_t smem = decode_smem_bytes<HD>();
+  auto kernel = paged_decode_split_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return ERR_CUDA;
+  kernel<<<dim3(a.max_splits, a.nkv, n_rows), DEC_WARPS * 32, smem, stream>>>(a);
+  return launch_result();
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+// 1 if zb_paged_decode takes this shape, else 0 (the caller then uses the general kernel).
+ZB_API int zb_paged_decode_supported(int nh, int nkv, int hd, int dtype) {
+  if (dtype != DTYPE_BF16 || nkv <= 0 || nh % nkv != 0 || nh / nkv > DEC_MAX_GROUP) return 0;
+  return hd == 32 || hd == 64 || hd == 96 || hd == 128 ? 1 : 0;
+}
+
+// Floats of scratch the two kernels need: part_o, then part_ml.
+ZB_API long long zb_paged_decode_scratch_floats(int n_rows, int nh, int hd, int max_splits) {
+  return static_cast<long long>(n_rows) * nh * max_splits * (hd + 2);
+}
+
+// Attention of `n_rows` single new tokens over their paged context.  `scratch` holds
+// zb_paged_decode_scratch_floats(...) floats.  max_splits >= ceil((longest context + 1) / split_size).
+ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                           int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
+                           const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
+                           float scale, int split_size, int max_splits, float* scratch, int* status, void* stream) {
+  if (n_rows < 0 || max_splits <= 0 || split_size <= 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0)
+    return ERR_BAD_ARGUMENT;
+  if (!zb_paged_decode_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
+  if (n_rows == 0) return OK;
+  if (n_rows > 65535 || nkv > 65535) return ERR_UNSUPPORTED;
+  DecodeArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.kv_cache = static_cast<const __nv_bfloat16*>(kv_cache);
+  a.block_table = block_table; a.rows = rows; a.row_q_start = row_q_start; a.row_ctx = row_ctx;
+  a.part_o = scratch;
+  a.part_ml = scratch + static_cast<size_t>(n_rows) * nh * max_splits * hd;
+  a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
+  a.nh = nh; a.nkv = nkv; a.window = window; a.split_size = split_size; a.max_splits = max_splits;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  auto s = static_cast<cudaStream_t>(stream);
+  int rc;
+  switch (hd) {
+    case 32: rc = decode_launch<32>(a, n_rows, s); break;
+    case 64: rc = decode_launch<64>(a, n_rows, s); break;
+    case 96: rc = decode_launch<96>(a, n_rows, s); break;
+    default: rc = decode_launch<128>(a, n_rows, s); break;
+  }
+  if (rc != OK) return rc;
+  paged_decode_combine_kernel<<<dim3(n_rows, nh), hd < 128 ? 64 : 128, 0, s>>>(
+      static_cast<__nv_bfloat16*>(out), a.part_o, a.part_ml, rows, row_q_start, row_ctx, num_rows, nh, hd, window,
+      split_size, max_splits);
+  return launch_result();
+}

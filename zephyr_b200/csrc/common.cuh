@@ -1,0 +1,86 @@
+// Shared helpers of the hand-written kernels: element types, conversions, reductions and the
+// device status word.  Everything is compiled for sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace zb {
+
+// dtype codes of the C interface.
+constexpr int DTYPE_F32 = 0;
+constexpr int DTYPE_BF16 = 1;
+
+// Return codes of the C interface (0 = launched).
+constexpr int OK = 0;
+constexpr int ERR_BAD_ARGUMENT = 1;     // a size or flag outside what the kernel takes
+constexpr int ERR_CUDA = 2;             // the launch itself failed; see zb_last_cuda_error
+constexpr int ERR_UNSUPPORTED = 3;      // a valid configuration that this kernel refuses
+
+// Codes a kernel leaves in the status word (status[0]); status[1] holds a detail value and
+// status[2] the index of the offending element.  The first error wins; nothing traps.
+constexpr int STATUS_OK = 0;
+constexpr int STATUS_TOKEN_OUT_OF_RANGE = 1;
+constexpr int STATUS_POSITION_OUT_OF_RANGE = 2;
+constexpr int STATUS_PAGE_OUT_OF_RANGE = 3;
+constexpr int STATUS_ROW_OUT_OF_RANGE = 4;
+constexpr int STATUS_BAD_LOGIT = 5;
+
+__device__ __forceinline__ void report(int* status, int code, int detail, int index) {
+  if (status != nullptr && atomicCAS(status, STATUS_OK, code) == STATUS_OK) {
+    status[1] = detail;
+    status[2] = index;
+  }
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// A norm scale may be stored in either type, whatever the activations are.
+__device__ __forceinline__ float load_scale(const void* w, int w_dtype, int i) {
+  return w_dtype == DTYPE_F32 ? static_cast<const float*>(w)[i]
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();                       // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+inline int launch_result() {
+  return cudaPeekAtLastError() == cudaSuccess ? OK : ERR_CUDA;
+}
+
+}  // namespace zb
+
+#define ZB_API extern "C" __attribute__((visibility("default")))

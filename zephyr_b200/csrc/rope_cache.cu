@@ -1,0 +1,233 @@
+// Per-head RMSNorm of q and k, NeoX rotary embedding, and the write of k and v into cache pages:
+// fused in one pass over the projection output, and as separate kernels for mixers that combine
+// other parts.
+//
+// Formulas (reference): q and k are normalised per head over the head size with one shared
+// scale vector each and the layer's eps, before the rotation (src/model/causal_lm/qwen3.cpp:53-56);
+// rotation pairs are (i, i + hd/2): x' = x*c - y*s, y' = y*c + x*s with c, s from the table row of
+// the token's position (src/layer/rotary_embedding.cu:24-47); k and v rows go to the page slot
+// page*page_size + pos % page_size (src/attention/cache.cu:17-56).  Unlike the reference, which
+// rounds to the storage type after the norm and after each product of the rotation, everything
+// here is float32 until the single store.
+//
+// Cache layout of one cache: [num_pages][2 (k, v)][num_kv_heads][page_size][head_dim].
+#include "common.cuh"
+
+namespace zb {
+
+constexpr int ROPE_WARPS = 4;
+constexpr int MAX_PAIRS_PER_LANE = 4;   // head sizes up to 256
+
+struct CacheView {
+  void* base;            // null: nothing is written
+  const int* block_table;
+  int max_blocks;        // row length of block_table
+  int page_size;
+  int num_pages;
+  int num_rows;
+};
+
+__device__ __forceinline__ long long cache_row_offset(const CacheView& c, int row, int pos, int kv_sel, int kvh,
+                                                      int nkv, int hd, int* status, int t) {
+  const int block = pos / c.page_size;
+  if (row < 0 || row >= c.num_rows || block >= c.max_blocks) {
+    report(status, STATUS_ROW_OUT_OF_RANGE, row, t);
+    return -1;
+  }
+  const int page = c.block_table[static_cast<size_t>(row) * c.max_blocks + block];
+  if (page <= 0 || page >= c.num_pages) {      // page 0 is the null page and is never written
+    report(status, STATUS_PAGE_OUT_OF_RANGE, page, t);
+    return -1;
+  }
+  return (((static_cast<long long>(page) * 2 + kv_sel) * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
+}
+
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, long long qkv_stride,
+                                          const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
+                                          int w_dtype, float eps, const float* __restrict__ cos_table,
+                                          const float* __restrict__ sin_table, int max_positions,
+                                          const int* __restrict__ positions, const int* __restrict__ token_row,
+                                          CacheView cache, int nh, int nkv, int hd, int* status) {
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5);
+  const int total_heads = cache.base != nullptr ? nh + 2 * nkv : nh;
+  if (head >= total_heads) return;
+  const int half = hd / 2;
+  const int pos = positions[t];
+  const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+  const T* src = qkv + static_cast<size_t>(t) * qkv_stride + static_cast<size_t>(head) * hd;
+
+  float x[MAX_PAIRS_PER_LANE], y[MAX_PAIRS_PER_LANE];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    x[k] = y[k] = 0.0f;
+    if (i < half) {
+      x[k] = to_float(src[i]);
+      y[k] = to_float(src[i + half]);
+      ss += x[k] * x[k] + y[k] * y[k];
+    }
+  }
+
+  T* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(t) * nh + head) * hd;
+  } else {
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    const long long off = cache_row_offset(cache, token_row[t], pos, is_k ? 0 : 1, kvh, nkv, hd, status, t);
+    if (off < 0) return;
+    dst = static_cast<T*>(cache.base) + off;
+  }
+
+  if (is_q || is_k) {
+    const void* w = is_q ? q_norm_w : k_norm_w;
+    if (w != nullptr) {
+      const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(hd) + eps);
+#pragma unroll
+      for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        if (i < half) {
+          x[k] *= inv * load_scale(w, w_dtype, i);
+          y[k] *= inv * load_scale(w, w_dtype, i + half);
+        }
+      }
+    }
+    if (cos_table != nullptr) {
+      if (pos < 0 || pos >= max_positions) {
+        if (lane == 0) report(status, STATUS_POSITION_OUT_OF_RANGE, pos, t);
+        return;
+      }
+      const float* c = cos_table + static_cast<size_t>(pos) * half;
+      const float* s = sin_table + static_cast<size_t>(pos) * half;
+#pragma unroll
+      for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        if (i < half) {
+          const float xr = x[k] * c[i] - y[k] * s[i];
+          const float yr = y[k] * c[i] + x[k] * s[i];
+          x[k] = xr;
+          y[k] = yr;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    if (i < half) {
+      dst[i] = from_float<T>(x[k]);
+      dst[i + half] = from_float<T>(y[k]);
+    }
+  }
+}
+
+// In-place rotation of x [T, heads, hd] (rows `stride` elements apart).
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, long long stride, int heads, int hd,
+                            const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                            int max_positions, const int* __restrict__ positions, int* status) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0 || pos >= max_positions) {
+    if (threadIdx.x == 0) report(status, STATUS_POSITION_OUT_OF_RANGE, pos, t);
+    return;
+  }
+  const int half = hd / 2;
+  const float* c = cos_table + static_cast<size_t>(pos) * half;
+  const float* s = sin_table + static_cast<size_t>(pos) * half;
+  for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+    const int h = e / half, i = e - h * half;
+    T* row = x + static_cast<size_t>(t) * stride + static_cast<size_t>(h) * hd;
+    const float a = to_float(row[i]), b = to_float(row[i + half]);
+    row[i] = from_float<T>(a * c[i] - b * s[i]);
+    row[i + half] = from_float<T>(b * c[i] + a * s[i]);
+  }
+}
+
+// k and v [T, nkv, hd] (rows `stride` elements apart) into their page slots.
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride,
+                                long long v_stride, const int* __restrict__ positions,
+                                const int* __restrict__ token_row, CacheView cache, int nkv, int hd, int* status) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int row = token_row[t];
+  for (int kvh = 0; kvh < nkv; ++kvh) {
+    for (int sel = 0; sel < 2; ++sel) {
+      const long long off = cache_row_offset(cache, row, pos, sel, kvh, nkv, hd, status, t);
+      if (off < 0) return;
+      const T* src = (sel == 0 ? k + static_cast<size_t>(t) * k_stride : v + static_cast<size_t>(t) * v_stride) +
+                     static_cast<size_t>(kvh) * hd;
+      T* dst = static_cast<T*>(cache.base) + off;
+      for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+    }
+  }
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+// Fused: per-head RMSNorm of q and k (scales may be null: no norm), NeoX rotation by the tables
+// (may be null: no rotation), q to q_out [T, nh*hd], k and v into the cache (kv_cache may be null:
+// only q is produced, for a layer that reads another layer's cache).
+// qkv: [T, >= (nh + 2*nkv)*hd], q heads first, then k heads, then v heads.
+ZB_API int zb_qk_norm_rope_cache(void* q_out, const void* qkv, long long qkv_stride, const void* q_norm_w,
+                                 const void* k_norm_w, int w_dtype, float eps, const float* cos_table,
+                                 const float* sin_table, int max_positions, const int* positions,
+                                 const int* token_row, void* kv_cache, const int* block_table, int max_blocks,
+                                 int page_size, int num_pages, int num_rows, int T, int nh, int nkv, int hd,
+                                 int dtype, int* status, void* stream) {
+  if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hd % 2 != 0 || page_size <= 0) return ERR_BAD_ARGUMENT;
+  if (hd > 64 * MAX_PAIRS_PER_LANE) return ERR_UNSUPPORTED;
+  if ((cos_table == nullptr) != (sin_table == nullptr)) return ERR_BAD_ARGUMENT;
+  if (T == 0) return OK;
+  const CacheView cache{kv_cache, block_table, max_blocks, page_size, num_pages, num_rows};
+  const int heads = kv_cache != nullptr ? nh + 2 * nkv : nh;
+  const dim3 grid(T, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32)
+    qk_norm_rope_cache_kernel<float><<<grid, ROPE_WARPS * 32, 0, s>>>(
+        (float*)q_out, (const float*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table, sin_table,
+        max_positions, positions, token_row, cache, nh, nkv, hd, status);
+  else
+    qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, 0, s>>>(
+        (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
+        sin_table, max_positions, positions, token_row, cache, nh, nkv, hd, status);
+  return launch_result();
+}
+
+ZB_API int zb_rope(void* x, long long stride, int T, int heads, int hd, const float* cos_table,
+                   const float* sin_table, int max_positions, const int* positions, int dtype, int* status,
+                   void* stream) {
+  if (T < 0 || heads <= 0 || hd <= 0 || hd % 2 != 0 || cos_table == nullptr || sin_table == nullptr)
+    return ERR_BAD_ARGUMENT;
+  if (T == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32)
+    rope_kernel<float><<<T, 128, 0, s>>>((float*)x, stride, heads, hd, cos_table, sin_table, max_positions,
+                                         positions, status);
+  else
+    rope_kernel<__nv_bfloat16><<<T, 128, 0, s>>>((__nv_bfloat16*)x, stride, heads, hd, cos_table, sin_table,
+                                                 max_positions, positions, status);
+  return launch_result();
+}
+
+ZB_API int zb_kv_write(const void* k, const void* v, long long k_stride, long long v_stride, const int* positions,
+                       const int* token_row, void* kv_cache, const int* block_table, int max_blocks, int page_size,
+                       int num_pages, int num_rows, int T, int nkv, int hd, int dtype, int* status, void* stream) {
+  if (T < 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || kv_cache == nullptr) return ERR_BAD_ARGUMENT;
+  if (T == 0) return OK;
+  const CacheView cache{kv_cache, block_table, max_blocks, page_size, num_pages, num_rows};
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32)
+    kv_write_kernel<float><<<T, 128, 0, s>>>((const float*)k, (const float*)v, k_stride, v_stride, positions,
+                                             token_row, cache, nkv, hd, status);
+  else
+    kv_write_kernel<__nv_bfloat16><<<T, 128, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_stride,
+                                                     v_stride, positions, token_row, cache, nkv, hd, status);
+  return launch_result();
+}

@@ -1,0 +1,398 @@
+"""Python faces of the hand-written kernels.
+
+Each function checks what the kernel cannot check for itself (device, types, contiguity, sizes),
+launches on the current CUDA stream and returns without synchronising.  There is no fallback of
+any kind: if the library cannot be built or loaded, or a kernel refuses a shape, the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..config.errors import InvalidArgumentError, ZephyrError
+from .build import BuildError, build_library
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+DECODE_SPLIT_SIZE = 256     # positions per split of the decode attention kernel: fixed, so that how a
+                            # row is cut depends on its own length only
+
+_RC_TEXT = {1: "an argument outside the kernel's contract", 2: "the CUDA launch failed",
+            3: "a configuration this kernel does not support"}
+STATUS_TEXT = {
+    1: "a token id outside the vocabulary",
+    2: "a position outside the position table",
+    3: "a page id outside the cache pool (or the null page) where a real page was expected",
+    4: "a request row or block index outside the step's tables",
+    5: "NaN or +inf among the logits",
+}
+
+
+class KernelError(ZephyrError):
+    pass
+
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+_SIGNATURES = {
+    "zb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_longlong, c_longlong, c_int,
+                   c_void_p],
+    "zb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "zb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                              c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_rope": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                c_void_p],
+    "zb_kv_write": [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_attention_simt_tile_tokens": [c_int],
+    "zb_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_float, c_int, c_void_p, c_void_p],
+    "zb_paged_decode_supported": [c_int, c_int, c_int, c_int],
+    "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+                        c_void_p],
+    "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                        c_int, c_int, c_void_p],
+    "zb_sample": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The compiled kernels, built at the first call.  Raises if they cannot be had."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            try:
+                path = build_library()
+            except BuildError as error:
+                raise KernelError(f"the CUDA kernels of zephyr_b200 are unavailable: {error}") from error
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as error:
+                raise KernelError(f"cannot load {path}: {error}") from error
+            for name, argtypes in _SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            lib.zb_paged_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+            lib.zb_paged_decode_scratch_floats.restype = c_longlong
+            _lib = lib
+    return _lib
+
+
+def library_path() -> str:
+    return library()._name
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        detail = ""
+        if rc == 2:
+            detail = f" ({torch.cuda.get_device_name()}; the library holds sm_100a code only)"
+        raise KernelError(f"{name}: {_RC_TEXT.get(rc, f'error {rc}')}{detail}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require(cond: bool, message: str) -> None:
+    if not cond:
+        raise InvalidArgumentError(message)
+
+
+def _cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("zephyr_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _i32(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        _require(t.dtype == torch.int32 and t.is_contiguous(), "index tensors must be contiguous int32")
+
+
+def new_status(device: torch.device | str = "cuda") -> torch.Tensor:
+    """The device status word kernels report into: [code, detail, index, unused]."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, where: str = "step") -> None:
+    """Read the status word (this synchronises) and raise if a kernel reported an error."""
+    code, detail, index, _ = status.tolist()
+    if code != 0:
+        status.zero_()
+        raise KernelError(f"{where}: a kernel reported {STATUS_TEXT.get(code, f'error {code}')} "
+                          f"(value {detail}, at element {index})")
+
+
+# --------------------------------------------------------------------------- elementwise
+def embedding(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, out: torch.Tensor | None = None):
+    _cuda(table, ids, status)
+    _i32(ids)
+    _require(table.dim() == 2 and table.is_contiguous() and table.dtype in DTYPE_CODE, "table must be [V, H]")
+    V, H = table.shape
+    T = ids.numel()
+    if out is None:
+        out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    _require(out.shape == (T, H) and out.dtype == table.dtype and out.is_contiguous(), "out must be [T, H]")
+    _check(library().zb_embedding(_ptr(out), _ptr(table), _ptr(ids), T, H, V, DTYPE_CODE[table.dtype],
+                                  _ptr(status), _stream()), "embedding")
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    _cuda(x, rows, status)
+    _i32(rows)
+    _require(x.dim() == 2 and x.is_contiguous() and x.dtype in DTYPE_CODE, "x must be a contiguous [T, H]")
+    out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(library().zb_gather_rows(_ptr(out), _ptr(x), _ptr(rows), rows.numel(), x.shape[1], x.shape[0],
+                                    DTYPE_CODE[x.dtype], _ptr(status), _stream()), "gather_rows")
+    return out
+
+
+def _scale_code(w: torch.Tensor, size: int) -> int:
+    _require(w.dim() == 1 and w.numel() == size and w.is_contiguous() and w.dtype in DTYPE_CODE,
+             f"a norm scale must be a contiguous vector of {size} float32 or bfloat16 values")
+    return DTYPE_CODE[w.dtype]
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm over the last dimension of a contiguous tensor (any leading shape)."""
+    _cuda(x, w)
+    _require(x.is_contiguous() and x.dtype in DTYPE_CODE, "x must be contiguous float32 or bfloat16")
+    H = x.shape[-1]
+    rows = x.numel() // H if H else 0
+    if out is None:
+        out = torch.empty_like(x)
+    _require(out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous(), "out must match x")
+    _check(library().zb_rmsnorm(_ptr(out), _ptr(x), _ptr(w), _scale_code(w, H), float(eps), rows, H, H, H,
+                                DTYPE_CODE[x.dtype], _stream()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta (in place), then return rmsnorm(residual) * w."""
+    _cuda(residual, delta, w)
+    _require(residual.dim() == 2 and residual.is_contiguous() and residual.dtype in DTYPE_CODE
+             and delta.shape == residual.shape and delta.dtype == residual.dtype and delta.is_contiguous(),
+             "residual and delta must be matching contiguous [T, H] tensors")
+    rows, H = residual.shape
+    if out is None:
+        out = torch.empty_like(residual)
+    _require(out.shape == residual.shape and out.dtype == residual.dtype and out.is_contiguous(), "out must match")
+    _check(library().zb_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(w), _scale_code(w, H), float(eps),
+                                    rows, H, DTYPE_CODE[residual.dtype], _stream()), "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """silu(gate_up[:, :I]) * gate_up[:, I:] for a contiguous [T, 2I] tensor."""
+    _cuda(gate_up)
+    _require(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.dtype in DTYPE_CODE
+             and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [T, 2I] tensor")
+    T, two_i = gate_up.shape
+    if out is None:
+        out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _require(out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype and out.is_contiguous(), "out must be [T, I]")
+    _check(library().zb_silu_mul(_ptr(out), _ptr(gate_up), T, two_i // 2, DTYPE_CODE[gate_up.dtype], _stream()),
+           "silu_mul")
+    return out
+
+
+# ------------------------------------------------------------------ position and cache
+def _check_cache(kv_cache: torch.Tensor, nkv: int, hd: int, dtype: torch.dtype) -> tuple[int, int]:
+    _require(kv_cache.dim() == 5 and kv_cache.is_contiguous() and kv_cache.shape[1] == 2
+             and kv_cache.shape[2] == nkv and kv_cache.shape[4] == hd and kv_cache.dtype == dtype,
+             "a cache must be a contiguous [pages, 2, kv_heads, page_size, head_dim] tensor of the model's type")
+    return kv_cache.shape[0], kv_cache.shape[3]
+
+
+def qk_norm_rope_cache(qkv: torch.Tensor, nh: int, nkv: int, hd: int, q_norm_w: torch.Tensor | None,
+                       k_norm_w: torch.Tensor | None, eps: float, cos: torch.Tensor | None,
+                       sin: torch.Tensor | None, positions: torch.Tensor, token_row: torch.Tensor,
+                       kv_cache: torch.Tensor | None, block_table: torch.Tensor, status: torch.Tensor,
+                       q_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused per-head norm of q and k, rotation, and the cache write; returns q as [T, nh*hd]."""
+    _cuda(qkv, positions, token_row, block_table, status, kv_cache)
+    _i32(positions, token_row, block_table)
+    T = qkv.shape[0]
+    width = (nh + 2 * nkv) * hd
+    _require(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1 and qkv.dtype in DTYPE_CODE,
+             "qkv must be [T, (heads + 2*kv_heads)*head_dim] with unit inner stride")
+    _require(hd % 2 == 0 and positions.numel() == T and token_row.numel() == T, "one position and row per token")
+    _require(block_table.dim() == 2, "block_table must be [rows, blocks]")
+    w_code = 0
+    if q_norm_w is not None or k_norm_w is not None:
+        _require(q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype == k_norm_w.dtype,
+                 "q and k norm scales come together and share a type")
+        w_code = _scale_code(q_norm_w, hd)
+        _scale_code(k_norm_w, hd)
+    max_positions = 0
+    if cos is not None:
+        _require(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32
+                 and cos.shape == sin.shape and cos.dim() == 2 and cos.shape[1] == hd // 2
+                 and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be float32 [positions, head_dim/2]")
+        max_positions = cos.shape[0]
+    pages, page_size = (0, 1)
+    if kv_cache is not None:
+        pages, page_size = _check_cache(kv_cache, nkv, hd, qkv.dtype)
+    if q_out is None:
+        q_out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    _require(q_out.shape == (T, nh * hd) and q_out.is_contiguous() and q_out.dtype == qkv.dtype, "q_out shape")
+    _check(library().zb_qk_norm_rope_cache(
+        _ptr(q_out), _ptr(qkv), qkv.stride(0), _ptr(q_norm_w), _ptr(k_norm_w), w_code, float(eps), _ptr(cos),
+        _ptr(sin), max_positions, _ptr(positions), _ptr(token_row), _ptr(kv_cache), _ptr(block_table),
+        block_table.shape[1], page_size, pages, block_table.shape[0], T, nh, nkv, hd, DTYPE_CODE[qkv.dtype],
+        _ptr(status), _stream()), "qk_norm_rope_cache")
+    return q_out
+
+
+def rope(x: torch.Tensor, heads: int, hd: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+         status: torch.Tensor) -> torch.Tensor:
+    """Rotate x [T, >= heads*hd] in place (rows may be strided)."""
+    _cuda(x, cos, sin, positions, status)
+    _i32(positions)
+    _require(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= heads * hd and x.dtype in DTYPE_CODE, "x shape")
+    _require(cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == hd // 2
+             and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be float32 [positions, head_dim/2]")
+    _check(library().zb_rope(_ptr(x), x.stride(0), x.shape[0], heads, hd, _ptr(cos), _ptr(sin), cos.shape[0],
+                             _ptr(positions), DTYPE_CODE[x.dtype], _ptr(status), _stream()), "rope")
+    return x
+
+
+def kv_write(k: torch.Tensor, v: torch.Tensor, nkv: int, hd: int, positions: torch.Tensor, token_row: torch.Tensor,
+             kv_cache: torch.Tensor, block_table: torch.Tensor, status: torch.Tensor) -> None:
+    _cuda(k, v, positions, token_row, kv_cache, block_table, status)
+    _i32(positions, token_row, block_table)
+    _require(k.dim() == 2 and v.dim() == 2 and k.stride(1) == 1 and v.stride(1) == 1 and k.dtype == v.dtype
+             and k.shape[0] == v.shape[0] and k.shape[1] >= nkv * hd and v.shape[1] >= nkv * hd, "k/v shapes")
+    pages, page_size = _check_cache(kv_cache, nkv, hd, k.dtype)
+    _check(library().zb_kv_write(_ptr(k), _ptr(v), k.stride(0), v.stride(0), _ptr(positions), _ptr(token_row),
+                                 _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+                                 block_table.shape[0], k.shape[0], nkv, hd, DTYPE_CODE[k.dtype], _ptr(status),
+                                 _stream()), "kv_write")
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_tile_tokens(group: int) -> int:
+    """New tokens of one request per tile of the general attention kernel, for this group size."""
+    return library().zb_attention_simt_tile_tokens(int(group))
+
+
+def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
+                    tile_q0: torch.Tensor, tile_tokens: int, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
+                    row_ctx: torch.Tensor, nh: int, nkv: int, hd: int, window: int, scale: float,
+                    status: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The general kernel: causal attention of every new token over its request's pages."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status)
+    _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
+    _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype in DTYPE_CODE, "q shape")
+    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    if out is None:
+        out = torch.empty_like(q)
+    _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    _check(library().zb_paged_attention_simt(
+        _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+        block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), int(tile_tokens), _ptr(row_q_start),
+        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), DTYPE_CODE[q.dtype], _ptr(status),
+        _stream()), "paged_attention")
+    return out
+
+
+def paged_decode_supported(nh: int, nkv: int, hd: int, dtype: torch.dtype) -> bool:
+    return dtype in DTYPE_CODE and bool(library().zb_paged_decode_supported(nh, nkv, hd, DTYPE_CODE[dtype]))
+
+
+def paged_decode_scratch_floats(n_rows: int, nh: int, hd: int, max_splits: int) -> int:
+    return int(library().zb_paged_decode_scratch_floats(n_rows, nh, hd, max_splits))
+
+
+def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
+                 row_q_start: torch.Tensor, row_ctx: torch.Tensor, max_context: int, nh: int, nkv: int, hd: int,
+                 window: int, scale: float, status: torch.Tensor, out: torch.Tensor,
+                 scratch: torch.Tensor | None = None, split_size: int = DECODE_SPLIT_SIZE) -> torch.Tensor:
+    """Split-context attention for rows with one new token each; writes those tokens' rows of ``out``.
+
+    ``max_context`` is at least the longest context of the rows, the new token included."""
+    _cuda(q, kv_cache, block_table, rows, row_q_start, row_ctx, status, out)
+    _i32(block_table, rows, row_q_start, row_ctx)
+    _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
+    _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    n_rows = rows.numel()
+    max_splits = max(1, math.ceil(max_context / split_size))
+    need = paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    _require(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+             f"scratch must hold {need} floats")
+    _check(library().zb_paged_decode(
+        _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+        block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
+        float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(status), _stream()), "paged_decode")
+    return out
+
+
+# ------------------------------------------------------------------------ matrix products
+def gemm_nt_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed, float32 multiply-adds on CUDA cores."""
+    _cuda(x, w)
+    _require(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.dtype == w.dtype
+             and x.dtype in DTYPE_CODE and x.stride(1) == 1 and w.stride(1) == 1, "x [M, K] and w [N, K] of one type")
+    out_dtype = out_dtype or x.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _require(out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1, "out must be [M, N]")
+    _check(library().zb_gemm_nt_simt(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                                     DTYPE_CODE[x.dtype], DTYPE_CODE[out_dtype], _stream()), "gemm_nt_simt")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = x w^T.  float32 runs on this package's CUDA-core kernel (no TF32 anywhere); bfloat16
+    runs on the vendor library's tensor-core product, as the reference's linear layers do
+    (src/layer/linear.cpp:22-24 -> cuBLASLt), with float32 accumulation."""
+    _cuda(x, w)
+    if x.dtype == torch.float32:
+        return gemm_nt_simt(x, w, out_dtype)
+    if out_dtype is None or out_dtype == x.dtype:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------------------ sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None, uniform: torch.Tensor | None,
+           status: torch.Tensor) -> torch.Tensor:
+    """One token per row of float32 logits: argmax where temperature < 1e-7 (or is absent), else a
+    draw from softmax(logits / temperature) with the row's uniform number."""
+    _cuda(logits, temperature, uniform, status)
+    _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 [rows, V]")
+    rows, V = logits.shape
+    for t in (temperature, uniform):
+        if t is not None:
+            _require(t.dtype == torch.float32 and t.numel() == rows and t.is_contiguous(), "one float32 value per row")
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(library().zb_sample(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(uniform),
+                               _ptr(status), _stream()), "sample")
+    return out
