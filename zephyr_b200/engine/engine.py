@@ -1,0 +1,356 @@
+"""The Python entry point: ``Engine(model_dir, ...).generate(token_ids, ...)``.
+
+Option names and meanings follow the reference's ``EngineConfig`` and ``Engine``
+(python/zephyr/engine/config.py:30-54, python/zephyr/engine/engine.py:50-117): ``dtype``,
+``max_seq_len`` (0 = the model's limit), ``gpu_memory_utilization``, ``scheduler``
+(``PagedSchedulerConfig``), ``kv_cache`` (``KvCacheOptions``), ``eos_token_ids``.  Prompts are
+token ids; there is no tokenizer here, so text prompts are refused.
+
+The loop is the reference's control loop without its thread (src/engine/engine.cpp:525-589,
+src/engine/generation.cpp:13-101): schedule, run one step, sample where a sequence's known tokens
+end, apply the finish rules, retire finished sequences.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+import time
+from dataclasses import dataclass, replace
+from pathlib import Path
+from typing import Any, Iterable, Sequence
+
+import torch
+
+from ..config import ConfigError, InvalidArgumentError, load_model_config
+from ..kernels import ops
+from ..parts import Model
+from ..sampling import MT19937_64, Sampler, SamplingParams
+from ..weights import Checkpoint
+from .params import (Choice, FinishReason, GenerationOutput, GenerationParams, KvCacheOptions, RequestStatus, Usage)
+from .runner import ModelRunner, StepEntry
+from .scheduler import PagedSchedulerConfig, Scheduler, Sequence as Seq, SequenceState
+
+_LOGGER = logging.getLogger("zephyr_b200")
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
+
+
+def resolve_dtype(dtype: str | torch.dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype in (torch.bfloat16, torch.float32):
+            return dtype
+    elif dtype in _DTYPES:
+        return _DTYPES[dtype]
+    raise ConfigError(f"dtype must be 'bfloat16' or 'float32', not {dtype!r}")
+
+
+@dataclass
+class _Request:
+    request_id: int
+    prompt: tuple[int, ...]
+    params: GenerationParams
+    sampling: SamplingParams
+    max_new_tokens: int
+    sequence_ids: list[tuple[int, int]]
+    finish_reasons: dict[int, FinishReason | None]
+    stop_reasons: dict[int, int | None]
+    error_message: str = ""
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    step_seconds: float = 0.0
+
+
+class Engine:
+    """One model on one GPU; synchronous batch generation."""
+
+    def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16", max_seq_len: int = 0,
+                 gpu_memory_utilization: float = 0.9, scheduler: PagedSchedulerConfig | None = None,
+                 kv_cache: KvCacheOptions | None = None, eos_token_ids: Sequence[int] | None = None,
+                 devices: Sequence[int] = (0,), weights: Any = None, model_config: Any = None):
+        if not torch.cuda.is_available():
+            raise ops.KernelError("zephyr_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        if len(tuple(devices)) != 1:
+            raise ConfigError("this engine runs on exactly one GPU")
+        if not 0.0 < gpu_memory_utilization <= 1.0:
+            raise ConfigError("gpu_memory_utilization must be in (0, 1]")
+        self.device = torch.device("cuda", tuple(devices)[0])
+        torch.cuda.set_device(self.device)
+        self.dtype = resolve_dtype(dtype)
+        self.scheduler_config = scheduler or PagedSchedulerConfig()
+        self.scheduler_config.validate()
+        kv_cache = kv_cache or KvCacheOptions()
+
+        started = time.perf_counter()
+        if model_config is None:
+            model_config = load_model_config(model)
+        self.model_config = model_config
+        spec = model_config.to_model_spec()
+        self.generation_defaults = self._read_generation_defaults(model) if model is not None else {}
+        store = weights if weights is not None else Checkpoint(model)
+        self.model = Model.load(spec, store, self.dtype, self.device)
+        _LOGGER.info("model ready: %s, %s, %.2f s", spec.architecture, self.dtype, time.perf_counter() - started)
+
+        limit = spec.max_seq_len if max_seq_len in (0, None) else min(max_seq_len, spec.max_seq_len)
+        num_pages = self._size_cache(kv_cache, gpu_memory_utilization, limit)
+        self.runner = ModelRunner(self.model, kv_cache.block_size, num_pages, self.scheduler_config.max_num_seqs,
+                                  max_seq_len=limit)
+        self.max_seq_len = limit
+        self.vocab_size = spec.vocab_size
+
+        eos = eos_token_ids
+        if eos is None:
+            eos = self.generation_defaults.get("eos_token_id")
+        if eos is None:
+            eos = spec.eos_token_ids
+        if isinstance(eos, int):
+            eos = [eos]
+        self.eos_token_ids = tuple(int(e) for e in (eos or ()))
+        for token in self.eos_token_ids:
+            if not 0 <= token < self.vocab_size:
+                raise ConfigError(f"eos token id {token} lies outside the vocabulary")
+
+        self.sampler = Sampler(self.device)
+        self.sequences: dict[tuple[int, int], Seq] = {}
+        self.scheduler = Scheduler(self.scheduler_config, self.sequences, _RunnerCache(self.runner))
+        self._requests: dict[int, _Request] = {}
+        self._generators: dict[tuple[int, int], MT19937_64] = {}
+        self._seed_source = MT19937_64(0)     # seeds for requests that bring none (engine.hpp:162)
+        self._next_request_id = 0
+        self.stats = EngineStats()
+        self._closed = False
+
+    # ------------------------------------------------------------------- set-up
+    @staticmethod
+    def _read_generation_defaults(model: str | Path) -> dict[str, Any]:
+        path = Path(model) / "generation_config.json"
+        if not path.exists():
+            return {}
+        data = json.loads(path.read_text(encoding="utf-8"))
+        if not isinstance(data, dict):
+            raise ConfigError(f"{path}: the generation configuration must be a JSON object")
+        supported = {"temperature", "top_k", "top_p", "min_p", "repetition_penalty", "max_new_tokens", "max_length",
+                     "do_sample", "eos_token_id"}
+        return {k: v for k, v in data.items() if k in supported}
+
+    def _size_cache(self, kv_cache: KvCacheOptions, utilization: float, max_seq_len: int) -> int:
+        """Number of pages: given, or what ``memory_bytes`` buys, or what is left of
+        ``gpu_memory_utilization`` x total memory after the weights, with room kept for one step's
+        activations (the reference profiles its peak instead, src/executor/causal_lm.cpp:495-537)."""
+        block = kv_cache.block_size
+        if block <= 0 or block & (block - 1):
+            raise ConfigError("kv_cache.block_size must be a power of two")
+        if kv_cache.num_blocks is not None:
+            pages = int(kv_cache.num_blocks)
+        else:
+            if kv_cache.memory_bytes is not None:
+                budget = int(kv_cache.memory_bytes)
+            else:
+                free, total = torch.cuda.mem_get_info(self.device)
+                used = total - free
+                tokens = self.scheduler_config.max_num_batched_tokens
+                spec = self.model.spec
+                transient = 8 * tokens * max(spec.hidden_size * 16, 1) * 4 \
+                    + 4 * self.scheduler_config.max_num_seqs * spec.vocab_size * 4 + (512 << 20)
+                budget = min(free - max(512 << 20, total // 50), int(utilization * total) - used) - transient
+            pages = ModelRunner.pages_for_memory(self.model, block, max(budget, 0))
+            # No use holding more pages than every resident sequence at full length can fill.
+            pages = min(pages, self.scheduler_config.max_num_seqs * -(-max_seq_len // block))
+        pages += 1      # the null page
+        if pages < 2:
+            raise ConfigError("the cache pool has no room for a single page; lower max_seq_len or free memory")
+        return pages
+
+    # ---------------------------------------------------------------- requests
+    def add_request(self, prompt: Sequence[int], params: GenerationParams | None = None) -> int:
+        """Queue one request and return its id.  ``step()`` makes progress; ``take_output`` collects."""
+        params = params or GenerationParams()
+        tokens = [int(t) for t in prompt]
+        if not tokens or len(tokens) > self.max_seq_len:
+            raise ValueError(f"Input must contain between 1 and {self.max_seq_len} tokens")
+        if any(not 0 <= t < self.vocab_size for t in tokens):
+            raise ValueError("Input contains a token ID outside the model vocabulary")
+        remaining = self.max_seq_len - len(tokens)
+        if remaining <= 0:
+            raise ValueError("The prompt must leave room for generation within max_seq_len")
+        defaults = self.generation_defaults
+        maximum = params.max_tokens
+        if maximum is None:
+            maximum = defaults.get("max_new_tokens")
+            if maximum is None and defaults.get("max_length") is not None:
+                maximum = defaults["max_length"] - len(tokens)
+            maximum = min(remaining, maximum) if maximum is not None else remaining
+        if type(maximum) is not int or not 0 < maximum <= remaining:
+            raise ValueError(f"max_tokens must be between 1 and {remaining} for this prompt")
+        sampling: dict[str, Any] = {}
+        for name in ("temperature", "top_k", "top_p", "min_p", "frequency_penalty", "presence_penalty",
+                     "repetition_penalty"):
+            value = getattr(params, name)
+            if value is None:
+                value = defaults.get(name)
+            if value is not None:
+                sampling[name] = value
+        if params.temperature is None and defaults.get("do_sample") is False:
+            sampling["temperature"] = 0.0
+        sampling_params = SamplingParams(**sampling, logits_bias=dict(params.logit_bias or {}),
+                                         top_logprobs=params.top_logprobs)
+        sampling_params.validate(self.vocab_size)
+        for token in params.stop_token_ids:
+            if not 0 <= int(token) < self.vocab_size:
+                raise ValueError("stop_token_ids contains a token outside the vocabulary")
+
+        request_id = self._next_request_id
+        self._next_request_id += 1
+        request = _Request(request_id, tuple(tokens), params, sampling_params, maximum, [], {}, {})
+        for choice in range(params.n):
+            key = (request_id, choice)
+            self.sequences[key] = Seq(key, list(tokens))
+            seed = params.seed + choice if params.seed is not None else self._seed_source.next_u64()
+            self._generators[key] = MT19937_64(seed)
+            request.sequence_ids.append(key)
+            request.finish_reasons[choice] = None
+            request.stop_reasons[choice] = None
+            self.scheduler.add(key)
+        self._requests[request_id] = request
+        return request_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished
+
+    # -------------------------------------------------------------------- step
+    def step(self) -> int:
+        """Schedule and run one step; returns the number of tokens it computed (0: nothing to do)."""
+        started = time.perf_counter()
+        plan = self.scheduler.schedule()
+        for key in plan.rejected:
+            request = self._requests[key[0]]
+            request.error_message = self.sequences[key].error_message
+            request.finish_reasons[key[1]] = FinishReason.ERROR
+        if not plan.sequences:
+            if self.scheduler.has_unfinished and not plan.preempted and not plan.rejected:
+                raise RuntimeError("the scheduler made no progress although sequences are unfinished")
+            return 0
+        entries = []
+        for item in plan.sequences:
+            sequence = self.sequences[item.sequence_id]
+            tokens = sequence.token_ids[item.start_token:item.start_token + item.num_tokens]
+            entries.append(StepEntry(item.sequence_id, tokens, (item.num_tokens - 1,) if item.sample else ()))
+        logits = self.runner.step(entries)
+        self.scheduler.commit(plan)
+        sampled = [item for item in plan.sequences if item.sample]
+        self.stats.prefill_tokens += sum(i.num_tokens for i in plan.sequences if i.num_tokens > 1 or not i.sample)
+        if sampled:
+            params = [self._requests[i.sequence_id[0]].sampling for i in sampled]
+            generators = [self._generators[i.sequence_id] for i in sampled]
+            ids = self.sampler.sample(logits, params, generators)
+            self.runner.check()
+            for item, token in zip(sampled, ids):
+                self._append_token(item.sequence_id, int(token))
+            self.stats.generated_tokens += len(ids)
+        self.stats.steps += 1
+        self.stats.preemptions = self.scheduler.num_preemptions
+        self.stats.step_seconds += time.perf_counter() - started
+        return plan.num_tokens
+
+    def _append_token(self, key: tuple[int, int], token: int) -> None:
+        """The finish rules in the reference's order (src/engine/generation.cpp:81-99).  The sampled
+        token enters the history now; its cache entry is made by the next step."""
+        sequence = self.sequences[key]
+        request = self._requests[key[0]]
+        reason = None
+        if not request.params.ignore_eos and token in self.eos_token_ids:
+            reason = FinishReason.EOS
+        elif token in request.params.stop_token_ids:
+            reason = FinishReason.STOP_TOKEN
+            request.stop_reasons[key[1]] = token
+        elif len(sequence.token_ids) - sequence.prompt_length + 1 >= request.max_new_tokens:
+            reason = FinishReason.LENGTH
+        elif len(sequence.token_ids) >= self.max_seq_len:
+            reason = FinishReason.MODEL_LENGTH
+        sequence.token_ids.append(token)
+        if reason is not None:
+            request.finish_reasons[key[1]] = reason
+            self.scheduler.finish(key)
+
+    def cancel(self, request_id: int) -> None:
+        request = self._requests[request_id]
+        for key in request.sequence_ids:
+            if not self.sequences[key].is_terminal:
+                request.finish_reasons[key[1]] = FinishReason.CANCELED
+                self.scheduler.finish(key)
+
+    def is_finished(self, request_id: int) -> bool:
+        return all(self.sequences[key].is_terminal for key in self._requests[request_id].sequence_ids)
+
+    def take_output(self, request_id: int) -> GenerationOutput:
+        """The finished request's output; the engine forgets the request."""
+        request = self._requests.pop(request_id)
+        choices = []
+        states = []
+        for key in request.sequence_ids:
+            sequence = self.sequences.pop(key)
+            self._generators.pop(key, None)
+            states.append(sequence.state)
+            choices.append(Choice(key[1], tuple(sequence.token_ids[sequence.prompt_length:]),
+                                  request.finish_reasons[key[1]], request.stop_reasons[key[1]]))
+        if any(s == SequenceState.REJECTED for s in states):
+            status = RequestStatus.REJECTED
+        elif any(s == SequenceState.ERROR for s in states):
+            status = RequestStatus.ERROR
+        elif any(c.finish_reason == FinishReason.CANCELED for c in choices):
+            status = RequestStatus.CANCELED
+        else:
+            status = RequestStatus.COMPLETED
+        usage = Usage(len(request.prompt), sum(len(c.token_ids) for c in choices))
+        return GenerationOutput(request_id, request.prompt, tuple(choices), status, usage, request.error_message)
+
+    # ---------------------------------------------------------------- generate
+    def generate(self, prompts, params: GenerationParams | None = None, **kwargs: Any):
+        """Generate for one prompt (a sequence of token ids) or a batch (a sequence of those); keyword
+        arguments override ``params``.  Returns one ``GenerationOutput`` or a list in input order."""
+        if self._closed:
+            raise RuntimeError("the engine is closed")
+        params = replace(params, **kwargs) if params is not None else GenerationParams(**kwargs)
+        if isinstance(prompts, str) or (isinstance(prompts, Sequence) and prompts and isinstance(prompts[0], str)):
+            raise ValueError("Text APIs require a tokenizer; this engine takes token ids")
+        single = isinstance(prompts, Sequence) and bool(prompts) and isinstance(prompts[0], int)
+        inputs: Iterable[Sequence[int]] = [prompts] if single else prompts
+        ids = [self.add_request(prompt, params) for prompt in inputs]
+        while any(not self.is_finished(i) for i in ids):
+            self.step()
+        outputs = [self.take_output(i) for i in ids]
+        return outputs[0] if single else outputs
+
+    def close(self) -> None:
+        self._closed = True
+
+    def __enter__(self) -> "Engine":
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.close()
+
+
+class _RunnerCache:
+    """The scheduler's view of the cache: the manager, with the runner's device-side duties
+    (zeroing a new state slot, poisoning freed pages in tests) done on the way."""
+
+    def __init__(self, runner: ModelRunner):
+        self._runner = runner
+
+    def add_request(self, request_id, reserve_tokens: int = 0, step_tokens: int = 1) -> bool:
+        return self._runner.add_request(request_id, reserve_tokens, step_tokens)
+
+    def ensure_capacity(self, request_id, length: int) -> bool:
+        return self._runner.manager.ensure_capacity(request_id, length)
+
+    def free_request(self, request_id) -> None:
+        self._runner.free_request(request_id)
+
+    def fits_at_all(self, length: int, step_tokens: int) -> bool:
+        return self._runner.manager.fits_at_all(length, step_tokens)

@@ -1,0 +1,187 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+``ModelRunner.step`` takes portions of prompts beside single decoded tokens, cut anywhere, runs
+exactly the tokens it is given as one batch, writes their cache entries and returns float32 logits
+at the wanted places.  It is what generation, trace replay and the bench all call.
+
+The reference's executor (src/executor/causal_lm.cpp:111-295,551-624) builds per-phase batches
+(padded prompt, packed prompt, prefix gather, decode) and never mixes phases; here every batch
+is one flat token stream with per-row metadata, and the attention kernels sort out which rows
+are long and which are single tokens.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage, bytes_per_page
+from ..config.errors import InvalidArgumentError, OutOfPagesError
+from ..kernels import ops
+from ..parts import Model, StepContext
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens, and the places among them whose logits are wanted."""
+
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class ModelRunner:
+    def __init__(self, model: Model, page_size: int, num_pages: int, max_requests: int,
+                 max_seq_len: int | None = None):
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.max_seq_len = min(max_seq_len or model.spec.max_seq_len, model.spec.max_seq_len)
+        self.manager = CacheManager(model.cache_specs, page_size, num_pages, max_requests)
+        self.storage = CacheStorage(self.manager, model.dtype, model.device)
+        self.status = ops.new_status(model.device)
+        self.poison_freed_pages = False      # tests: NaN into every page that is given back
+        self.steps = 0
+
+    # ------------------------------------------------------------------ sizing
+    @staticmethod
+    def pages_for_memory(model: Model, page_size: int, memory_bytes: int) -> int:
+        per_page = bytes_per_page(model.cache_specs, page_size, model.dtype)
+        return max(0, memory_bytes // max(per_page, 1))
+
+    def cache_bytes_per_token(self) -> int:
+        return bytes_per_page(self.model.cache_specs, self.manager.page_size, self.dtype) // self.manager.page_size
+
+    # --------------------------------------------------------------- lifecycle
+    def add_request(self, request_id: Hashable, reserve_tokens: int = 0, step_tokens: int = 1) -> bool:
+        """Admit a request (state slot, page reservation).  False if there is no room."""
+        if not self.manager.add_request(request_id, reserve_tokens, step_tokens):
+            return False
+        if self.manager.state_cache_ids:
+            self.storage.reset_state_slot(self.manager, self.manager.state_slot(request_id))
+        return True
+
+    def free_request(self, request_id: Hashable) -> None:
+        if self.poison_freed_pages:
+            for group in range(len(self.manager.groups)):
+                self.storage.poison_pages(self.manager, group, list(self.manager.block_table(request_id, group)))
+        self.manager.free_request(request_id)
+
+    def num_computed(self, request_id: Hashable) -> int:
+        return self.manager.computed(request_id)
+
+    # -------------------------------------------------------------------- step
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise InvalidArgumentError("a step needs at least one entry")
+        seen = set()
+        vocab = self.model.spec.vocab_size
+        for entry in entries:
+            if entry.request_id not in self.manager:
+                raise InvalidArgumentError(f"request {entry.request_id!r} is unknown to the runner")
+            if entry.request_id in seen:
+                raise InvalidArgumentError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            n = len(entry.tokens)
+            if n == 0:
+                raise InvalidArgumentError(f"request {entry.request_id!r} brings no tokens")
+            if self.manager.computed(entry.request_id) + n > self.max_seq_len:
+                raise InvalidArgumentError(
+                    f"request {entry.request_id!r} would exceed the maximum sequence length {self.max_seq_len}")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise InvalidArgumentError(f"token id {token} lies outside the vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= int(place) < n:
+                    raise InvalidArgumentError(f"wanted place {place} lies outside the {n} tokens brought")
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        manager = self.manager
+        q_len = [len(e.tokens) for e in entries]
+        ctx_before = [manager.computed(e.request_id) for e in entries]
+        for entry, ctx, n in zip(entries, ctx_before, q_len):
+            if not manager.ensure_capacity(entry.request_id, ctx + n):
+                raise OutOfPagesError(
+                    f"no pages left for request {entry.request_id!r} ({ctx} cached + {n} new tokens); "
+                    f"free pages per group: {[g.pool.num_free for g in manager.groups]}")
+        R, T = len(entries), sum(q_len)
+        q_start = np.zeros(R, dtype=np.int32)
+        np.cumsum(q_len[:-1], out=q_start[1:])
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        positions = np.concatenate([np.arange(c, c + n, dtype=np.int32) for c, n in zip(ctx_before, q_len)])
+        token_row = np.repeat(np.arange(R, dtype=np.int32), q_len)
+        slots = np.asarray([manager.state_slot(e.request_id) for e in entries], dtype=np.int32)
+        tables = []
+        for group in range(len(manager.groups)):
+            rows = [manager.block_table(e.request_id, group) for e in entries]
+            width = max(1, max(len(r) for r in rows))
+            table = np.zeros((R, width), dtype=np.int32)
+            for i, r in enumerate(rows):
+                table[i, :len(r)] = r
+            tables.append(table)
+        logit_tokens = np.asarray([q_start[i] + int(p) for i, e in enumerate(entries) for p in e.want], dtype=np.int32)
+        decode_rows = np.asarray([i for i, n in enumerate(q_len) if n == 1], dtype=np.int32)
+        max_decode_context = max([ctx_before[i] + 1 for i in decode_rows], default=0)
+        tiles = {}
+        for tile_tokens, which in self.model.tile_requests:
+            tile_row, tile_q0 = [], []
+            for i, n in enumerate(q_len):
+                if which == "multi" and n == 1:
+                    continue
+                for q0 in range(0, n, tile_tokens):
+                    tile_row.append(i)
+                    tile_q0.append(q0)
+            tiles[(tile_tokens, which)] = (np.asarray(tile_row, dtype=np.int32), np.asarray(tile_q0, dtype=np.int32))
+
+        # One pinned buffer, one copy; the device tensors are views of it.
+        arrays = [token_ids, positions, token_row, q_start, np.asarray(q_len, dtype=np.int32),
+                  np.asarray(ctx_before, dtype=np.int32), slots, logit_tokens, decode_rows]
+        arrays += [t.reshape(-1) for t in tables]
+        for pair in tiles.values():
+            arrays += list(pair)
+        sizes = [a.size for a in arrays]
+        host = torch.empty(max(1, sum(sizes)), dtype=torch.int32, pin_memory=True)
+        if sum(sizes):
+            np.concatenate(arrays, out=host.numpy()[:sum(sizes)])
+        device = host.to(self.device, non_blocking=True)
+        views, offset = [], 0
+        for size in sizes:
+            views.append(device[offset:offset + size])
+            offset += size
+        (d_tokens, d_pos, d_row, d_qstart, d_qlen, d_ctx, d_slots, d_logit, d_decode), rest = views[:9], views[9:]
+        d_tables = [rest[g].view(R, tables[g].shape[1]) for g in range(len(tables))]
+        rest = rest[len(tables):]
+        d_tiles = {key: (rest[2 * i], rest[2 * i + 1]) for i, key in enumerate(tiles)}
+        return StepContext(
+            num_tokens=T, num_rows=R, token_ids=d_tokens, positions=d_pos, token_row=d_row, row_q_start=d_qstart,
+            row_q_len=d_qlen, row_ctx=d_ctx, state_slots=d_slots, block_tables=d_tables,
+            group_of_cache=manager.group_of_cache, logit_tokens=d_logit, decode_rows=d_decode,
+            num_decode_rows=int(decode_rows.size), max_decode_context=int(max_decode_context), tiles=d_tiles,
+            caches=self.storage, status=self.status, dtype=self.dtype, host_q_len=list(q_len),
+            host_ctx=list(ctx_before), host_slots=slots.tolist())
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch.  Returns float32 logits [sum of wanted places, vocab] on the
+        device, in the order of the entries and of each entry's ``want``.  The call does not wait for
+        the GPU; ``check()`` (or reading the logits on the host and then ``check()``) does."""
+        self._validate(entries)
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx)
+        for entry, before in zip(entries, ctx.host_ctx):
+            if self.poison_freed_pages:
+                old = [list(self.manager.block_table(entry.request_id, g)) for g in range(len(self.manager.groups))]
+            self.manager.commit(entry.request_id, before + len(entry.tokens))
+            if self.poison_freed_pages:
+                for g, pages in enumerate(old):
+                    now = self.manager.block_table(entry.request_id, g)
+                    self.storage.poison_pages(self.manager, g, [p for p, q in zip(pages, now) if p != q])
+        self.steps += 1
+        return logits
+
+    def check(self) -> None:
+        """Wait for the device and raise if a kernel of an earlier step reported an error."""
+        ops.check_status(self.status, "model step")

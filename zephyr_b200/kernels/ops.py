@@ -234,7 +234,7 @@ def qk_norm_rope_cache(qkv: torch.Tensor, nh: int, nkv: int, hd: int, q_norm_w: 
     _cuda(qkv, positions, token_row, block_table, status, kv_cache)
     _i32(positions, token_row, block_table)
     T = qkv.shape[0]
-    width = (nh + 2 * nkv) * hd
+    width = (nh + 2 * nkv) * hd if kv_cache is not None else nh * hd
     _require(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1 and qkv.dtype in DTYPE_CODE,
              "qkv must be [T, (heads + 2*kv_heads)*head_dim] with unit inner stride")
     _require(hd % 2 == 0 and positions.numel() == T and token_row.numel() == T, "one position and row per token")

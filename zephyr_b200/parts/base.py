@@ -1,0 +1,186 @@
+"""What every part is, the registries that name the kinds, and what a step hands to the parts.
+
+A part is built from its spec (all sizes and constants), the loaded tensors it named in
+``weight_decls`` and the engine's dtype.  It never learns which model it is in.
+
+Registering a new kind is one call, from anywhere (a test included):
+
+    register_mixer("my_mixer", MyMixer)
+
+with the interface of the matching base class below.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping
+
+import torch
+
+from ..cache import CacheStorage, PagedCacheSpec, StateCacheSpec
+from ..config.errors import ConfigError
+from ..config.spec import FeedForwardSpec, LayerCall, MixerSpec, NormSpec, PositionSpec
+from ..weights.loader import WeightDecl
+
+
+@dataclass
+class StepContext:
+    """One step's batch, as the parts see it.  Index tensors are int32 on the device.
+
+    The new tokens of all rows (requests) lie behind one another in one stream of ``num_tokens``
+    tokens; row ``r`` owns tokens ``row_q_start[r] .. row_q_start[r] + row_q_len[r]`` and had
+    ``row_ctx[r]`` tokens in the cache before this step, so its first new token sits at position
+    ``row_ctx[r]``."""
+
+    num_tokens: int
+    num_rows: int
+    token_ids: torch.Tensor            # [T]
+    positions: torch.Tensor            # [T] absolute position of each token in its request
+    token_row: torch.Tensor            # [T] row of each token
+    row_q_start: torch.Tensor          # [R]
+    row_q_len: torch.Tensor            # [R]
+    row_ctx: torch.Tensor              # [R]
+    state_slots: torch.Tensor          # [R] state slot of each row's request
+    block_tables: list[torch.Tensor]   # per cache group: [R, max_blocks]
+    group_of_cache: Mapping[int, int]  # cache id -> group
+    logit_tokens: torch.Tensor         # [n] stream indices of the tokens whose logits are wanted
+    decode_rows: torch.Tensor          # [n_dec] rows with exactly one new token
+    num_decode_rows: int
+    max_decode_context: int            # longest context among decode rows, the new token included
+    tiles: dict[tuple[int, str], tuple[torch.Tensor, torch.Tensor]]   # (tile_tokens, which) -> (tile_row, tile_q0)
+    caches: CacheStorage
+    status: torch.Tensor
+    dtype: torch.dtype
+    # Host copies for parts that plan on the host.
+    host_q_len: list[int] = field(default_factory=list)
+    host_ctx: list[int] = field(default_factory=list)
+    host_slots: list[int] = field(default_factory=list)
+
+    def block_table(self, cache_id: int) -> torch.Tensor:
+        return self.block_tables[self.group_of_cache[cache_id]]
+
+
+class Part:
+    """Common ground of all parts."""
+
+    @staticmethod
+    def weight_decls(spec) -> dict[str, WeightDecl]:
+        """Full tensor names this part reads, with shapes and roles."""
+        return {}
+
+    def weights_read(self) -> list[torch.Tensor]:
+        """The weight tensors one forward pass reads (views of another listed tensor left out)."""
+        return [value for value in vars(self).values()
+                if isinstance(value, torch.Tensor) and value.is_floating_point() and not value._is_view()]
+
+
+class Norm(Part):
+    def __init__(self, spec: NormSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Normalise the last dimension of ``x`` ([T, size])."""
+        raise NotImplementedError
+
+    def add_forward(self, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+        """``residual += delta`` in place, then the norm of the sum.  The default does the two steps
+        apart; a kind with a fused kernel overrides it."""
+        residual.add_(delta)
+        return self.forward(residual)
+
+
+class PositionEncoding(Part):
+    def __init__(self, spec: PositionSpec, dtype: torch.dtype, device: torch.device | str): ...
+
+    def apply(self, x: torch.Tensor, heads: int, positions: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        """Encode positions into ``x`` [T, heads*head_dim] in place and return it."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
+                 device: torch.device | str): ...
+
+    @staticmethod
+    def cache_spec(spec: MixerSpec) -> PagedCacheSpec | StateCacheSpec | None:
+        """What this mixer stores per request: pages, a fixed state, or nothing."""
+        return None
+
+    @staticmethod
+    def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
+        """Tilings of the new tokens this mixer wants in ``StepContext.tiles``: (tokens per tile,
+        "all" rows or only "multi"-token rows)."""
+        return []
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+        """x [T, hidden] -> [T, hidden], reading and (if ``call.writes_cache``) writing cache ``call.cache``."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def __init__(self, spec: FeedForwardSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class ResidualStream:
+    """The hidden states between blocks: the stream itself and a summand not yet added, which the
+    next norm adds in the same pass that normalises."""
+
+    hidden: torch.Tensor
+    pending: torch.Tensor | None = None
+
+    def flush(self) -> torch.Tensor:
+        if self.pending is not None:
+            self.hidden.add_(self.pending)
+            self.pending = None
+        return self.hidden
+
+
+class Block(Part):
+    """The arrangement of a layer's parts around the residual stream."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm): ...
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
+        raise NotImplementedError
+
+
+NORMS: dict[str, type] = {}
+POSITION_ENCODINGS: dict[str, type] = {}
+MIXERS: dict[str, type] = {}
+FEED_FORWARDS: dict[str, type] = {}
+BLOCKS: dict[str, type] = {}
+
+
+def _register(table: dict[str, type], what: str, kind: str, cls: type, replace: bool) -> None:
+    if kind in table and not replace:
+        raise ConfigError(f"{what} kind '{kind}' is already registered")
+    table[kind] = cls
+
+
+def register_norm(kind: str, cls: type, replace: bool = False) -> None:
+    _register(NORMS, "norm", kind, cls, replace)
+
+
+def register_position_encoding(kind: str, cls: type, replace: bool = False) -> None:
+    _register(POSITION_ENCODINGS, "position encoding", kind, cls, replace)
+
+
+def register_mixer(kind: str, cls: type, replace: bool = False) -> None:
+    _register(MIXERS, "mixer", kind, cls, replace)
+
+
+def register_feed_forward(kind: str, cls: type, replace: bool = False) -> None:
+    _register(FEED_FORWARDS, "feed-forward", kind, cls, replace)
+
+
+def register_block(kind: str, cls: type, replace: bool = False) -> None:
+    _register(BLOCKS, "block", kind, cls, replace)
+
+
+def lookup(table: dict[str, type], what: str, kind: str) -> type:
+    if kind not in table:
+        raise ConfigError(f"unknown {what} kind '{kind}'; registered: {', '.join(sorted(table)) or 'none'}")
+    return table[kind]

@@ -1,0 +1,32 @@
+"""Arrangements of a layer's parts around the residual stream.
+
+``prenorm_residual``: r = x + mixer(norm1(x)); x' = r + ffn(norm2(r)), the sums in float32
+(reference: src/model/causal_lm/qwen3.cpp:79-88).  Each sum is folded into the norm that follows
+it, so the block hands its last summand on as ``pending``.
+"""
+
+from __future__ import annotations
+
+from ..config.spec import LayerCall
+from .base import Block, FeedForward, Mixer, Norm, ResidualStream, StepContext, register_block
+
+
+class PreNormResidual(Block):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
+        if stream.pending is None:
+            normed = self.mixer_norm.forward(stream.hidden)
+        else:
+            normed = self.mixer_norm.add_forward(stream.hidden, stream.pending)
+        mixed = self.mixer.forward(normed, ctx, call)
+        normed = self.feed_forward_norm.add_forward(stream.hidden, mixed)
+        stream.pending = self.feed_forward.forward(normed)
+        return stream
+
+
+register_block("prenorm_residual", PreNormResidual)
