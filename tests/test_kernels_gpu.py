@@ -1,0 +1,455 @@
+"""Each kernel alone against a plain float64 PyTorch reference of the same operation, at sizes other
+than the engine's tiny configurations (sizes that are no power of two, odd head counts and groups,
+page edges, windows), in 32-bit and in bfloat16."""
+
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rand(shape, dtype, device, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(device)
+
+
+@pytest.fixture(scope="module")
+def ops(cuda_device):
+    from zephyr_b200.kernels import ops as module
+
+    module.library()
+    return module
+
+
+def ref_rmsnorm(x, w, eps):
+    x = x.double()
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+
+
+# ------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,V", [(100, 77), (1000, 311), (4096, 1000), (8, 3)])
+def test_embedding(ops, cuda_device, dtype, H, V):
+    table = rand((V, H), dtype, cuda_device, 1)
+    ids = torch.randint(0, V, (37,), generator=torch.Generator().manual_seed(2)).int().to(cuda_device)
+    status = ops.new_status(cuda_device)
+    out = ops.embedding(table, ids, status)
+    assert torch.equal(out, table[ids.long()])
+    ops.check_status(status)
+
+
+def test_embedding_reports_bad_token(ops, cuda_device):
+    table = rand((10, 16), torch.float32, cuda_device, 1)
+    ids = torch.tensor([1, 10, 3], dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    ops.embedding(table, ids, status)
+    with pytest.raises(ops.KernelError, match="token id"):
+        ops.check_status(status)
+    ops.check_status(status)        # the word was cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("rows,H", [(5, 100), (3, 1000), (2, 4096), (7, 24), (1, 5120)])
+def test_rmsnorm_and_fused_add(ops, cuda_device, dtype, wdtype, rows, H):
+    x = rand((rows, H), dtype, cuda_device, 3, 2.0)
+    d = rand((rows, H), dtype, cuda_device, 4)
+    w = (1 + rand((H,), torch.float32, cuda_device, 5, 0.1)).to(wdtype)
+    eps = 1e-5
+    got = ops.rmsnorm(x, w, eps)
+    assert (got.double() - ref_rmsnorm(x, w, eps)).abs().max() <= tol(dtype, 4.0)
+    residual = x.clone()
+    got = ops.add_rmsnorm(residual, d, w, eps)
+    summed = (x.double() + d.double()).to(dtype)           # one rounding of the float sum
+    assert torch.equal(residual, summed)
+    assert (got.double() - ref_rmsnorm(summed, w, eps)).abs().max() <= tol(dtype, 4.0)
+    # fused and separate give the same bits
+    assert torch.equal(got, ops.rmsnorm(summed, w, eps))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_over_heads(ops, cuda_device, dtype):
+    x = rand((9, 5, 48), dtype, cuda_device, 6)
+    w = (1 + rand((48,), torch.float32, cuda_device, 7, 0.1)).to(dtype)
+    got = ops.rmsnorm(x, w, 1e-6)
+    assert (got.double() - ref_rmsnorm(x, w, 1e-6)).abs().max() <= tol(dtype, 4.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(5, 200), (3, 3072), (2, 37), (130, 144)])
+def test_silu_mul(ops, cuda_device, dtype, T, I):
+    gu = rand((T, 2 * I), dtype, cuda_device, 8, 3.0)
+    got = ops.silu_mul(gu)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    assert (got.double() - g / (1 + torch.exp(-g)) * u).abs().max() <= tol(dtype, 8.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gather_rows(ops, cuda_device, dtype):
+    x = rand((50, 96), dtype, cuda_device, 9)
+    rows = torch.tensor([49, 0, 7, 7, 13], dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    assert torch.equal(ops.gather_rows(x, rows, status), x[rows.long()])
+    ops.check_status(status)
+
+
+# ------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [(1, 311, 100), (7, 64, 64), (130, 200, 96), (65, 1000, 1030), (3, 5, 1)])
+def test_gemm_simt_float32_is_exact_float32(ops, cuda_device, M, N, K):
+    x = rand((M, K), torch.float32, cuda_device, 10)
+    w = rand((N, K), torch.float32, cuda_device, 11)
+    got = ops.gemm_nt_simt(x, w)
+    expected = x.double() @ w.double().T
+    # float32 accumulation of K products of magnitude ~1: error ~ sqrt(K) * 2^-24 * |terms|.
+    assert (got.double() - expected).abs().max() <= 3e-6 * math.sqrt(K) * 4
+    # TF32 would be wrong in the 4th digit: this bound is 1000x tighter than that.
+
+
+def test_gemm_simt_rows_do_not_depend_on_batch(ops, cuda_device):
+    x = rand((70, 200), torch.float32, cuda_device, 12)
+    w = rand((311, 200), torch.float32, cuda_device, 13)
+    whole = ops.gemm_nt_simt(x, w)
+    assert torch.equal(ops.gemm_nt_simt(x[5:6].contiguous(), w), whole[5:6])
+    assert torch.equal(ops.gemm_nt_simt(x[60:].contiguous(), w), whole[60:])
+
+
+def test_gemm_simt_bfloat16_inputs(ops, cuda_device):
+    x = rand((33, 136), torch.bfloat16, cuda_device, 14)
+    w = rand((77, 136), torch.bfloat16, cuda_device, 15)
+    got = ops.gemm_nt_simt(x, w, out_dtype=torch.float32)
+    assert (got.double() - x.double() @ w.double().T).abs().max() <= 1e-4
+    assert ops.linear(x, w, out_dtype=torch.float32).dtype == torch.float32
+    assert (ops.linear(x, w, out_dtype=torch.float32).double() - x.double() @ w.double().T).abs().max() <= 1e-3
+
+
+# ------------------------------------------------------- norm + rotation + cache
+def ref_rope(x, positions, theta):
+    """x [T, heads, hd] double; float32 angles as the reference computes them."""
+    hd = x.shape[-1]
+    i = torch.arange(hd // 2, dtype=torch.float32)
+    inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2.0 * i / hd)
+    ang = (positions.float()[:, None] * inv[None, :]).double()
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = x[..., : hd // 2], x[..., hd // 2:]
+    return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+
+def make_tables(ctx_lens, page_size, num_pages, seed):
+    """Random distinct pages for each row's context; returns (block_table tensor rows, list of lists)."""
+    rng = random.Random(seed)
+    pages = list(range(1, num_pages))
+    rng.shuffle(pages)
+    tables, cursor = [], 0
+    for n in ctx_lens:
+        need = -(-n // page_size)
+        tables.append(pages[cursor:cursor + need])
+        cursor += need
+    assert cursor <= len(pages)
+    width = max(1, max(len(t) for t in tables))
+    table = torch.zeros((len(tables), width), dtype=torch.int32)
+    for r, t in enumerate(tables):
+        table[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    return table, tables
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 4), (6, 3, 48, 8), (16, 8, 128, 16), (5, 5, 256, 32), (8, 1, 80, 64)])
+def test_qk_norm_rope_cache(ops, cuda_device, dtype, nh, nkv, hd, page):
+    from zephyr_b200.parts import rope_tables
+
+    q_lens, ctx = [3, 1, 9], [5, 31, 0]
+    T, R = sum(q_lens), len(q_lens)
+    theta, eps = 50000.0, 1e-5
+    qkv = rand((T, (nh + 2 * nkv) * hd), dtype, cuda_device, 20)
+    wq = (1 + rand((hd,), torch.float32, cuda_device, 21, 0.1)).to(dtype)
+    wk = (1 + rand((hd,), torch.float32, cuda_device, 22, 0.1)).to(dtype)
+    cos, sin = (t.to(cuda_device) for t in rope_tables(hd, 64, theta))
+    positions = torch.cat([torch.arange(c, c + n) for c, n in zip(ctx, q_lens)]).int().to(cuda_device)
+    token_row = torch.repeat_interleave(torch.arange(R), torch.tensor(q_lens)).int().to(cuda_device)
+    num_pages = 40
+    table, tables = make_tables([c + n for c, n in zip(ctx, q_lens)], page, num_pages, 23)
+    cache = torch.full((num_pages, 2, nkv, page, hd), float("nan"), dtype=dtype, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    q = ops.qk_norm_rope_cache(qkv, nh, nkv, hd, wq, wk, eps, cos, sin, positions, token_row, cache,
+                               table.to(cuda_device), status)
+    ops.check_status(status)
+    x = qkv.double().cpu()
+    pos = positions.cpu()
+    q_ref = ref_rope(ref_rmsnorm(x[:, : nh * hd].view(T, nh, hd), wq.cpu(), eps), pos, theta)
+    k_ref = ref_rope(ref_rmsnorm(x[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd), wk.cpu(), eps), pos, theta)
+    v_ref = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    assert (q.double().cpu().view(T, nh, hd) - q_ref).abs().max() <= tol(dtype, 8.0)
+    cache_cpu = cache.double().cpu()
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for t in range(T):
+        r, p = int(token_row[t]), int(pos[t])
+        pg, off = tables[r][p // page], p % page
+        written[pg, off] = True
+        assert (cache_cpu[pg, 0, :, off] - k_ref[t]).abs().max() <= tol(dtype, 8.0)
+        assert torch.equal(cache_cpu[pg, 1, :, off], v_ref[t])
+    # nothing else was touched
+    untouched = cache_cpu[:, 0, 0, :, 0][~written]
+    assert torch.isnan(untouched).all()
+
+    # The separate kernels give the same q (float32: the same bits up to the norm's rounding).
+    q2 = ops.rmsnorm(qkv[:, : nh * hd].contiguous().view(T, nh, hd), wq, eps).view(T, nh * hd)
+    q2 = ops.rope(q2, nh, hd, cos, sin, positions, status)
+    assert (q2.double() - q.double()).abs().max() <= tol(dtype, 8.0)
+    k2 = ops.rmsnorm(qkv[:, nh * hd: (nh + nkv) * hd].contiguous().view(T, nkv, hd), wk, eps).view(T, nkv * hd)
+    k2 = ops.rope(k2, nkv, hd, cos, sin, positions, status)
+    cache2 = torch.zeros_like(cache)
+    ops.kv_write(k2, qkv[:, (nh + nkv) * hd:], nkv, hd, positions, token_row, cache2, table.to(cuda_device), status)
+    ops.check_status(status)
+    mask = written[:, None, None, :, None].expand_as(cache_cpu)
+    assert (cache2.double().cpu()[mask] - cache_cpu[mask]).abs().max() <= tol(dtype, 8.0)
+
+
+def test_cache_write_reports_bad_page_and_position(ops, cuda_device):
+    from zephyr_b200.parts import rope_tables
+
+    nh, nkv, hd, page = 2, 1, 16, 4
+    qkv = rand((2, (nh + 2 * nkv) * hd), torch.float32, cuda_device, 30)
+    cos, sin = (t.to(cuda_device) for t in rope_tables(hd, 8, 10000.0))
+    cache = torch.zeros((6, 2, nkv, page, hd), device=cuda_device)
+    token_row = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    table = torch.tensor([[9]], dtype=torch.int32, device=cuda_device)       # page 9 of 6
+    ops.qk_norm_rope_cache(qkv, nh, nkv, hd, None, None, 0.0, cos, sin,
+                           torch.tensor([0, 1], dtype=torch.int32, device=cuda_device), token_row, cache, table, status)
+    with pytest.raises(ops.KernelError, match="page id"):
+        ops.check_status(status)
+    table = torch.tensor([[1, 2, 3]], dtype=torch.int32, device=cuda_device)
+    ops.qk_norm_rope_cache(qkv, nh, nkv, hd, None, None, 0.0, cos, sin,
+                           torch.tensor([7, 8], dtype=torch.int32, device=cuda_device), token_row, cache, table, status)
+    with pytest.raises(ops.KernelError, match="position"):
+        ops.check_status(status)
+
+
+# --------------------------------------------------------------------- attention
+def ref_attention_row(q, K, V, ctx, q_len, window, nh, nkv):
+    """q [q_len, nh, hd]; K, V [ctx + q_len, nkv, hd] doubles; the new tokens sit at ctx..ctx+q_len-1."""
+    hd = q.shape[-1]
+    g = nh // nkv
+    out = torch.zeros_like(q)
+    for i in range(q_len):
+        p = ctx + i
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(nh):
+            s = (K[lo:p + 1, h // g] @ q[i, h]) / math.sqrt(hd)
+            out[i, h] = torch.softmax(s, 0) @ V[lo:p + 1, h // g]
+    return out
+
+
+def build_paged_case(device, dtype, nh, nkv, hd, page, q_lens, ctx, seed, spike=None):
+    """Dense random K/V per row placed into shuffled pages of a NaN-filled cache.
+    ``spike=(row, key_position)`` scales that key and the row's last query so that this one key,
+    however far away, must dominate the softmax."""
+    R = len(q_lens)
+    totals = [c + n for c, n in zip(ctx, q_lens)]
+    num_pages = sum(-(-n // page) for n in totals) + 3
+    table, tables = make_tables(totals, page, num_pages, seed)
+    cache = torch.full((num_pages, 2, nkv, page, hd), float("nan"), dtype=dtype, device=device)
+    Ks, Vs, qs = [], [], []
+    for r in range(R):
+        K = rand((totals[r], nkv, hd), dtype, "cpu", seed + 10 * r + 1)
+        V = rand((totals[r], nkv, hd), dtype, "cpu", seed + 10 * r + 2)
+        q = rand((q_lens[r], nh, hd), dtype, "cpu", seed + 10 * r + 3)
+        if spike is not None and spike[0] == r:
+            direction = torch.ones(hd) / math.sqrt(hd)
+            K[spike[1]] = (direction * 6.0).to(dtype)
+            q[-1] = (direction * 6.0 * math.sqrt(hd) / 2).to(dtype)
+        Ks.append(K), Vs.append(V), qs.append(q)
+        for p in range(totals[r]):
+            pg, off = tables[r][p // page], p % page
+            cache[pg, 0, :, off] = K[p].to(device)
+            cache[pg, 1, :, off] = V[p].to(device)
+    q_all = torch.cat(qs).reshape(-1, nh * hd).to(device)
+    meta = dict(
+        table=table.to(device),
+        row_q_start=torch.tensor([sum(q_lens[:r]) for r in range(R)], dtype=torch.int32, device=device),
+        row_q_len=torch.tensor(q_lens, dtype=torch.int32, device=device),
+        row_ctx=torch.tensor(ctx, dtype=torch.int32, device=device))
+    return q_all, cache, meta, Ks, Vs, qs
+
+
+def tiles_for(q_lens, tile_tokens, device, only_multi=False):
+    rows, q0s = [], []
+    for r, n in enumerate(q_lens):
+        if only_multi and n == 1:
+            continue
+        for q0 in range(0, n, tile_tokens):
+            rows.append(r), q0s.append(q0)
+    return (torch.tensor(rows, dtype=torch.int32, device=device), torch.tensor(q0s, dtype=torch.int32, device=device))
+
+
+SIMT_CASES = [
+    # nh, nkv, hd, page, window
+    (4, 2, 16, 4, 0), (6, 3, 32, 8, 0), (8, 2, 48, 16, 24), (16, 8, 128, 16, 0), (3, 3, 80, 4, 7),
+    (20, 1, 64, 32, 0), (5, 1, 256, 64, 100), (9, 3, 112, 16, 0),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page,window", SIMT_CASES)
+def test_paged_attention_general(ops, cuda_device, dtype, nh, nkv, hd, page, window):
+    q_lens, ctx = [1, 37, 2, 1, 70], [130, 0, 63, 0, 41]
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 100)
+    tile_tokens = ops.attention_tile_tokens(nh // nkv)
+    tile_row, tile_q0 = tiles_for(q_lens, tile_tokens, cuda_device)
+    status = ops.new_status(cuda_device)
+    out = ops.paged_attention(q, cache, meta["table"], tile_row, tile_q0, tile_tokens, meta["row_q_start"],
+                              meta["row_q_len"], meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status)
+    ops.check_status(status)
+    got = out.double().cpu().view(-1, nh, hd)
+    cursor = 0
+    for r, n in enumerate(q_lens):
+        expected = ref_attention_row(qs[r].double(), Ks[r].double(), Vs[r].double(), ctx[r], n, window, nh, nkv)
+        error = (got[cursor:cursor + n] - expected).abs().max()
+        assert torch.isfinite(got[cursor:cursor + n]).all()
+        assert error <= tol(dtype, 2.0), f"row {r}: {error}"
+        cursor += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_far_key_and_window_edge(ops, cuda_device, dtype):
+    """One key among hundreds carries the softmax: at position 3 (far), and exactly at / just outside a window's edge."""
+    nh, nkv, hd, page = 4, 2, 64, 16
+    for window, key, visible in ((0, 3, True), (50, 700 - 50 + 1, True), (50, 700 - 50, False)):
+        q_lens, ctx = [1, 5], [700, 696]
+        for row in (0, 1):
+            q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 200,
+                                                          spike=(row, key))
+            tile_tokens = ops.attention_tile_tokens(nh // nkv)
+            tile_row, tile_q0 = tiles_for(q_lens, tile_tokens, cuda_device)
+            status = ops.new_status(cuda_device)
+            out = ops.paged_attention(q, cache, meta["table"], tile_row, tile_q0, tile_tokens, meta["row_q_start"],
+                                      meta["row_q_len"], meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd),
+                                      status)
+            ops.check_status(status)
+            got = out.double().cpu().view(-1, nh, hd)
+            last = sum(q_lens[:row + 1]) - 1
+            expected = ref_attention_row(qs[row].double(), Ks[row].double(), Vs[row].double(), ctx[row], q_lens[row],
+                                         window, nh, nkv)[-1]
+            assert (got[last] - expected).abs().max() <= tol(dtype, 2.0)
+            spike_value = Vs[row][key].double()                        # what the output is if that key dominates
+            dominated = (got[last, 0] - spike_value[0]).abs().max() <= 0.05
+            assert dominated == visible
+
+
+DECODE_CASES = [(4, 2, 32, 8, 0), (16, 8, 128, 16, 0), (8, 8, 64, 4, 0), (32, 2, 128, 16, 0), (12, 3, 96, 32, 0),
+                (16, 8, 128, 16, 300), (6, 2, 64, 64, 0)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", DECODE_CASES)
+def test_paged_decode_split(ops, cuda_device, nh, nkv, hd, page, window):
+    """The split-context decode kernel at context lengths around tile and split edges, mixed with
+    multi-token rows that it must leave alone."""
+    dtype = torch.bfloat16
+    assert ops.paged_decode_supported(nh, nkv, hd, dtype)
+    q_lens = [1, 1, 4, 1, 1, 1, 1, 1]
+    ctx = [0, 15, 20, 63, 255, 256, 600, 1029]
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 300)
+    rows = torch.tensor([r for r, n in enumerate(q_lens) if n == 1], dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    out = torch.full_like(q, float("nan"))
+    ops.paged_decode(q, cache, meta["table"], rows, meta["row_q_start"], meta["row_ctx"], max(ctx) + 1, nh, nkv, hd,
+                     window, 1 / math.sqrt(hd), status, out=out)
+    ops.check_status(status)
+    got = out.double().cpu().view(-1, nh, hd)
+    cursor = 0
+    for r, n in enumerate(q_lens):
+        if n == 1:
+            expected = ref_attention_row(qs[r].double(), Ks[r].double(), Vs[r].double(), ctx[r], 1, window, nh, nkv)
+            error = (got[cursor:cursor + 1] - expected).abs().max()
+            assert error <= tol(dtype, 2.0), f"row {r} (context {ctx[r]}): {error}"
+        else:
+            assert torch.isnan(got[cursor:cursor + n]).all()      # not a decode row: untouched
+        cursor += n
+
+
+def test_paged_decode_far_key(ops, cuda_device):
+    nh, nkv, hd, page = 16, 8, 128, 16
+    for key in (2, 255, 256, 511, 900):
+        q_lens, ctx = [1, 1], [1000, 1000]
+        q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, torch.bfloat16, nh, nkv, hd, page, q_lens, ctx, 400,
+                                                      spike=(1, key))
+        rows = torch.tensor([0, 1], dtype=torch.int32, device=cuda_device)
+        status = ops.new_status(cuda_device)
+        out = torch.zeros_like(q)
+        ops.paged_decode(q, cache, meta["table"], rows, meta["row_q_start"], meta["row_ctx"], 1001, nh, nkv, hd, 0,
+                         1 / math.sqrt(hd), status, out=out)
+        ops.check_status(status)
+        got = out.double().cpu().view(-1, nh, hd)
+        assert (got[1, 0] - Vs[1][key].double()[0]).abs().max() <= 0.05
+        expected = ref_attention_row(qs[1].double(), Ks[1].double(), Vs[1].double(), 1000, 1, 0, nh, nkv)
+        assert (got[1:2] - expected).abs().max() <= tol(torch.bfloat16, 2.0)
+
+
+def test_kernels_refuse_what_they_do_not_take(ops, cuda_device):
+    assert not ops.paged_decode_supported(16, 8, 128, torch.float32)
+    assert not ops.paged_decode_supported(34, 2, 128, torch.bfloat16)     # 17 heads per group
+    assert not ops.paged_decode_supported(4, 2, 48, torch.bfloat16)
+    q = torch.zeros((1, 2 * 24), device=cuda_device)
+    cache = torch.zeros((3, 2, 2, 4, 24), device=cuda_device)
+    z = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    with pytest.raises(ops.KernelError, match="does not support"):
+        ops.paged_attention(q, cache, z.view(1, 1), z, z, 1, z, z, z, 2, 2, 24, 0, 1.0, ops.new_status(cuda_device))
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(torch.zeros(4, 4), torch.ones(4), 1e-6)               # CPU tensors: no CPU path
+
+
+# ---------------------------------------------------------------------- sampling
+def test_argmax_lowest_index_on_ties(ops, cuda_device):
+    logits = torch.full((3, 151936), -1.0, device=cuda_device)
+    logits[0, [77, 5000, 151935]] = 3.0
+    logits[1, 151935] = 0.5
+    logits[2, 0] = 0.0
+    status = ops.new_status(cuda_device)
+    assert ops.sample(logits, None, None, status).tolist() == [77, 151935, 0]
+    ops.check_status(status)
+
+
+def test_temperature_sampling_follows_the_prefix_sums(ops, cuda_device):
+    from plain_qwen3 import plain_sample
+
+    for V in (311, 5000, 151936):
+        g = torch.Generator().manual_seed(V)
+        logits = (torch.randn((16, V), generator=g) * 2).to(cuda_device)
+        temperature = torch.tensor([0.7, 1.0, 0.3, 1.5] * 4, device=cuda_device)
+        temperature[5] = 0.0            # a greedy row among sampled ones
+        uniform = torch.rand(16, generator=g).to(cuda_device)
+        status = ops.new_status(cuda_device)
+        got = ops.sample(logits, temperature, uniform, status).tolist()
+        ops.check_status(status)
+        for r in range(16):
+            if r == 5:
+                assert got[r] == int(logits[r].argmax())
+                continue
+            index, margin = plain_sample(logits[r].cpu(), float(temperature[r]), float(uniform[r]))
+            if margin > 1e-4:
+                assert got[r] == index, (V, r, got[r], index, margin)
+            # Always: u * total lies in the chosen token's interval of the exact prefix sums, give or
+            # take what float32 prefix sums over V terms can differ by.
+            z = (logits[r].double().cpu() - logits[r].double().max().cpu()) / float(temperature[r])
+            cdf = torch.cumsum(torch.exp(z), 0)
+            target, slack = float(uniform[r]) * float(cdf[-1]), 1e-4 * float(cdf[-1])
+            assert float(cdf[got[r]]) >= target - slack
+            assert (float(cdf[got[r] - 1]) if got[r] > 0 else 0.0) <= target + slack
+
+
+def test_sampling_reports_nan(ops, cuda_device):
+    logits = torch.zeros((2, 100), device=cuda_device)
+    logits[1, 7] = float("nan")
+    status = ops.new_status(cuda_device)
+    ops.sample(logits, None, None, status)
+    with pytest.raises(ops.KernelError, match="NaN"):
+        ops.check_status(status)

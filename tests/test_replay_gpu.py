@@ -1,0 +1,116 @@
+"""The engine against the plain implementation under every way of cutting the work, in 32-bit and
+in bfloat16, on three tiny configurations: each request alone and whole; most of it in one step and
+the last 32 tokens one by one; portions of changing size down to two tokens; and mixed, up to four
+live requests with so few pages that they are used again (pages given back are filled with NaN, so a
+kernel that reads a page it should not shows up as a non-finite logit)."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from replay_util import (collect, first_mismatch, peak_tokens, random_tokens, run_in_process, trace_mixed,
+                         trace_portions, trace_tail, trace_whole)
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [70, 128, 45, 33, 100, 5, 17, 64], "B": [1, 9, 33, 70, 150, 256, 41, 96],
+           "C": [60, 130, 250, 40, 90, 33, 17, 200]}
+TRACES = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions, "mixed": trace_mixed}
+
+
+def make_requests(name: str) -> dict[str, list[int]]:
+    vocab = TINY[name]["config"]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, seed=1000 * ord(name) + i) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_matches_plain(model_folders, cuda_device, name, dtype, mode):
+    folder = model_folders(name, dtype)
+    requests = make_requests(name)
+    steps = TRACES[mode](requests)
+    outputs = run_in_process(folder, dtype, steps, TINY[name]["page_size"])
+    rows = collect(steps, outputs)
+    assert len(rows) >= sum(1 for _ in requests)
+    first, worst, where = first_mismatch(rows, requests, folder, dtype)
+    assert first is None, (f"{name} {dtype} {mode}: first wrong logits at request {first[0]} position {first[1]}: "
+                           f"error {first[2]:.3e} > {first[3]:.1e}; worst {worst:.3e} at {where}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuttings_agree_with_each_other(model_folders, cuda_device, dtype):
+    """The same (request, position) gives the same logits however the tokens were cut, beyond rounding."""
+    name = "B"
+    folder = model_folders(name, dtype)
+    requests = make_requests(name)
+    results = {}
+    for mode, build in TRACES.items():
+        steps = build(requests)
+        results[mode] = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+    tol = 2e-4 if dtype == "float32" else 0.04
+    for key, row in results["whole"].items():
+        for mode in ("portions", "mixed"):
+            assert np.abs(results[mode][key] - row).max() <= tol, (mode, key)
+    for key, row in results["tail"].items():
+        assert np.abs(results["whole"][key] - row).max() <= tol, ("tail", key)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_folders, cuda_device, tmp_path, dtype):
+    """bin/trace_run itself: a mixed trace through the program, files and ``done`` lines checked."""
+    name = "A"
+    folder = model_folders(name, dtype)
+    requests = make_requests(name)
+    steps = trace_mixed(requests, seed=3)
+    root = Path(__file__).resolve().parent.parent
+    out = tmp_path / "out"
+    command = [sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out",
+               str(out), "--max-tokens", str(peak_tokens(steps)), "--page-size", str(TINY[name]["page_size"])]
+    feed = "".join(json.dumps(step) + "\n" for step in steps)
+    done = subprocess.run(command, input=feed, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.splitlines() if line.startswith("done ")] == \
+        [f"done {step['step']}" for step in steps]
+    vocab = TINY[name]["config"]["vocab_size"]
+    outputs = {}
+    for step in steps:
+        wanted = sum(len(e["want"]) for e in step["entries"])
+        path = out / f"{step['step']}.f32"
+        assert path.exists() == (wanted > 0)
+        if wanted:
+            outputs[step["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+    first, worst, where = first_mismatch(collect(steps, outputs), requests, folder, dtype)
+    assert first is None, f"trace_run {dtype}: {first}; worst {worst:.3e} at {where}"
+
+
+def test_long_decoding(model_folders, cuda_device):
+    """A short prompt, then 200 tokens one by one, across many page edges."""
+    for name, dtype in (("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16")):
+        folder = model_folders(name, dtype)
+        tokens = random_tokens(TINY[name]["config"]["vocab_size"], 230, seed=77)
+        requests = {"long": tokens}
+        steps = trace_tail(requests, tail=200)
+        rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+        first, worst, where = first_mismatch(rows, requests, folder, dtype)
+        assert first is None, f"{name} {dtype}: {first}; worst {worst:.3e} at {where}"
+
+
+def test_first_tokens(model_folders, cuda_device):
+    """The first tokens of a sequence, one at a time from the very start (position 0 has one key)."""
+    for name in ("A", "B", "C"):
+        for dtype in ("float32", "bfloat16"):
+            folder = model_folders(name, dtype)
+            tokens = random_tokens(TINY[name]["config"]["vocab_size"], 6, seed=5)
+            requests = {"s": tokens}
+            steps = [{"step": i, "entries": [{"id": "s", "tokens": [t], "want": [0]}], "end": []}
+                     for i, t in enumerate(tokens)]
+            rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+            first, worst, where = first_mismatch(rows, requests, folder, dtype)
+            assert first is None, f"{name} {dtype}: {first}"
