@@ -45,6 +45,7 @@ class ModelRunner:
         self.status = ops.new_status(model.device)
         self.poison_freed_pages = False      # tests: NaN into every page that is given back
         self.steps = 0
+        self.last_step_h2d_bytes = 0     # bytes of the last step's description copied to the device
 
     # ------------------------------------------------------------------ sizing
     @staticmethod
@@ -147,6 +148,7 @@ class ModelRunner:
         if sum(sizes):
             np.concatenate(arrays, out=host.numpy()[:sum(sizes)])
         device = host.to(self.device, non_blocking=True)
+        self.last_step_h2d_bytes = 4 * sum(sizes)
         views, offset = [], 0
         for size in sizes:
             views.append(device[offset:offset + size])

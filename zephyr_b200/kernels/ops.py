@@ -96,7 +96,12 @@ def library_path() -> str:
     return library()._name
 
 
-def _check(rc: int, name: str) -> None:
+LAUNCHES = 0      # kernels of this package launched so far (the bench reports the count of a timed region)
+
+
+def _check(rc: int, name: str, kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += kernels
     if rc != 0:
         detail = ""
         if rc == 2:
@@ -347,7 +352,7 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     _check(library().zb_paged_decode(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
-        float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(status), _stream()), "paged_decode")
+        float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(status), _stream()), "paged_decode", kernels=2)
     return out
 
 

@@ -65,7 +65,9 @@ class SafetensorsFile:
                 size = handle.seek(0, 2)
                 if size < 8:
                     raise WeightError(f"{self.path}: too short to hold a safetensors header")
-                self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_READ)
+                # A private copy-on-write map: nothing reaches the file, and the buffer counts as writable,
+                # which torch.frombuffer wants.
+                self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_COPY)
         except OSError as error:
             raise WeightError(f"cannot open checkpoint file {self.path}: {error.strerror}") from error
         (header_len,) = struct.unpack("<Q", self._map[:8])
