@@ -1,0 +1,114 @@
+"""The entry point for callers that cannot allocate device memory (a plug-in inside another
+program's memory budget, a loop that may not take the allocator's lock): decode attention whose
+scratch is a fixed array inside the library, ``zb_paged_decode_no_alloc``.
+
+It is called here through its exported C symbol, straight from the shared library, twice in a row
+(the second call finds the first call's partial results still in the shared array), and its output
+is compared with the ordinary entry point's, which takes a scratch buffer from the caller.  A
+problem too large for the built-in array must be refused with the code the header names.
+
+This file sorts last on purpose: should it fail, a run that stops at the first failure has
+already run every other test."""
+
+import ctypes
+import math
+import random
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+NH, NKV, HD, PAGE = 16, 8, 128, 16
+SCRATCH_BYTES = 4 << 20
+ERR_SCRATCH_TOO_SMALL = 4
+
+
+def make_case(device, contexts, seed):
+    """Random queries and a paged cache holding ``contexts[r] + 1`` positions for row r."""
+    g = torch.Generator().manual_seed(seed)
+    rows = len(contexts)
+    totals = [c + 1 for c in contexts]
+    pages_needed = sum(-(-n // PAGE) for n in totals)
+    num_pages = pages_needed + 2
+    order = list(range(1, num_pages))
+    random.Random(seed).shuffle(order)
+    width = max(-(-n // PAGE) for n in totals)
+    table = torch.zeros((rows, width), dtype=torch.int32)
+    cursor = 0
+    for r, n in enumerate(totals):
+        need = -(-n // PAGE)
+        table[r, :need] = torch.tensor(order[cursor:cursor + need], dtype=torch.int32)
+        cursor += need
+    cache = torch.randn((num_pages, 2, NKV, PAGE, HD), generator=g).to(torch.bfloat16).to(device)
+    q = torch.randn((rows, NH * HD), generator=g).to(torch.bfloat16).to(device)
+    return dict(
+        q=q, cache=cache, table=table.to(device), num_pages=num_pages,
+        rows=torch.arange(rows, dtype=torch.int32, device=device),
+        row_q_start=torch.arange(rows, dtype=torch.int32, device=device),
+        row_ctx=torch.tensor(contexts, dtype=torch.int32, device=device))
+
+
+def load_symbol():
+    from zephyr_b200.kernels.build import build_library
+
+    lib = ctypes.CDLL(str(build_library()))
+    fn = lib.zb_paged_decode_no_alloc
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                   c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+    lib.zb_paged_decode_no_alloc_bytes_needed.restype = c_longlong
+    lib.zb_paged_decode_no_alloc_bytes_needed.argtypes = [c_int, c_int, c_int, c_int]
+    lib.zb_paged_decode_no_alloc_error.restype = ctypes.c_char_p
+    lib.zb_paged_decode_no_alloc_error.argtypes = [c_int]
+    return lib
+
+
+def call_no_alloc(lib, case, out, status, split_size, max_splits, n_rows=None):
+    n_rows = case["rows"].numel() if n_rows is None else n_rows
+    return lib.zb_paged_decode_no_alloc(
+        out.data_ptr(), case["q"].data_ptr(), case["cache"].data_ptr(), case["table"].data_ptr(),
+        case["table"].shape[1], PAGE, case["num_pages"], case["table"].shape[0], case["rows"].data_ptr(), n_rows,
+        case["row_q_start"].data_ptr(), case["row_ctx"].data_ptr(), NH, NKV, HD, 0, 1.0 / math.sqrt(HD), split_size,
+        max_splits, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
+def test_no_alloc_entry_point_matches_the_ordinary_one(cuda_device):
+    from zephyr_b200.kernels import ops
+
+    lib = load_symbol()
+    split = ops.DECODE_SPLIT_SIZE
+    # Two different problems in a row: the second finds the first one's partial results in the array.
+    for seed, contexts in ((1, [0, 255, 256, 1000, 77]), (2, [600, 3, 2047])):
+        case = make_case(cuda_device, contexts, seed)
+        max_splits = math.ceil((max(contexts) + 1) / split)
+        status = ops.new_status(cuda_device)
+        expected = torch.zeros_like(case["q"])
+        ops.paged_decode(case["q"], case["cache"], case["table"], case["rows"], case["row_q_start"], case["row_ctx"],
+                         max(contexts) + 1, NH, NKV, HD, 0, 1.0 / math.sqrt(HD), status, out=expected)
+        got = torch.full_like(case["q"], float("nan"))
+        assert lib.zb_paged_decode_no_alloc_bytes_needed(len(contexts), NH, HD, max_splits) <= SCRATCH_BYTES
+        rc = call_no_alloc(lib, case, got, status, split, max_splits)
+        assert rc == 0, lib.zb_paged_decode_no_alloc_error(rc).decode()
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        assert torch.isfinite(got.float()).all()
+        # The same kernels on the same inputs: the tolerance of the kernel tests holds with room to spare.
+        assert (got.float() - expected.float()).abs().max() <= 1.6e-2
+
+
+def test_no_alloc_entry_point_refuses_what_does_not_fit(cuda_device):
+    from zephyr_b200.kernels import ops
+
+    lib = load_symbol()
+    case = make_case(cuda_device, [10, 20], 3)
+    out = torch.zeros_like(case["q"])
+    status = ops.new_status(cuda_device)
+    too_many_splits = SCRATCH_BYTES // (2 * NH * (HD + 2) * 4) + 1
+    assert lib.zb_paged_decode_no_alloc_bytes_needed(2, NH, HD, too_many_splits) > SCRATCH_BYTES
+    rc = call_no_alloc(lib, case, out, status, ops.DECODE_SPLIT_SIZE, too_many_splits)
+    assert rc == ERR_SCRATCH_TOO_SMALL
+    assert b"4 MiB" in lib.zb_paged_decode_no_alloc_error(rc)
+    torch.cuda.synchronize()
+    assert out.abs().max() == 0         # nothing was launched

@@ -371,3 +371,71 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
       split_size, max_splits);
   return launch_result();
 }
+
+// ------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and explained in no_alloc.h).  Its scratch
+// is the array below, a part of the library image on every device that loads it.
+#include <mutex>
+
+#include "no_alloc.h"
+
+static __device__ __align__(256) float zb_no_alloc_scratch[ZB_NO_ALLOC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+std::mutex no_alloc_mutex;
+float* no_alloc_address[NO_ALLOC_MAX_DEVICES] = {};   // device address of the array, per device ordinal
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address the kernels get is looked up here: once per device, with that device current.
+float* no_alloc_scratch_for_current_device() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NO_ALLOC_MAX_DEVICES) return nullptr;
+  std::lock_guard<std::mutex> lock(no_alloc_mutex);
+  if (no_alloc_address[device] == nullptr) {
+    float* address = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&address), zb_no_alloc_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();      // leave no sticky error behind for the caller's next call
+      return nullptr;
+    }
+    no_alloc_address[device] = address;
+  }
+  return no_alloc_address[device];
+}
+
+}  // namespace
+
+ZB_API long long zb_paged_decode_no_alloc_bytes_needed(int n_rows, int nh, int hd, int max_splits) {
+  return zb_paged_decode_scratch_floats(n_rows, nh, hd, max_splits) * static_cast<long long>(sizeof(float));
+}
+
+ZB_API const char* zb_paged_decode_no_alloc_error(int code) {
+  switch (code) {
+    case OK: return "launched";
+    case ERR_BAD_ARGUMENT: return "an argument lies outside the kernel's contract";
+    case ERR_CUDA: return "the CUDA launch failed";
+    case ERR_UNSUPPORTED: return "this head size, group size or type is not supported by the decode kernel";
+    case ZB_ERR_SCRATCH_TOO_SMALL:
+      return "the problem needs more than the 4 MiB of built-in scratch: n_rows * heads * max_splits * "
+             "(head_dim + 2) * 4 bytes must not exceed ZB_NO_ALLOC_SCRATCH_BYTES; use zb_paged_decode with a buffer "
+             "of your own, or split the rows over several calls";
+    case ZB_ERR_SCRATCH_ADDRESS: return "the device address of the built-in scratch array could not be looked up";
+    default: return "unknown code";
+  }
+}
+
+ZB_API int zb_paged_decode_no_alloc(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                    int max_blocks, int page_size, int num_pages, int num_rows, const int* rows,
+                                    int n_rows, const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd,
+                                    int window, float scale, int split_size, int max_splits, int* status,
+                                    void* stream) {
+  if (n_rows < 0 || nh <= 0 || hd <= 0 || max_splits <= 0) return ERR_BAD_ARGUMENT;
+  if (zb_paged_decode_no_alloc_bytes_needed(n_rows, nh, hd, max_splits) > static_cast<long long>(ZB_NO_ALLOC_SCRATCH_BYTES))
+    return ZB_ERR_SCRATCH_TOO_SMALL;
+  float* scratch = no_alloc_scratch_for_current_device();
+  if (scratch == nullptr) return ZB_ERR_SCRATCH_ADDRESS;
+  return zb_paged_decode(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
+                         row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, status,
+                         stream);
+}
