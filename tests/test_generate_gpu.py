@@ -1,0 +1,168 @@
+"""Generation through the Python entry point: greedy and temperature sampling against the plain
+implementation, the benchmark description's two tiny workloads, preemption under a small pool, the
+finish rules, and the command line."""
+
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from plain_qwen3 import load_model_folder, plain_forward, plain_sample
+from replay_util import random_tokens
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def make_engine(folder, name, dtype, **kwargs):
+    from zephyr_b200 import Engine
+    from zephyr_b200.engine import KvCacheOptions, PagedSchedulerConfig
+
+    scheduler = PagedSchedulerConfig(**{k: kwargs.pop(k) for k in list(kwargs)
+                                        if k in ("max_num_seqs", "max_num_batched_tokens", "max_prefill_chunk_tokens")})
+    return Engine(folder, dtype=dtype, scheduler=scheduler,
+                  kv_cache=KvCacheOptions(block_size=TINY[name]["page_size"], num_blocks=kwargs.pop("num_blocks", 64)),
+                  **kwargs)
+
+
+def plain_greedy_with_margins(config, weights, prompt, count):
+    tokens, margins = list(prompt), []
+    for _ in range(count):
+        logits = plain_forward(config, weights, tokens)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        tokens.append(int(logits.argmax()))
+    return tokens[len(prompt):], margins
+
+
+def assert_greedy_agrees(got, expected, margins, tolerance):
+    """Equal tokens, except that a first difference is forgiven where the plain logits' two best lie
+    closer than the engine's error bound (after which the sequences may part)."""
+    for index, (g, e) in enumerate(zip(got, expected)):
+        if g != e:
+            assert margins[index] <= tolerance, f"token {index}: {g} != {e} with margin {margins[index]:.3e}"
+            return
+    assert len(got) == len(expected)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "float32"), ("B", "bfloat16"),
+                                        ("C", "bfloat16")])
+def test_greedy_generation_matches_plain(model_folders, cuda_device, name, dtype):
+    folder = model_folders(name, dtype)
+    config, weights = load_model_folder(folder)
+    engine = make_engine(folder, name, dtype, max_num_seqs=4, max_num_batched_tokens=16, max_prefill_chunk_tokens=7)
+    prompts = [random_tokens(config["vocab_size"], n, seed=n) for n in (5, 11, 17, 40)]
+    outputs = engine.generate(prompts, max_tokens=8, temperature=0.0, ignore_eos=True)
+    for prompt, output in zip(prompts, outputs):
+        expected, margins = plain_greedy_with_margins(config, weights, prompt, 8)
+        assert output.prompt_token_ids == tuple(prompt) and output.status.value == "completed"
+        assert output.choices[0].finish_reason.value == "length" and output.usage.completion_tokens == 8
+        assert_greedy_agrees(list(output.token_ids), expected, margins, 2e-4 if dtype == "float32" else 0.04)
+    assert engine.runner.manager.num_requests == 0
+    engine.runner.manager.check_invariants()
+
+
+def test_workload_a_three_requests_greedy(model_folders, cuda_device):
+    """Tiny A, prompts of 5/11/17 tokens, 8 greedy tokens each, page size 4 (float32)."""
+    folder = model_folders("A", "float32")
+    config, weights = load_model_folder(folder)
+    prompts = [random_tokens(256, n, seed=10 + n) for n in (5, 11, 17)]
+    engine = make_engine(folder, "A", "float32", max_num_seqs=8, max_num_batched_tokens=512,
+                         max_prefill_chunk_tokens=512)
+    together = [list(o.token_ids) for o in engine.generate(prompts, max_tokens=8, temperature=0.0, ignore_eos=True)]
+    alone = [list(engine.generate(p, max_tokens=8, temperature=0.0, ignore_eos=True).token_ids) for p in prompts]
+    assert together == alone
+    for prompt, got in zip(prompts, together):
+        expected, margins = plain_greedy_with_margins(config, weights, prompt, 8)
+        assert_greedy_agrees(got, expected, margins, 2e-4)
+
+
+def test_workload_b_four_requests_temperature(model_folders, cuda_device):
+    """Tiny B, prompts of 1/9/33/70 tokens, prompt portions of 16, 12 tokens at temperature 0.7 from
+    seeded generators (float32): the batch gives what each request gives alone, and each first token
+    is the one the plain logits and the same uniform number select."""
+    from zephyr_b200.sampling import MT19937_64
+
+    folder = model_folders("B", "float32")
+    config, weights = load_model_folder(folder)
+    prompts = [random_tokens(311, n, seed=20 + n) for n in (1, 9, 33, 70)]
+    engine = make_engine(folder, "B", "float32", max_num_seqs=4, max_num_batched_tokens=64,
+                         max_prefill_chunk_tokens=16)
+    from zephyr_b200 import GenerationParams
+
+    ids = [engine.add_request(p, GenerationParams(max_tokens=12, temperature=0.7, seed=100 + i, ignore_eos=True))
+           for i, p in enumerate(prompts)]
+    while engine.has_unfinished():
+        engine.step()
+    together = [list(engine.take_output(i).token_ids) for i in ids]
+    alone = [list(engine.generate(p, max_tokens=12, temperature=0.7, seed=100 + i, ignore_eos=True).token_ids)
+             for i, p in enumerate(prompts)]
+    assert together == alone
+    for i, (prompt, got) in enumerate(zip(prompts, together)):
+        u = MT19937_64(100 + i).next_uniform()
+        index, margin = plain_sample(plain_forward(config, weights, prompt)[-1], 0.7, u)
+        if margin > 1e-5:
+            assert got[0] == index
+
+
+def test_small_pool_preempts_and_tokens_do_not_change(model_folders, cuda_device):
+    folder = model_folders("A", "float32")
+    prompts = [random_tokens(256, n, seed=30 + n) for n in (10, 9, 14)]
+    roomy = make_engine(folder, "A", "float32", max_num_seqs=3, max_num_batched_tokens=16, max_prefill_chunk_tokens=16)
+    expected = [list(o.token_ids) for o in roomy.generate(prompts, max_tokens=20, temperature=0.0, ignore_eos=True)]
+    tight = make_engine(folder, "A", "float32", max_num_seqs=3, max_num_batched_tokens=16, max_prefill_chunk_tokens=16,
+                        num_blocks=16)          # 64 tokens for three sequences that grow to 30, 29 and 34
+    tight.runner.poison_freed_pages = True
+    got = [list(o.token_ids) for o in tight.generate(prompts, max_tokens=20, temperature=0.0, ignore_eos=True)]
+    assert tight.stats.preemptions > 0
+    assert got == expected
+    tight.runner.manager.check_invariants()
+    assert tight.runner.manager.num_free_pages() == 16
+
+
+def test_finish_rules_and_choices(model_folders, cuda_device):
+    folder = model_folders("A", "float32")
+    engine = make_engine(folder, "A", "float32", max_num_seqs=4, max_num_batched_tokens=32, max_prefill_chunk_tokens=32)
+    prompt = random_tokens(256, 6, seed=1)
+    free = list(engine.generate(prompt, max_tokens=6, temperature=0.0, ignore_eos=True).token_ids)
+    # EOS: the terminating token is part of the output (src/engine/generation.cpp:81-99).
+    eos_engine = make_engine(folder, "A", "float32", max_num_seqs=4, max_num_batched_tokens=32,
+                             max_prefill_chunk_tokens=32, eos_token_ids=[free[2]])
+    stopped = eos_engine.generate(prompt, max_tokens=6, temperature=0.0)
+    first = free.index(free[2])
+    assert list(stopped.token_ids) == free[:first + 1] and stopped.choices[0].finish_reason.value == "eos"
+    assert list(eos_engine.generate(prompt, max_tokens=6, temperature=0.0, ignore_eos=True).token_ids) == free
+    stop = engine.generate(prompt, max_tokens=6, temperature=0.0, stop_token_ids=[free[1]], ignore_eos=True)
+    assert stop.choices[0].finish_reason.value == "stop_token" and stop.choices[0].stop_reason == free[1]
+    assert list(stop.token_ids) == free[:free.index(free[1]) + 1]
+    # The model's length: a prompt of 126 in a context of 128 can hold two more tokens' keys.
+    long_prompt = random_tokens(256, 126, seed=2)
+    out = engine.generate(long_prompt, temperature=0.0, ignore_eos=True)
+    assert out.choices[0].finish_reason.value in ("length", "model_length") and len(out.token_ids) == 2
+    with pytest.raises(ValueError, match="between 1 and"):
+        engine.generate(random_tokens(256, 129, seed=3), max_tokens=1)
+    with pytest.raises(ValueError, match="outside the model vocabulary"):
+        engine.generate([1, 256], max_tokens=1)
+    with pytest.raises(ValueError, match="token ids"):
+        engine.generate("some text", max_tokens=1)
+    # Two choices: seeds seed and seed + 1 (src/engine/engine.cpp:350-351).
+    pair = engine.generate(prompt, max_tokens=5, temperature=1.0, seed=7, n=2, ignore_eos=True)
+    one = engine.generate(prompt, max_tokens=5, temperature=1.0, seed=8, ignore_eos=True)
+    assert len(pair.choices) == 2 and pair.choices[1].token_ids == one.choices[0].token_ids
+
+
+def test_command_line_generates(model_folders, cuda_device):
+    folder = model_folders("A", "float32")
+    root = Path(__file__).resolve().parent.parent
+    prompt = random_tokens(256, 7, seed=4)
+    done = subprocess.run(
+        [sys.executable, "-m", "zephyr_b200", "generate", str(folder), "--prompt-ids", ",".join(map(str, prompt)),
+         "--max-tokens", "5", "--temperature", "0", "--dtype", "float32", "--kv-block-size", "4", "--num-kv-blocks", "40",
+         "--ignore-eos"], capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    engine = make_engine(folder, "A", "float32", max_num_seqs=2, max_num_batched_tokens=32, max_prefill_chunk_tokens=32)
+    expected = list(engine.generate(prompt, max_tokens=5, temperature=0.0, ignore_eos=True).token_ids)
+    assert [int(t) for t in done.stdout.split()] == expected

@@ -1,0 +1,204 @@
+"""Parts that the framework does not have, defined here and registered from outside: a mixer with a
+state of its own (a running mean over the sequence, kept in the per-request state slots), in a toy
+architecture whose run order names a layer twice and lets a layer read another layer's cache.  The
+model is built, stepped whole, in portions and mixed with other requests, and compared with a plain
+float64 computation written in this file.  No file of the framework is changed for it."""
+
+import json
+import math
+
+import pytest
+import torch
+
+from plain_qwen3 import F64, plain_attention, plain_mlp, plain_rmsnorm, plain_rope, plain_rope_tables
+from replay_util import collect, random_tokens, trace_mixed, trace_portions, trace_tail, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN, VOCAB, HEADS, KV_HEADS, HEAD_DIM, INTER, EPS, THETA, MAX_POS = 48, 101, 4, 2, 16, 80, 1e-5, 10000.0, 128
+
+
+def toy_classes():
+    from zephyr_b200.cache import StateCacheSpec
+    from zephyr_b200.config import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+    from zephyr_b200.kernels import ops
+    from zephyr_b200.parts import Mixer
+    from zephyr_b200.weights import WeightDecl
+
+    class RunningMeanMixer(Mixer):
+        """y_t = W * mean(x_0 .. x_t).  The state is the running sum, one float32 vector per request."""
+
+        def __init__(self, spec, weights, dtype, device):
+            self.weight = weights[spec.params["proj"]]
+            self.hidden = spec.params["hidden_size"]
+
+        @staticmethod
+        def weight_decls(spec):
+            return {spec.params["proj"]: WeightDecl((spec.params["hidden_size"], spec.params["hidden_size"]))}
+
+        @staticmethod
+        def cache_spec(spec):
+            return StateCacheSpec(shape=(spec.params["hidden_size"],), dtype="float32")
+
+        def forward(self, x, ctx, call):
+            state = ctx.caches[call.cache]
+            means = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            start = 0
+            for n, before, slot in zip(ctx.host_q_len, ctx.host_ctx, ctx.host_slots):
+                sums = state[slot] + torch.cumsum(x[start:start + n].float(), dim=0)
+                counts = torch.arange(before + 1, before + n + 1, device=x.device, dtype=torch.float32)
+                means[start:start + n] = sums / counts[:, None]
+                if call.writes_cache:
+                    state[slot] = sums[-1]
+                start += n
+            return ops.linear(means.to(x.dtype), self.weight)
+
+    class ToyConfig:
+        model_type, architecture = "toy_mix", "ToyMixForCausalLM"
+
+        @classmethod
+        def from_dict(cls, config, where="config.json"):
+            assert config["model_type"] == cls.model_type
+            return cls()
+
+        def to_dict(self):
+            return {"model_type": self.model_type, "architectures": [self.architecture]}
+
+        def to_model_spec(self):
+            position = PositionSpec("rope_neox", HEAD_DIM, MAX_POS, {"theta": THETA})
+
+            def norm(name):
+                return NormSpec("rmsnorm", HIDDEN, EPS, name)
+
+            def ffn(prefix):
+                return FeedForwardSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": INTER,
+                                                  "gate_proj": f"{prefix}.gate_proj.weight",
+                                                  "up_proj": f"{prefix}.up_proj.weight",
+                                                  "down_proj": f"{prefix}.down_proj.weight"})
+
+            def attention(prefix):
+                return MixerSpec("attention", {
+                    "hidden_size": HIDDEN, "num_heads": HEADS, "num_kv_heads": KV_HEADS, "head_dim": HEAD_DIM,
+                    "window": 0, "qk_norm_eps": EPS, "q_proj": f"{prefix}.q_proj.weight",
+                    "k_proj": f"{prefix}.k_proj.weight", "v_proj": f"{prefix}.v_proj.weight",
+                    "o_proj": f"{prefix}.o_proj.weight", "q_norm": f"{prefix}.q_norm.weight",
+                    "k_norm": f"{prefix}.k_norm.weight"}, position)
+
+            layers = []
+            for index in range(3):
+                prefix = f"toy.layers.{index}"
+                mixer = (MixerSpec("running_mean", {"hidden_size": HIDDEN, "proj": f"{prefix}.mean.proj.weight"})
+                         if index == 1 else attention(f"{prefix}.attn"))
+                layers.append(LayerSpec("prenorm_residual", mixer, ffn(f"{prefix}.mlp"), norm(f"{prefix}.norm1.weight"),
+                                        norm(f"{prefix}.norm2.weight")))
+            run_order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2),        # layer 0 runs twice, own caches
+                         LayerCall(2, 0, writes_cache=False),                     # layer 2 reads the cache of call 0
+                         LayerCall(1, 3))                                         # the stateful layer again, own state
+            return ModelSpec("ToyMixForCausalLM", VOCAB, HIDDEN, MAX_POS, "toy.embed.weight", tuple(layers), run_order,
+                             norm("toy.norm.weight"), "toy.head.weight")
+
+    return RunningMeanMixer, ToyConfig
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    from zephyr_b200.config import register_architecture, unregister_architecture
+    from zephyr_b200.parts import MIXERS, register_mixer
+    from zephyr_b200.weights import write_random_model
+
+    mixer, config = toy_classes()
+    register_mixer("running_mean", mixer)
+    register_architecture(config.model_type, config.architecture, config)
+    folders = {}
+    for dtype in ("float32", "bfloat16"):
+        folders[dtype] = write_random_model(config(), 11, tmp_path_factory.mktemp(f"toy_{dtype}"),
+                                            dtype=getattr(torch, dtype))
+    yield folders
+    unregister_architecture(config.architecture)
+    MIXERS.pop("running_mean", None)
+
+
+# ------------------------------------------------------------- the plain computation
+def plain_toy_logits(folder, tokens):
+    from safetensors import safe_open
+
+    w = {}
+    with safe_open(str(folder / "model.safetensors"), framework="pt", device="cpu") as handle:
+        for name in handle.keys():
+            w[name] = handle.get_tensor(name).to(F64)
+    T = len(tokens)
+    cos, sin = plain_rope_tables(HEAD_DIM, T, THETA)
+    x = w["toy.embed.weight"][torch.tensor(tokens)]
+
+    def qkv(h, prefix):
+        q = plain_rope(plain_rmsnorm((h @ w[f"{prefix}.q_proj.weight"].T).view(T, HEADS, HEAD_DIM),
+                                     w[f"{prefix}.q_norm.weight"], EPS), range(T), cos, sin)
+        k = plain_rope(plain_rmsnorm((h @ w[f"{prefix}.k_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM),
+                                     w[f"{prefix}.k_norm.weight"], EPS), range(T), cos, sin)
+        v = (h @ w[f"{prefix}.v_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM)
+        return q, k, v
+
+    def finish(x, mixed, index):
+        r = x + mixed
+        return r + plain_mlp(plain_rmsnorm(r, w[f"toy.layers.{index}.norm2.weight"], EPS), w, f"toy.layers.{index}.mlp")
+
+    def attention_layer(x, index, kv=None):
+        h = plain_rmsnorm(x, w[f"toy.layers.{index}.norm1.weight"], EPS)
+        q, k, v = qkv(h, f"toy.layers.{index}.attn")
+        if kv is not None:
+            k, v = kv
+        out = plain_attention(q, k, v).reshape(T, HEADS * HEAD_DIM) @ w[f"toy.layers.{index}.attn.o_proj.weight"].T
+        return finish(x, out, index), (k, v)
+
+    def mean_layer(x, index):
+        h = plain_rmsnorm(x, w[f"toy.layers.{index}.norm1.weight"], EPS)
+        means = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=F64)[:, None]
+        return finish(x, means @ w[f"toy.layers.{index}.mean.proj.weight"].T, index)
+
+    x, kv0 = attention_layer(x, 0)
+    x = mean_layer(x, 1)
+    x, _ = attention_layer(x, 0)
+    x, _ = attention_layer(x, 2, kv=kv0)
+    x = mean_layer(x, 1)
+    return (plain_rmsnorm(x, w["toy.norm.weight"], EPS) @ w["toy.head.weight"].T).numpy()
+
+
+def test_toy_architecture_is_found_and_built(toy_folder, cuda_device):
+    from zephyr_b200.cache import PagedCacheSpec, StateCacheSpec
+    from zephyr_b200.config import load_model_spec
+    from zephyr_b200.parts import Model
+    from zephyr_b200.weights import Checkpoint
+
+    spec = load_model_spec(toy_folder["float32"])
+    model = Model.load(spec, Checkpoint(toy_folder["float32"]), torch.float32, cuda_device)
+    kinds = [type(s).__name__ for s in model.cache_specs]
+    assert kinds == ["PagedCacheSpec", "StateCacheSpec", "PagedCacheSpec", "StateCacheSpec"]
+    assert len(model.layers) == 3 and len(spec.run_order) == 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_toy_model_under_every_cutting(toy_folder, cuda_device, dtype, mode):
+    from zephyr_b200.engine.replay import TraceReplayer
+    from replay_util import peak_tokens
+
+    folder = toy_folder[dtype]
+    requests = {f"t{i}": random_tokens(VOCAB, n, seed=50 + i) for i, n in enumerate((40, 75, 9, 128, 33, 60))}
+    steps = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions, "mixed": trace_mixed}[mode](requests)
+    replayer = TraceReplayer(folder, dtype, peak_tokens(steps), page_size=8, max_requests=4)
+    replayer.runner.poison_freed_pages = True
+    outputs = {}
+    for step in steps:
+        result = replayer.step(step)
+        if result is not None:
+            outputs[step["step"]] = result
+        replayer.runner.manager.check_invariants()
+    rows = collect(steps, outputs)
+    tolerance = 1e-4 if dtype == "float32" else 0.03
+    expected = {rid: plain_toy_logits(folder, tokens) for rid, tokens in requests.items()}
+    worst = 0.0
+    for (rid, position), got in sorted(rows.items()):
+        error = float(abs(got - expected[rid][position]).max())
+        worst = max(worst, error)
+        assert error <= tolerance, f"{mode} {dtype}: request {rid} position {position}: {error:.3e}"
+    assert replayer.runner.manager.slots.num_free == 4          # every state slot came back
