@@ -35,7 +35,7 @@ class StepEntry:
 
 class ModelRunner:
     def __init__(self, model: Model, page_size: int, num_pages: int, max_requests: int,
-                 max_seq_len: int | None = None):
+                 max_seq_len: int | None = None, use_cuda_graphs: bool = True):
         self.model = model
         self.device = model.device
         self.dtype = model.dtype
@@ -45,6 +45,8 @@ class ModelRunner:
         self.status = ops.new_status(model.device)
         self.poison_freed_pages = False      # tests: NaN into every page that is given back
         self.steps = 0
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graphs: dict[tuple[int, int], dict] = {}
         self.last_step_h2d_bytes = 0     # bytes of the last step's description copied to the device
 
     # ------------------------------------------------------------------ sizing
@@ -99,7 +101,8 @@ class ModelRunner:
                 if not 0 <= int(place) < n:
                     raise InvalidArgumentError(f"wanted place {place} lies outside the {n} tokens brought")
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _describe(self, entries: Sequence[StepEntry], table_width: int | None = None):
+        """The step as host arrays (all int32), in the order they are packed for the device."""
         manager = self.manager
         q_len = [len(e.tokens) for e in entries]
         ctx_before = [manager.computed(e.request_id) for e in entries]
@@ -108,7 +111,7 @@ class ModelRunner:
                 raise OutOfPagesError(
                     f"no pages left for request {entry.request_id!r} ({ctx} cached + {n} new tokens); "
                     f"free pages per group: {[g.pool.num_free for g in manager.groups]}")
-        R, T = len(entries), sum(q_len)
+        R = len(entries)
         q_start = np.zeros(R, dtype=np.int32)
         np.cumsum(q_len[:-1], out=q_start[1:])
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
@@ -118,7 +121,7 @@ class ModelRunner:
         tables = []
         for group in range(len(manager.groups)):
             rows = [manager.block_table(e.request_id, group) for e in entries]
-            width = max(1, max(len(r) for r in rows))
+            width = table_width or max(1, max(len(r) for r in rows))
             table = np.zeros((R, width), dtype=np.int32)
             for i, r in enumerate(rows):
                 table[i, :len(r)] = r
@@ -136,44 +139,116 @@ class ModelRunner:
                     tile_row.append(i)
                     tile_q0.append(q0)
             tiles[(tile_tokens, which)] = (np.asarray(tile_row, dtype=np.int32), np.asarray(tile_q0, dtype=np.int32))
-
-        # One pinned buffer, one copy; the device tensors are views of it.
         arrays = [token_ids, positions, token_row, q_start, np.asarray(q_len, dtype=np.int32),
                   np.asarray(ctx_before, dtype=np.int32), slots, logit_tokens, decode_rows]
         arrays += [t.reshape(-1) for t in tables]
         for pair in tiles.values():
             arrays += list(pair)
+        info = dict(R=R, T=sum(q_len), q_len=q_len, ctx_before=ctx_before, slots=slots.tolist(),
+                    table_widths=[t.shape[1] for t in tables], tile_keys=list(tiles),
+                    num_decode_rows=int(decode_rows.size), max_decode_context=int(max_decode_context))
+        return arrays, info
+
+    def _context_from(self, device: torch.Tensor, sizes: list[int], info: dict) -> StepContext:
+        """A StepContext whose index tensors are views of the packed device buffer."""
+        views, offset = [], 0
+        for size in sizes:
+            views.append(device[offset:offset + size])
+            offset += size
+        (d_tokens, d_pos, d_row, d_qstart, d_qlen, d_ctx, d_slots, d_logit, d_decode), rest = views[:9], views[9:]
+        widths = info["table_widths"]
+        d_tables = [rest[g].view(info["R"], widths[g]) for g in range(len(widths))]
+        rest = rest[len(widths):]
+        d_tiles = {key: (rest[2 * i], rest[2 * i + 1]) for i, key in enumerate(info["tile_keys"])}
+        return StepContext(
+            num_tokens=info["T"], num_rows=info["R"], token_ids=d_tokens, positions=d_pos, token_row=d_row,
+            row_q_start=d_qstart, row_q_len=d_qlen, row_ctx=d_ctx, state_slots=d_slots, block_tables=d_tables,
+            group_of_cache=self.manager.group_of_cache, logit_tokens=d_logit, decode_rows=d_decode,
+            num_decode_rows=info["num_decode_rows"], max_decode_context=info["max_decode_context"], tiles=d_tiles,
+            caches=self.storage, status=self.status, dtype=self.dtype, host_q_len=list(info["q_len"]),
+            host_ctx=list(info["ctx_before"]), host_slots=list(info["slots"]))
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Describe the step and bring the description to the device: one pinned buffer, one copy."""
+        arrays, info = self._describe(entries)
         sizes = [a.size for a in arrays]
         host = torch.empty(max(1, sum(sizes)), dtype=torch.int32, pin_memory=True)
         if sum(sizes):
             np.concatenate(arrays, out=host.numpy()[:sum(sizes)])
         device = host.to(self.device, non_blocking=True)
         self.last_step_h2d_bytes = 4 * sum(sizes)
-        views, offset = [], 0
-        for size in sizes:
-            views.append(device[offset:offset + size])
-            offset += size
-        (d_tokens, d_pos, d_row, d_qstart, d_qlen, d_ctx, d_slots, d_logit, d_decode), rest = views[:9], views[9:]
-        d_tables = [rest[g].view(R, tables[g].shape[1]) for g in range(len(tables))]
-        rest = rest[len(tables):]
-        d_tiles = {key: (rest[2 * i], rest[2 * i + 1]) for i, key in enumerate(tiles)}
-        return StepContext(
-            num_tokens=T, num_rows=R, token_ids=d_tokens, positions=d_pos, token_row=d_row, row_q_start=d_qstart,
-            row_q_len=d_qlen, row_ctx=d_ctx, state_slots=d_slots, block_tables=d_tables,
-            group_of_cache=manager.group_of_cache, logit_tokens=d_logit, decode_rows=d_decode,
-            num_decode_rows=int(decode_rows.size), max_decode_context=int(max_decode_context), tiles=d_tiles,
-            caches=self.storage, status=self.status, dtype=self.dtype, host_q_len=list(q_len),
-            host_ctx=list(ctx_before), host_slots=slots.tolist())
+        return self._context_from(device, sizes, info)
+
+    # ------------------------------------------------------------ decode graphs
+    def _graph_key(self, entries: Sequence[StepEntry]):
+        """Decode-only steps (one token and its logits per entry) replay a captured CUDA graph: the
+        launches of a whole step become one.  The key fixes everything a launch bakes in: the number
+        of rows, and a power-of-two bound on the context (it sizes the attention grid)."""
+        if not self.use_cuda_graphs or not self.model.graph_safe:
+            return None
+        if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
+            return None
+        longest = max(self.manager.computed(e.request_id) for e in entries) + 1
+        bound = max(ops.DECODE_SPLIT_SIZE, 1 << (longest - 1).bit_length())
+        return (len(entries), min(bound, max(self.max_seq_len, ops.DECODE_SPLIT_SIZE)))
+
+    def _step_with_graph(self, key, entries: Sequence[StepEntry]) -> tuple[torch.Tensor, dict]:
+        width = self.manager.blocks_for(self.max_seq_len)
+        arrays, info = self._describe(entries, table_width=width)
+        info["max_decode_context"] = key[1]
+        sizes = [a.size for a in arrays]
+        total = sum(sizes)
+        record = self._graphs.get(key)
+        if record is None:
+            # A small ring of pinned buffers: the host may run ahead of the device, and a buffer must not
+            # be refilled before the copy that reads it has been done.
+            record = {"host": [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(4)],
+                      "copied": [None] * 4, "turn": 0,
+                      "device": torch.empty(total, dtype=torch.int32, device=self.device), "graph": None}
+            self._graphs[key] = record
+        turn = record["turn"]
+        record["turn"] = (turn + 1) % len(record["host"])
+        if record["copied"][turn] is not None:
+            record["copied"][turn].synchronize()
+        np.concatenate(arrays, out=record["host"][turn].numpy())
+        record["device"].copy_(record["host"][turn], non_blocking=True)
+        event = record["copied"][turn] or torch.cuda.Event()
+        event.record()
+        record["copied"][turn] = event
+        self.last_step_h2d_bytes = 4 * total
+        if record["graph"] is None:
+            ctx = self._context_from(record["device"], sizes, info)
+            # One ordinary run first (libraries pick their algorithms and allocate workspaces outside the
+            # capture), then the capture, which records the launches without running them.
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.model.forward(ctx)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                record["logits"] = self.model.forward(ctx)
+            record["graph"] = graph
+        record["graph"].replay()
+        return record["logits"], info
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries as one batch.  Returns float32 logits [sum of wanted places, vocab] on the
         device, in the order of the entries and of each entry's ``want``.  The call does not wait for
-        the GPU; ``check()`` (or reading the logits on the host and then ``check()``) does."""
+        the GPU; ``check()`` (or reading the logits on the host and then ``check()``) does.  The tensor
+        returned by a decode-only step belongs to that step's graph and is overwritten by the next
+        step of the same shape: use it (sample from it, copy it) before stepping again."""
         self._validate(entries)
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx)
-        for entry, before in zip(entries, ctx.host_ctx):
+        key = self._graph_key(entries)
+        if key is not None:
+            logits, info = self._step_with_graph(key, entries)
+            before_all = info["ctx_before"]
+        else:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx)
+            before_all = ctx.host_ctx
+        for entry, before in zip(entries, before_all):
             if self.poison_freed_pages:
                 old = [list(self.manager.block_table(entry.request_id, g)) for g in range(len(self.manager.groups))]
             self.manager.commit(entry.request_id, before + len(entry.tokens))

@@ -26,6 +26,8 @@ from .base import POSITION_ENCODINGS, Mixer, StepContext, lookup, register_mixer
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
                  device: torch.device | str):
         p = spec.params

@@ -63,6 +63,12 @@ class StepContext:
 class Part:
     """Common ground of all parts."""
 
+    # True if ``forward`` only launches work whose shapes depend on the step's sizes, and reads the
+    # step's values (positions, tables, slots) on the device.  Steps of a model whose parts are all
+    # graph-safe may be captured once and replayed.  A part that plans with host values of the
+    # step (``StepContext.host_*``) must leave this False.
+    graph_safe = False
+
     @staticmethod
     def weight_decls(spec) -> dict[str, WeightDecl]:
         """Full tensor names this part reads, with shapes and roles."""

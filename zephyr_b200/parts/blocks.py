@@ -12,6 +12,8 @@ from .base import Block, FeedForward, Mixer, Norm, ResidualStream, StepContext, 
 
 
 class PreNormResidual(Block):
+    graph_safe = True
+
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
         self.mixer = mixer
         self.feed_forward = feed_forward

@@ -18,6 +18,8 @@ from .base import FeedForward, register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec: FeedForwardSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype):
         p = spec.params
         self.hidden = int(p["hidden_size"])

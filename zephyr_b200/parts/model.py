@@ -92,6 +92,11 @@ class Model:
                                      norm2(layer.feed_forward_norm, weights, dtype)))
         self.final_norm = lookup(NORMS, "norm", spec.final_norm.kind)(spec.final_norm, weights, dtype)
         self.cache_specs = cache_specs(spec)
+        parts = [self.final_norm]
+        for block in self.layers:
+            parts += [block, block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm,
+                      getattr(block.mixer, "position", None)]
+        self.graph_safe = all(getattr(part, "graph_safe", False) for part in parts if part is not None)
         self.tile_requests = tile_requests(spec)
 
     @classmethod

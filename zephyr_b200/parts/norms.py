@@ -15,6 +15,8 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec: NormSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype):
         self.size = spec.size
         self.eps = float(spec.eps)

@@ -28,6 +28,8 @@ def rope_tables(head_dim: int, max_positions: int, theta: float) -> tuple[torch.
 
 
 class RopeNeox(PositionEncoding):
+    graph_safe = True
+
     kind = "rope_neox"
 
     def __init__(self, spec: PositionSpec, dtype: torch.dtype, device: torch.device | str):
@@ -47,6 +49,8 @@ class RopeNeox(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     kind = "none"
 
     def __init__(self, spec: PositionSpec, dtype: torch.dtype, device: torch.device | str):
