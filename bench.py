@@ -65,7 +65,7 @@ class ClockSampler:
     def start(self):
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.process = None
@@ -97,7 +97,8 @@ class ClockSampler:
                 "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def build_engine(shape: str, layers: int | None, batch: int, context: int, dtype: str = "bfloat16"):
+def build_engine(shape: str, layers: int | None, batch: int, context: int, dtype: str = "bfloat16",
+                 prefill_together: int = 1):
     import torch
 
     from zephyr_b200 import Engine, Qwen3Config
@@ -116,8 +117,12 @@ def build_engine(shape: str, layers: int | None, batch: int, context: int, dtype
     pages = batch * (-(-context // PAGE_SIZE) + 1) + 1
     engine = Engine(None, dtype=dtype, model_config=config, weights=store,
                     kv_cache=KvCacheOptions(block_size=PAGE_SIZE, num_blocks=pages),
-                    scheduler=PagedSchedulerConfig(max_num_seqs=batch, max_num_batched_tokens=max(PREFILL_TOKENS, batch),
-                                                   max_prefill_chunk_tokens=PREFILL_TOKENS))
+                    # The token budget lets `prefill_together` whole prompts share one step, so that the
+                    # sequences of the end-to-end run start decoding together and the batch stays whole.
+                    scheduler=PagedSchedulerConfig(max_num_seqs=batch,
+                                                   max_num_batched_tokens=max(PREFILL_TOKENS, batch,
+                                                                              prefill_together * context),
+                                                   max_prefill_chunk_tokens=max(PREFILL_TOKENS, context)))
     return engine, config, full_layers
 
 
@@ -160,11 +165,11 @@ def device_decode(engine, batch: int, context: int, warmup: int, steps: int, sam
         logits = runner.step([StepEntry(rid, [rng.randrange(vocab)], (0,)) for rid in ids])
         return engine.sampler.sample_async(logits, greedy, [None] * batch)
 
+    if sampler_clock:
+        sampler_clock.start()        # nvidia-smi takes a moment to start: the warm-up gives it that
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
-    if sampler_clock:
-        sampler_clock.start()
     launches_before = ops.LAUNCHES
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
@@ -195,6 +200,7 @@ def e2e_decode(engine, batch: int, context: int, warmup: int, steps: int):
                 for _ in range(batch)]
     while any(engine.sequences[(r, 0)].state.value != "decode" for r in requests):
         engine.step()
+    assert len({len(engine.sequences[(r, 0)].token_ids) for r in requests}) == 1, "the batch must decode in step"
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
@@ -245,7 +251,7 @@ def run_ours(args) -> dict:
         raise SystemExit("bench.py: no CUDA device")
     peak, peak_source = peaks()
     engine, config, full_layers = build_engine(args.shape, args.layers, max(args.batch, 64) if args.points else args.batch,
-                                               args.context)
+                                               args.context, prefill_together=args.batch)
     runner = engine.runner
     clock = ClockSampler()
     ms, launches, clocks = device_decode(engine, args.batch, args.context, args.warmup, args.steps, clock)

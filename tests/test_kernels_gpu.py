@@ -345,6 +345,61 @@ def test_paged_attention_far_key_and_window_edge(ops, cuda_device, dtype):
             assert dominated == visible
 
 
+PREFILL_CASES = [(4, 2, 32, 8, 0), (16, 8, 128, 16, 0), (6, 6, 64, 4, 0), (32, 2, 128, 16, 0), (12, 3, 96, 32, 0),
+                 (16, 8, 128, 16, 100), (6, 2, 64, 64, 17), (40, 1, 128, 16, 0)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", PREFILL_CASES)
+def test_paged_prefill_tensor_core(ops, cuda_device, nh, nkv, hd, page, window):
+    """The tensor-core prompt kernel: portions of 2 to 300 tokens, with and without cached context
+    before them (lower-right causal alignment), tile edges at 64 and 128, next to single-token rows
+    that it must leave alone."""
+    dtype = torch.bfloat16
+    assert ops.paged_prefill_supported(nh, nkv, hd, dtype)
+    q_lens = [2, 1, 129, 64, 300, 1, 17]
+    ctx = [0, 50, 0, 63, 200, 7, 500]
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 500)
+    tile_row, tile_q0 = tiles_for(q_lens, ops.paged_prefill_tile_tokens(), cuda_device, only_multi=True)
+    status = ops.new_status(cuda_device)
+    out = torch.full_like(q, float("nan"))
+    ops.paged_prefill(q, cache, meta["table"], tile_row, tile_q0, meta["row_q_start"], meta["row_q_len"],
+                      meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status, out=out)
+    ops.check_status(status)
+    got = out.double().cpu().view(-1, nh, hd)
+    cursor = 0
+    for r, n in enumerate(q_lens):
+        if n == 1:
+            assert torch.isnan(got[cursor]).all()              # a single-token row: untouched
+        else:
+            expected = ref_attention_row(qs[r].double(), Ks[r].double(), Vs[r].double(), ctx[r], n, window, nh, nkv)
+            assert torch.isfinite(got[cursor:cursor + n]).all(), f"row {r}"
+            error = (got[cursor:cursor + n] - expected).abs().max()
+            assert error <= tol(dtype, 2.0), f"row {r} (context {ctx[r]}, {n} new): {error}"
+        cursor += n
+
+
+def test_paged_prefill_far_key_and_window_edge(ops, cuda_device):
+    nh, nkv, hd, page = 4, 2, 64, 16
+    for window, key, visible in ((0, 3, True), (50, 700 - 50 + 1, True), (50, 700 - 50, False)):
+        q_lens, ctx = [150, 5], [551, 696]                         # both rows end at position 700
+        for row in (0, 1):
+            q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, torch.bfloat16, nh, nkv, hd, page, q_lens, ctx,
+                                                          600, spike=(row, key))
+            tile_row, tile_q0 = tiles_for(q_lens, ops.paged_prefill_tile_tokens(), cuda_device, only_multi=True)
+            status = ops.new_status(cuda_device)
+            out = torch.zeros_like(q)
+            ops.paged_prefill(q, cache, meta["table"], tile_row, tile_q0, meta["row_q_start"], meta["row_q_len"],
+                              meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status, out=out)
+            ops.check_status(status)
+            got = out.double().cpu().view(-1, nh, hd)
+            last = sum(q_lens[:row + 1]) - 1
+            expected = ref_attention_row(qs[row].double(), Ks[row].double(), Vs[row].double(), ctx[row], q_lens[row],
+                                         window, nh, nkv)[-1]
+            assert (got[last] - expected).abs().max() <= tol(torch.bfloat16, 2.0)
+            dominated = (got[last, 0] - Vs[row][key].double()[0]).abs().max() <= 0.05
+            assert dominated == visible
+
+
 DECODE_CASES = [(4, 2, 32, 8, 0), (16, 8, 128, 16, 0), (8, 8, 64, 4, 0), (32, 2, 128, 16, 0), (12, 3, 96, 32, 0),
                 (16, 8, 128, 16, 300), (6, 2, 64, 64, 0)]
 

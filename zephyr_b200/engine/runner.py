@@ -133,7 +133,7 @@ class ModelRunner:
         for tile_tokens, which in self.model.tile_requests:
             tile_row, tile_q0 = [], []
             for i, n in enumerate(q_len):
-                if which == "multi" and n == 1:
+                if (which == "multi" and n == 1) or (which == "single" and n != 1):
                     continue
                 for q0 in range(0, n, tile_tokens):
                     tile_row.append(i)
@@ -226,10 +226,13 @@ class ModelRunner:
                 self.model.forward(ctx)
             torch.cuda.current_stream(self.device).wait_stream(side)
             graph = torch.cuda.CUDAGraph()
+            launched = ops.LAUNCHES
             with torch.cuda.graph(graph):
                 record["logits"] = self.model.forward(ctx)
+            record["kernels"] = ops.LAUNCHES - launched     # this package's kernels inside the graph
             record["graph"] = graph
         record["graph"].replay()
+        ops.LAUNCHES += record["kernels"]
         return record["logits"], info
 
     @torch.no_grad()

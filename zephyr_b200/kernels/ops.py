@@ -61,6 +61,10 @@ _SIGNATURES = {
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                         c_void_p],
+    "zb_paged_prefill_tile_tokens": [],
+    "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
+    "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
     "zb_sample": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -353,6 +357,33 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
         float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(status), _stream()), "paged_decode", kernels=2)
+    return out
+
+
+def paged_prefill_tile_tokens() -> int:
+    """New tokens of one request per tile of the tensor-core prompt attention kernel."""
+    return library().zb_paged_prefill_tile_tokens()
+
+
+def paged_prefill_supported(nh: int, nkv: int, hd: int, dtype: torch.dtype) -> bool:
+    return dtype in DTYPE_CODE and bool(library().zb_paged_prefill_supported(nh, nkv, hd, DTYPE_CODE[dtype]))
+
+
+def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
+                  tile_q0: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx: torch.Tensor,
+                  nh: int, nkv: int, hd: int, window: int, scale: float, status: torch.Tensor,
+                  out: torch.Tensor) -> torch.Tensor:
+    """Tensor-core attention for rows with several new tokens, cut into tiles of
+    ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out)
+    _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
+    _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
+    _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    _check(library().zb_paged_prefill(
+        _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+        block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
+        _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), _ptr(status), _stream()), "paged_prefill")
     return out
 
 

@@ -60,6 +60,8 @@ class Attention(Mixer):
         self.group = self.nh // self.nkv
         self.tile_tokens = ops.attention_tile_tokens(self.group)
         self.fast_decode = ops.paged_decode_supported(self.nh, self.nkv, self.hd, dtype)
+        self.fast_prefill = ops.paged_prefill_supported(self.nh, self.nkv, self.hd, dtype)
+        self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     @staticmethod
     def weight_decls(spec: MixerSpec) -> dict[str, WeightDecl]:
@@ -85,7 +87,7 @@ class Attention(Mixer):
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
         p = spec.params
         tokens = ops.attention_tile_tokens(int(p["num_heads"]) // int(p["num_kv_heads"]))
-        return [(tokens, "all"), (tokens, "multi")]
+        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (ops.paged_prefill_tile_tokens(), "multi")]
 
     # ------------------------------------------------------------------ forward
     def _project_and_store(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
@@ -122,16 +124,28 @@ class Attention(Mixer):
         return q
 
     def attend(self, q: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+        """Rows with one new token go to the split-context decode kernel, rows with several to the
+        tensor-core prompt kernel, where those kernels take this shape and type; whatever is left
+        goes to the general kernel."""
         cache = ctx.caches[call.cache]
         table = ctx.block_table(call.cache)
         out = torch.empty_like(q)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
-        if self.fast_decode and ctx.num_decode_rows > 0:
+        decode_done = self.fast_decode and ctx.num_decode_rows > 0
+        if decode_done:
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
                              *common, out=out)
-            tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "multi")]
-        else:
-            tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
+        prefill_done = False
+        if self.fast_prefill:
+            tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "multi")]
+            prefill_done = True
+            if tile_row.numel() > 0:
+                ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,
+                                  *common, out=out)
+        if decode_done and prefill_done:
+            return out
+        which = "multi" if decode_done else ("single" if prefill_done else "all")
+        tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
                                 ctx.row_ctx, *common, out=out)

@@ -114,7 +114,7 @@ class Mixer(Part):
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
         """Tilings of the new tokens this mixer wants in ``StepContext.tiles``: (tokens per tile,
-        "all" rows or only "multi"-token rows)."""
+        "all" rows, only "multi"-token rows, or only "single"-token rows)."""
         return []
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
