@@ -86,7 +86,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(cuda_device):
         status = ops.new_status(cuda_device)
         expected = torch.zeros_like(case["q"])
         ops.paged_decode(case["q"], case["cache"], case["table"], case["rows"], case["row_q_start"], case["row_ctx"],
-                         max(contexts) + 1, NH, NKV, HD, 0, 1.0 / math.sqrt(HD), status, out=expected)
+                         max(contexts) + 1, NH, NKV, HD, 0, 1.0 / math.sqrt(HD), status, out=expected, split_size=split)
         got = torch.full_like(case["q"], float("nan"))
         assert lib.zb_paged_decode_no_alloc_bytes_needed(len(contexts), NH, HD, max_splits) <= SCRATCH_BYTES
         rc = call_no_alloc(lib, case, got, status, split, max_splits)

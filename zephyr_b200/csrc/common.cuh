@@ -26,6 +26,7 @@ constexpr int STATUS_POSITION_OUT_OF_RANGE = 2;
 constexpr int STATUS_PAGE_OUT_OF_RANGE = 3;
 constexpr int STATUS_ROW_OUT_OF_RANGE = 4;
 constexpr int STATUS_BAD_LOGIT = 5;
+constexpr int STATUS_COPY_TIMEOUT = 6;    // an asynchronous copy did not complete within the wait limit
 
 __device__ __forceinline__ void report(int* status, int code, int detail, int index) {
   if (status != nullptr && atomicCAS(status, STATUS_OK, code) == STATUS_OK) {

@@ -7,16 +7,17 @@
 // scratch buffer for the partial results of the context splits, which such a caller could not
 // provide; here the scratch is a fixed array that is part of the library image itself.
 //
-// Limit: the partial results must fit ZB_NO_ALLOC_SCRATCH_BYTES (4 MiB):
-//     n_rows * num_heads * max_splits * (head_dim + 2) * 4 bytes <= 4 MiB,
-// for example 32 rows of 16 heads of size 128 at 4,096 tokens of context (16 splits of 256).
+// Limit: the partial results and the arrival counters must fit ZB_NO_ALLOC_SCRATCH_BYTES (4 MiB):
+//     n_rows * num_heads * (max_splits * (head_dim + 2) + 1) * 4 bytes (+ up to 255) <= 4 MiB,
+// for example 31 rows of 16 heads of size 128 at 4,096 tokens of context (16 splits of 256).
 // A larger problem is refused with ZB_ERR_SCRATCH_TOO_SMALL and nothing is launched.
 // Every GPU on which the library is loaded holds these 4 MiB until the process exits.
 //
 // The first call on a device looks up the array's device address (once per device, with that
 // device current); make that first call outside any stream capture.  All calls share the one
-// array, which keeps whatever the last call left in it.  Nothing in it has to start at zero:
-// each call overwrites every partial result it later reads.  Two calls whose kernels overlap on
+// array, which keeps whatever the last call left in it.  The arrival counters at its head must be
+// zero when the kernel starts, so every call clears them first (a memset on the caller's stream);
+// every partial result a call reads it has written itself.  Two calls whose kernels overlap on
 // the GPU (different streams, no ordering between them) would overwrite each other's partial
 // results: order them, or use zb_paged_decode with separate buffers.
 //

@@ -18,8 +18,7 @@ from ..config.errors import InvalidArgumentError, ZephyrError
 from .build import BuildError, build_library
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
-DECODE_SPLIT_SIZE = 256     # positions per split of the decode attention kernel: fixed, so that how a
-                            # row is cut depends on its own length only
+DECODE_SPLIT_SIZE = 256     # the shortest context a captured decode graph is sized for
 
 _RC_TEXT = {1: "an argument outside the kernel's contract", 2: "the CUDA launch failed",
             3: "a configuration this kernel does not support"}
@@ -29,6 +28,7 @@ STATUS_TEXT = {
     3: "a page id outside the cache pool (or the null page) where a real page was expected",
     4: "a request row or block index outside the step's tables",
     5: "NaN or +inf among the logits",
+    6: "an asynchronous copy into shared memory that did not complete within the wait limit",
 }
 
 
@@ -60,7 +60,7 @@ _SIGNATURES = {
     "zb_paged_decode_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
-                        c_void_p],
+                        c_void_p, c_void_p],
     "zb_paged_prefill_tile_tokens": [],
     "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -147,6 +147,9 @@ def check_status(status: torch.Tensor, where: str = "step") -> None:
     code, detail, index, _ = status.tolist()
     if code != 0:
         status.zero_()
+        for pool in _decode_buffers.values():       # a kernel that gave up may have left counters behind
+            for _, count in pool:
+                count.zero_()
         raise KernelError(f"{where}: a kernel reported {STATUS_TEXT.get(code, f'error {code}')} "
                           f"(value {detail}, at element {index})")
 
@@ -334,29 +337,65 @@ def paged_decode_scratch_floats(n_rows: int, nh: int, hd: int, max_splits: int) 
     return int(library().zb_paged_decode_scratch_floats(n_rows, nh, hd, max_splits))
 
 
+# Buffers of the decode kernel, kept for the life of the process: the partial results of the splits
+# (contents irrelevant between calls) and the arrival counters (zero between calls: the kernel
+# leaves them as it found them).  Buffers are only ever added, never freed or moved, because
+# captured graphs hold their addresses.
+_decode_buffers: dict[torch.device, list[tuple[torch.Tensor, torch.Tensor]]] = {}
+
+
+def _decode_workspace(device: torch.device, floats: int, counters: int) -> tuple[torch.Tensor, torch.Tensor]:
+    pool = _decode_buffers.setdefault(device, [])
+    for scratch, count in pool:
+        if scratch.numel() >= floats and count.numel() >= counters:
+            return scratch, count
+    scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    count = torch.zeros(max(counters, 1 << 12), dtype=torch.int32, device=device)
+    pool.append((scratch, count))
+    return scratch, count
+
+
+def decode_split_size(n_rows: int, nkv: int, max_context: int) -> int:
+    """Positions per split: as long as possible (fewer partial results to merge, less start-up cost
+    per CTA) while the grid still fills the GPU.  It depends on the batch, so the split points of a
+    row, and with them the last bits of its result, depend on what else is decoded beside it."""
+    split = 1024
+    while split > 128 and n_rows * nkv * math.ceil(max_context / split) < 256:
+        split //= 2
+    return split
+
+
 def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
                  row_q_start: torch.Tensor, row_ctx: torch.Tensor, max_context: int, nh: int, nkv: int, hd: int,
                  window: int, scale: float, status: torch.Tensor, out: torch.Tensor,
-                 scratch: torch.Tensor | None = None, split_size: int = DECODE_SPLIT_SIZE) -> torch.Tensor:
+                 scratch: torch.Tensor | None = None, split_size: int | None = None,
+                 counters: torch.Tensor | None = None) -> torch.Tensor:
     """Split-context attention for rows with one new token each; writes those tokens' rows of ``out``.
 
-    ``max_context`` is at least the longest context of the rows, the new token included."""
+    ``max_context`` is at least the longest context of the rows, the new token included.  ``scratch``
+    (float32, any contents) and ``counters`` (int32, zero) come from a process-wide workspace unless
+    given."""
     _cuda(q, kv_cache, block_table, rows, row_q_start, row_ctx, status, out)
     _i32(block_table, rows, row_q_start, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
     n_rows = rows.numel()
+    if split_size is None:
+        split_size = decode_split_size(n_rows, nkv, max_context)
     max_splits = max(1, math.ceil(max_context / split_size))
     need = paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
-    if scratch is None:
-        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if scratch is None or counters is None:
+        scratch, counters = _decode_workspace(q.device, need, n_rows * nkv)
     _require(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
              f"scratch must hold {need} floats")
+    _require(counters.dtype == torch.int32 and counters.is_contiguous() and counters.numel() >= n_rows * nkv,
+             f"counters must hold {n_rows * nkv} zeroed int32 values")
     _check(library().zb_paged_decode(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
-        float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(status), _stream()), "paged_decode", kernels=2)
+        float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(counters), _ptr(status), _stream()),
+        "paged_decode")
     return out
 
 
