@@ -102,6 +102,16 @@ def test_gather_rows(ops, cuda_device, dtype):
     ops.check_status(status)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(5, 200), (3, 3072), (130, 144), (1, 8)])
+def test_silu_mul_blocked_layout(ops, cuda_device, dtype, T, I):
+    g = rand((T, I), dtype, cuda_device, 8, 3.0)
+    u = rand((T, I), dtype, cuda_device, 9, 3.0)
+    gu = torch.stack([g.view(T, I // 8, 8), u.view(T, I // 8, 8)], dim=2).reshape(T, 2 * I).contiguous()
+    got = ops.silu_mul(gu, blocked=True)
+    assert torch.equal(got, ops.silu_mul(torch.cat([g, u], dim=1).contiguous()))
+
+
 # ------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("M,N,K", [(1, 311, 100), (7, 64, 64), (130, 200, 96), (65, 1000, 1030), (3, 5, 1)])
 def test_gemm_simt_float32_is_exact_float32(ops, cuda_device, M, N, K):
@@ -129,6 +139,51 @@ def test_gemm_simt_bfloat16_inputs(ops, cuda_device):
     assert (got.double() - x.double() @ w.double().T).abs().max() <= 1e-4
     assert ops.linear(x, w, out_dtype=torch.float32).dtype == torch.float32
     assert (ops.linear(x, w, out_dtype=torch.float32).double() - x.double() @ w.double().T).abs().max() <= 1e-3
+
+
+SMALL_GEMM_CASES = [(1, 311, 96), (8, 4096, 1024), (8, 1024, 3072), (3, 200, 200), (16, 1024, 2048), (33, 96, 136),
+                    (64, 6144, 1024), (7, 50, 8), (8, 151936, 1024)]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", SMALL_GEMM_CASES)
+def test_gemm_small_weight_streamer(ops, cuda_device, M, N, K, out_dtype):
+    x = rand((M, K), torch.bfloat16, cuda_device, 40)
+    w = rand((N, K), torch.bfloat16, cuda_device, 41, 0.1)
+    assert ops.gemm_small_supported(x, w)
+    got = ops.gemm_small(x, w, out_dtype=out_dtype)
+    expected = x.double() @ w.double().T
+    bound = 1e-3 * math.sqrt(K) if out_dtype == torch.float32 else 4e-3 * max(1.0, float(expected.abs().max()))
+    assert got.dtype == out_dtype and (got.double() - expected).abs().max() <= bound
+    # rows do not depend on the rows beside them
+    if M > 1:
+        alone = ops.gemm_small(x[M - 1:].contiguous(), w, out_dtype=out_dtype)
+        assert torch.equal(alone, got[M - 1:])
+    # strided activations (a slice of a wider buffer)
+    wide = torch.zeros((M, K + 16), dtype=torch.bfloat16, device=cuda_device)
+    wide[:, :K] = x
+    assert torch.equal(ops.gemm_small(wide[:, :K], w, out_dtype=out_dtype), got)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 3072, 1024), (20, 200, 96), (64, 144, 80)])
+def test_gemm_small_fused_swiglu(ops, cuda_device, M, I, K):
+    x = rand((M, K), torch.bfloat16, cuda_device, 42)
+    gate = rand((I, K), torch.bfloat16, cuda_device, 43, 0.2)
+    up = rand((I, K), torch.bfloat16, cuda_device, 44, 0.2)
+    w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    got = ops.gemm_small(x, w, swiglu=True)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    expected = g / (1 + torch.exp(-g)) * u
+    assert got.shape == (M, I) and (got.double() - expected).abs().max() <= 8e-3 * max(1.0, float(expected.abs().max()))
+
+
+def test_gemm_small_refuses(ops, cuda_device):
+    x = rand((65, 64), torch.bfloat16, cuda_device, 45)
+    w = rand((32, 64), torch.bfloat16, cuda_device, 46)
+    assert not ops.gemm_small_supported(x, w)
+    assert not ops.gemm_small_supported(x[:4, :60], w[:, :60])          # K no multiple of 8
+    assert not ops.gemm_small_supported(x[:4].float(), w.float())
+    assert ops.linear(x, w).shape == (65, 32)                            # the library product takes over
 
 
 # ------------------------------------------------------- norm + rotation + cache

@@ -166,6 +166,45 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ g
   }
 }
 
+// The same for gate and up columns interleaved in blocks of 8: columns [16j, 16j+8) are gate
+// values, [16j+8, 16j+16) the matching up values; out[t, 8j + r] = silu(gate) * up.
+template <typename T>
+__global__ void silu_mul_blocked_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int I) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long t = e / I;
+    const int i = static_cast<int>(e - t * I);
+    const long long base = t * 2 * I + (i / 8) * 16 + (i % 8);
+    const float g = to_float(gu[base]);
+    const float u = to_float(gu[base + 8]);
+    out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// One thread per block of 8 outputs: the gate block and the up block are one 16-byte (bfloat16) or
+// two 16-byte (float32) loads each.
+template <typename T>
+__global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, long long blocks8, int I) {
+  constexpr int N = Vec<T>::N, PARTS = 8 / N;
+  const int per_row = I / 8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < blocks8; e += stride) {
+    const long long t = e / per_row;
+    const int j = static_cast<int>(e - t * per_row);
+    const T* src = gu + t * 2 * I + j * 16;
+    T* dst = out + t * I + j * 8;
+#pragma unroll
+    for (int p = 0; p < PARTS; ++p) {
+      float g[N], u[N];
+      load_vec<T>(src + p * N, g);
+      load_vec<T>(src + 8 + p * N, u);
+#pragma unroll
+      for (int k = 0; k < N; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+      store_vec<T>(dst + p * N, g);
+    }
+  }
+}
+
 template <typename T> bool aligned16(const void* p, long long elems) {
   return reinterpret_cast<uintptr_t>(p) % 16 == 0 && elems % Vec<T>::N == 0;
 }
@@ -266,10 +305,25 @@ ZB_API int zb_add_rmsnorm(void* out, void* residual, const void* delta, const vo
              : rmsnorm_launch<__nv_bfloat16>(out, residual, delta, w, w_dtype, eps, rows, H, H, H, s);
 }
 
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i]
-ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, void* stream) {
-  if (T < 0 || I < 0) return ERR_BAD_ARGUMENT;
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]; with blocked != 0 gate and up columns alternate in
+// blocks of 8 (I a multiple of 8): out[t, 8j + r] = silu(gu[t, 16j + r]) * gu[t, 16j + 8 + r].
+ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int blocked, void* stream) {
+  if (T < 0 || I < 0 || (blocked && I % 8 != 0)) return ERR_BAD_ARGUMENT;
   auto s = static_cast<cudaStream_t>(stream);
+  if (blocked) {
+    if (T == 0 || I == 0) return OK;
+    const bool vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0;
+    const long long total = vec ? static_cast<long long>(T) * (I / 8) : static_cast<long long>(T) * I;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+    if (dtype == DTYPE_F32) {
+      if (vec) silu_mul_blocked_vec_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I);
+      else silu_mul_blocked_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I);
+    } else {
+      if (vec) silu_mul_blocked_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I);
+      else silu_mul_blocked_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I);
+    }
+    return launch_result();
+  }
   return dtype == DTYPE_F32 ? silu_mul_launch<float>(out, gu, T, I, s)
                             : silu_mul_launch<__nv_bfloat16>(out, gu, T, I, s);
 }

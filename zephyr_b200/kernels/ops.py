@@ -45,7 +45,7 @@ _SIGNATURES = {
     "zb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_longlong, c_longlong, c_int,
                    c_void_p],
     "zb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p],
-    "zb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_void_p, c_void_p],
@@ -65,6 +65,9 @@ _SIGNATURES = {
     "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "zb_gemm_small_supported": [c_int, c_int, c_int],
+    "zb_gemm_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                      c_int, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
     "zb_sample": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -215,8 +218,9 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, ep
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """silu(gate_up[:, :I]) * gate_up[:, I:] for a contiguous [T, 2I] tensor."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bool = False) -> torch.Tensor:
+    """silu(gate_up[:, :I]) * gate_up[:, I:] for a contiguous [T, 2I] tensor.  With ``blocked`` the gate
+    and up columns alternate in blocks of 8 (the layout ``gemm_small(..., swiglu=True)`` reads)."""
     _cuda(gate_up)
     _require(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.dtype in DTYPE_CODE
              and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [T, 2I] tensor")
@@ -224,8 +228,9 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
     if out is None:
         out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _require(out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype and out.is_contiguous(), "out must be [T, I]")
-    _check(library().zb_silu_mul(_ptr(out), _ptr(gate_up), T, two_i // 2, DTYPE_CODE[gate_up.dtype], _stream()),
-           "silu_mul")
+    _require(not blocked or (two_i // 2) % 8 == 0, "the blocked layout needs I to be a multiple of 8")
+    _check(library().zb_silu_mul(_ptr(out), _ptr(gate_up), T, two_i // 2, DTYPE_CODE[gate_up.dtype], int(blocked),
+                                 _stream()), "silu_mul")
     return out
 
 
@@ -444,13 +449,46 @@ def gemm_nt_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None
     return out
 
 
+SMALL_GEMM_MAX_ROWS = 64      # what the kernel takes
+SMALL_GEMM_ROWS = 16          # up to here it beats the library product; beyond, activations are re-read too often
+
+
+def gemm_small_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """True if the weight-streaming kernel for few rows takes x [M, K] times w [N, K] transposed."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.shape[0] <= SMALL_GEMM_MAX_ROWS and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(library().zb_gemm_small_supported(x.shape[0], w.shape[0], x.shape[1])))
+
+
+def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+               swiglu: bool = False) -> torch.Tensor:
+    """x [M <= 64, K] times w [N, K] transposed, bfloat16, float32 accumulation, weights read once.
+    With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up rows, and the
+    result is silu(gate) * up, [M, N / 2]."""
+    _cuda(x, w)
+    _require(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "x [M, K] and w [N, K]")
+    _require(gemm_small_supported(x, w), "gemm_small takes bfloat16, M <= 64, K a multiple of 8, 16-byte aligned rows")
+    out_dtype = out_dtype or x.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    _require(not swiglu or N % 16 == 0, "swiglu needs a multiple of 16 rows")
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    _check(library().zb_gemm_small(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                                   DTYPE_CODE[out_dtype], int(swiglu), _stream()), "gemm_small")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """y = x w^T.  float32 runs on this package's CUDA-core kernel (no TF32 anywhere); bfloat16
-    runs on the vendor library's tensor-core product, as the reference's linear layers do
-    (src/layer/linear.cpp:22-24 -> cuBLASLt), with float32 accumulation."""
+    """y = x w^T.  float32 runs on this package's CUDA-core kernel (no TF32 anywhere).  bfloat16
+    with up to 64 rows (a decode step) runs on this package's weight-streaming kernel; larger
+    bfloat16 products run on the vendor library's tensor-core product, as the reference's linear
+    layers do (src/layer/linear.cpp:22-24 -> cuBLASLt).  Accumulation is float32 everywhere."""
     _cuda(x, w)
     if x.dtype == torch.float32:
         return gemm_nt_simt(x, w, out_dtype)
+    if x.shape[0] <= SMALL_GEMM_ROWS and gemm_small_supported(x, w):
+        return gemm_small(x, w, out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -1,7 +1,8 @@
 """The dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases.
 
-Gate and up run as one product over the row-concatenated weight [2I, H] (rows 0..I-1 gate), as the
-reference packs them at load (src/layer/mlp.cpp:16-36).  silu and the product are one float32
+Gate and up run as one product over one packed weight [2I, H], as the reference packs them at
+load (src/layer/mlp.cpp:16-36); the reference puts all gate rows first, this part alternates blocks
+of 8 gate rows and 8 up rows (see ``__init__``).  silu and the product are one float32
 pass with a single rounding; the reference rounds between them (src/layer/activation.cu:31-33).
 """
 
@@ -24,7 +25,15 @@ class SwiGLU(FeedForward):
         p = spec.params
         self.hidden = int(p["hidden_size"])
         self.intermediate = int(p["intermediate_size"])
-        self.w_gate_up = torch.cat([weights[p["gate_proj"]], weights[p["up_proj"]]], dim=0).contiguous()
+        gate, up = weights[p["gate_proj"]], weights[p["up_proj"]]
+        # With I a multiple of 8 the rows alternate in blocks of 8 gate rows and their 8 up rows, the
+        # order in which the decode kernel applies silu(gate) * up inside the product's epilogue.
+        self.blocked = self.intermediate % 8 == 0
+        if self.blocked:
+            k = gate.shape[1]
+            self.w_gate_up = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(-1, k).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights[p["down_proj"]]
 
     @staticmethod
@@ -38,7 +47,11 @@ class SwiGLU(FeedForward):
         }
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+        if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
+            hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True)       # product and activation in one kernel
+        else:
+            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked)
+        return ops.linear(hidden, self.w_down)
 
 
 register_feed_forward("swiglu", SwiGLU)
