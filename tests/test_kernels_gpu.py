@@ -249,8 +249,9 @@ def test_qk_norm_rope_cache(ops, cuda_device, dtype, nh, nkv, hd, page):
         r, p = int(token_row[t]), int(pos[t])
         pg, off = tables[r][p // page], p % page
         written[pg, off] = True
-        assert (cache_cpu[pg, 0, :, off] - k_ref[t]).abs().max() <= tol(dtype, 8.0)
-        assert torch.equal(cache_cpu[pg, 1, :, off], v_ref[t])
+        perm = ops.kv_row_permutation(p, hd, dtype)            # rows are stored with permuted 16-byte chunks
+        assert (cache_cpu[pg, 0, :, off][:, perm] - k_ref[t]).abs().max() <= tol(dtype, 8.0)
+        assert torch.equal(cache_cpu[pg, 1, :, off][:, perm], v_ref[t])
     # nothing else was touched
     untouched = cache_cpu[:, 0, 0, :, 0][~written]
     assert torch.isnan(untouched).all()
@@ -323,10 +324,13 @@ def build_paged_case(device, dtype, nh, nkv, hd, page, q_lens, ctx, seed, spike=
             K[spike[1]] = (direction * 6.0).to(dtype)
             q[-1] = (direction * 6.0 * math.sqrt(hd) / 2).to(dtype)
         Ks.append(K), Vs.append(V), qs.append(q)
+        from zephyr_b200.kernels.ops import kv_row_permutation
+
         for p in range(totals[r]):
             pg, off = tables[r][p // page], p % page
-            cache[pg, 0, :, off] = K[p].to(device)
-            cache[pg, 1, :, off] = V[p].to(device)
+            inverse = torch.argsort(kv_row_permutation(p, hd, dtype))     # stored[j] = logical[inverse[j]]
+            cache[pg, 0, :, off] = K[p][:, inverse].to(device)
+            cache[pg, 1, :, off] = V[p][:, inverse].to(device)
     q_all = torch.cat(qs).reshape(-1, nh * hd).to(device)
     meta = dict(
         table=table.to(device),
@@ -459,7 +463,7 @@ DECODE_CASES = [(4, 2, 32, 8, 0), (16, 8, 128, 16, 0), (8, 8, 64, 4, 0), (32, 2,
                 (16, 8, 128, 16, 300), (6, 2, 64, 64, 0)]
 
 
-@pytest.mark.parametrize("split_size", [None, 64, 256])
+@pytest.mark.parametrize("split_size", [None, 32, 64, 256])
 @pytest.mark.parametrize("nh,nkv,hd,page,window", DECODE_CASES)
 def test_paged_decode_split(ops, cuda_device, nh, nkv, hd, page, window, split_size):
     """The split-context decode kernel at context lengths around tile and split edges, mixed with

@@ -3,7 +3,11 @@
 A paged cache is ``[num_pages, 2 (keys, values), kv_heads, page_size, head_dim]`` in the model's
 type: the rows of one page and head lie together (``page_size * head_dim`` contiguous elements), so
 a kernel fetches a page's keys for one head as one contiguous run.  Caches of one group are indexed
-by the same page ids.  A state cache is ``[num_slots, *shape]``.
+by the same page ids.  Inside a row (the ``head_dim`` values of one position and head) the 16-byte
+chunks are permuted by the position (``kv_swizzle`` in csrc/common.cuh, mirrored by
+``kernels.ops.kv_swizzle``): a page copied into shared memory as it is, by one bulk copy, can then be
+read by the tensor-core loads without bank conflicts.  Only the kernels (and tests that fill a cache
+by hand) know of the permutation.  A state cache is ``[num_slots, *shape]``.
 
 The reference keeps two tensors per layer, keys packed ``[blocks, kvh, hd/x, bs, x]`` and values
 ``[blocks, kvh, hd, bs]`` (src/kv_cache/cache_engine.cpp:66-102), a layout made for scalar loads.

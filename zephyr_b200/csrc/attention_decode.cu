@@ -1,31 +1,40 @@
 // Split-context paged attention for single decoded tokens, bfloat16 keys and values, float32
 // scores, softmax and accumulation.
 //
-// The decode step is bound by reading the cache, so the kernel is built around the copy.  Each CTA
-// owns one (request, key/value head, split of the context) and streams its keys and values
-// through a ring of shared-memory tiles.  The copies are bulk asynchronous copies (the TMA engine's
-// untiled form, cp.async.bulk): one instruction per key row, completion counted on an mbarrier, so
-// the threads spend no time on address arithmetic and several tiles are in flight per SM.  All query
-// heads of the group share each tile; the two small products (scores, and probabilities times
-// values) run on tensor cores with the group's heads padded to the 16 rows of an m16n8k16 tile.
-// The last CTA of a (request, key/value head) to finish merges the splits: an atomic counter tells
-// it that it is last, so no CTA ever waits for another, and no second launch is needed.
+// The decode step is bound by reading the cache, so the kernel is built around the copy.  One
+// persistent CTA per SM walks a list of work items, an item being one (request, key/value head,
+// split of the context).  Inside the CTA the work is split by role:
+//   * one producer warp runs ahead through the items and streams their keys and values into a
+//     ring of shared-memory tiles of 32 positions with bulk asynchronous copies (the TMA engine's
+//     untiled form, cp.async.bulk), one instruction per page of keys or values (the cache stores
+//     rows with permuted 16-byte chunks so that a page copied as it is can be read without bank
+//     conflicts), completion counted on an mbarrier per tile; it waits only for a tile's slot to be
+//     handed back, so the ring, nearly all of the SM's shared memory, stays full of copies in
+//     flight, across item boundaries too;
+//   * four consumer warps each take every fourth tile of the current item, whole: scores and
+//     probabilities-times-values run on tensor cores (m16n8k16, the group's query heads padded to
+//     the 16 rows), the softmax is online in float32; a consumer hands the slot back the moment
+//     it has read it.  No barrier spans the CTA inside an item.
+// When an item's tiles are done the consumers merge their four states; the item's result is a
+// partial one unless the item covers its row's whole context.  The last item of a (request,
+// key/value head) to finish, found with an atomic counter, merges the splits' partial results, so
+// no CTA ever waits for another and there is no second launch.
 //
 // Math as in attention_simt.cu (reference: src/attention/paged_decode.cu:169-352 for the split
 // scheme), except where that kernel is not exact: no epsilon is added to the denominator, and
 // partial results stay float32.  Probabilities are rounded to bfloat16 for the second product, as
-// the reference does (paged_decode.cu:289).
+// the reference does (paged_decode.cu:289).  Every wait is bounded and reports instead of hanging.
 #include "common.cuh"
 #include "mma.cuh"
 
 namespace zb {
 
-constexpr int DEC_WARPS = 4;
-constexpr int DEC_TILE = 64;            // keys per shared-memory tile; 16 per warp
-constexpr int DEC_STAGES = 3;
-constexpr int DEC_MAX_GROUP = 16;       // query heads per key/value head that fit one MMA tile
-constexpr int DEC_WAIT_LIMIT = 1 << 22; // polls of an mbarrier before the kernel gives up and reports
-static_assert(DEC_WARPS * 32 == 2 * DEC_TILE, "one key row or one value row per thread and tile");
+constexpr int DEC_CONSUMERS = 4;
+constexpr int DEC_THREADS = (DEC_CONSUMERS + 1) * 32;   // consumers are warps 0..3, the producer is warp 4
+constexpr int DEC_TILE = 32;             // positions per tile: one consumer warp's unit of work
+constexpr int DEC_MAX_GROUP = 16;        // query heads per key/value head that fit one MMA tile
+constexpr int DEC_WAIT_LIMIT = 1 << 24;  // polls of an mbarrier before a warp gives up and reports
+constexpr int DEC_SMEM_BUDGET = 227 * 1024 - 1024;
 
 struct DecodeArgs {
   const __nv_bfloat16* q;        // [T, nh*hd]
@@ -38,8 +47,8 @@ struct DecodeArgs {
   float* part_o;                 // [n_rows, nh, max_splits, hd]
   float* part_ml;                // [n_rows, nh, max_splits, 2]
   int* counters;                 // [n_rows, nkv] zero on entry, zero again on exit
-  int max_blocks, page_shift, num_pages, num_rows;
-  int nh, nkv, window, split_size, max_splits;
+  int max_blocks, page_shift, num_pages, num_rows, n_rows;
+  int nh, nkv, window, split_size, max_splits, ring_slots;
   float scale_log2;              // scale * log2(e)
   int* status;
 };
@@ -51,293 +60,390 @@ __device__ __forceinline__ void split_range(int ctx_total, int window, int split
   end = min((s + 1) * split_size, ctx_total);
 }
 
+// One work item, as producer and consumers both derive it from the item's number.
+struct DecodeItem {
+  int r, row, kvh, split, ctx_total, begin, end, first_tile, n_tiles;
+};
+
+__device__ __forceinline__ bool decode_item(const DecodeArgs& a, int id, DecodeItem& it) {
+  it.split = id % a.max_splits;
+  it.kvh = (id / a.max_splits) % a.nkv;
+  it.r = id / (a.max_splits * a.nkv);
+  it.row = a.rows[it.r];
+  if (it.row < 0 || it.row >= a.num_rows) return false;        // reported once, by the consumers
+  it.ctx_total = a.row_ctx[it.row] + 1;
+  split_range(it.ctx_total, a.window, a.split_size, it.split, it.begin, it.end);
+  if (it.begin >= it.end) return false;
+  it.first_tile = it.begin / DEC_TILE * DEC_TILE;
+  it.n_tiles = (it.end - it.first_tile + DEC_TILE - 1) / DEC_TILE;
+  return true;
+}
+
+__device__ __forceinline__ void consumer_barrier() {      // the 128 consumer threads only
+  asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_CONSUMERS * 32) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <int HD>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-paged_decode_split_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+paged_decode_kernel(const DecodeArgs a) {
   static_assert(HD % 32 == 0 && HD <= 128, "head sizes 32, 64, 96, 128");
-  constexpr int KROW = HD + 8;                     // padded row: ldmatrix reads without bank conflicts
-  constexpr int STAGE = 2 * DEC_TILE * KROW;       // elements of one stage (keys, then values)
+  constexpr int KROW = HD + 8;                     // padded row of the query buffer
+  constexpr int CHUNKS = HD / 8;                   // 16-byte chunks of a cache row
+  // A ring slot holds 32 key rows and 32 value rows exactly as they lie in the cache pages: back to
+  // back, chunks permuted (kv_swizzle), which is what makes unpadded rows conflict-free for ldmatrix.
+  constexpr int SLOT = 2 * DEC_TILE * HD;
   constexpr unsigned ROW_BYTES = HD * sizeof(__nv_bfloat16);
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(tiles + DEC_STAGES * STAGE);
+  const int g = a.nh / a.nkv, R = a.ring_slots;
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [R][2][DEC_TILE][HD]
+  __nv_bfloat16* qbuf = ring + static_cast<size_t>(R) * SLOT;                        // [2][16][KROW]
+  float* merge_o = reinterpret_cast<float*>(qbuf + 2 * 16 * KROW);                   // [consumers][g][HD]
+  float* merge_ml = merge_o + DEC_CONSUMERS * g * HD;                                // [consumers][g][2]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(merge_ml + DEC_CONSUMERS * g * 2);
+  unsigned long long* empty = full + R;
+  unsigned long long* qfull = empty + R;
+  unsigned long long* qempty = qfull + 2;
+  int* page_ids = reinterpret_cast<int*>(qempty + 2);         // the current item's pages, for the producer
   __shared__ int is_last;
+  __shared__ volatile int abort_flag;      // set by the first warp whose wait ran out; every later wait gives up at once
 
-  const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
-  const int row = a.rows[r];
-  if (row < 0 || row >= a.num_rows) {
-    if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, r);
-    return;
-  }
-  const int ctx_total = a.row_ctx[row] + 1;
-  int begin, end;
-  split_range(ctx_total, a.window, a.split_size, split, begin, end);
-  if (begin >= end) return;
-
-  const int g = a.nh / a.nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
-  const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
-  const int page_size = 1 << a.page_shift;
-
+  if (threadIdx.x == 0) abort_flag = 0;
+  // A bounded wait that also ends when another warp has given up.
+  auto wait = [&](unsigned long long* bar, unsigned parity) -> bool {
+    for (int i = 0; i < DEC_WAIT_LIMIT; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 63) == 63 && abort_flag) return false;
+    }
+    return false;
+  };
+  for (int e = threadIdx.x; e < 2 * 16 * KROW / 8; e += DEC_THREADS)
+    reinterpret_cast<uint4*>(qbuf)[e] = make_uint4(0, 0, 0, 0);      // rows past the group stay zero for good
   if (threadIdx.x == 0) {
-#pragma unroll
-    for (int st = 0; st < DEC_STAGES; ++st) mbar_init(&bars[st], 1);
+    for (int s = 0; s < R; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&qfull[s], 1); mbar_init(&qempty[s], DEC_CONSUMERS); }
     fence_barrier_init();
   }
   __syncthreads();
-
-  const int first_tile = begin / DEC_TILE * DEC_TILE;
-  const int n_tiles = (end - first_tile + DEC_TILE - 1) / DEC_TILE;
-
-  // Thread (j, sel) brings key row j (sel 0) or value row j (sel 1) of every tile.
-  const int my_key = threadIdx.x & (DEC_TILE - 1), my_sel = threadIdx.x >> 6;
+  fence_proxy_async();
+  const int n_items = a.n_rows * a.nkv * a.max_splits;
+  const int page_size = 1 << a.page_shift;
   const long long page_stride = 2LL * a.nkv * page_size * HD;
-  const __nv_bfloat16* my_base = a.kv_cache + (static_cast<long long>(my_sel) * a.nkv + kvh) * page_size * HD;
-  __nv_bfloat16* my_dst = tiles + my_sel * DEC_TILE * KROW + my_key * KROW;
-  // The page of this thread's row of tile t (-1 outside the split).  Looked up one iteration before it
-  // is needed, so that the copy of a tile is issued the moment its stage is free.
-  auto lookup = [&](int t) -> int {
-    const int pos = first_tile + t * DEC_TILE + my_key;
-    if (t >= n_tiles || pos < begin || pos >= end) return -1;
-    const int block = pos >> a.page_shift;
-    const int page = block < a.max_blocks ? table[block] : 0;
-    return page < 0 ? 0 : page;
-  };
-  auto load_tile = [&](int t, int page) {
-    const int stage = t % DEC_STAGES;
-    __nv_bfloat16* dst = my_dst + stage * STAGE;
-    const int k0 = first_tile + t * DEC_TILE;
-    if (threadIdx.x == 0) {
-      const int n_valid = max(0, min(end, k0 + DEC_TILE) - max(begin, k0));
-      mbar_arrive_expect_tx(&bars[stage], static_cast<unsigned>(n_valid) * 2u * ROW_BYTES);
-    }
-    if (page >= 0) {
-      if (page == 0 || page >= a.num_pages) {
-        report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, row);
-        page = 0;            // the announced bytes must still arrive: read the null page instead
+
+  if (warp == DEC_CONSUMERS) {
+    // ------------------------------------------------------------------------- the producer
+    int tile_seq = 0, item_seq = 0;
+    for (int id = blockIdx.x; id < n_items; id += gridDim.x) {
+      DecodeItem it;
+      if (!decode_item(a, id, it)) continue;
+      const int qb = item_seq & 1;
+      if (!wait(&qempty[qb], ((item_seq >> 1) & 1) ^ 1)) {
+        if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -1, it.row);
+        abort_flag = 1;
+        return;
       }
-      bulk_copy_g2s(dst, my_base + page * page_stride + ((k0 + my_key) & (page_size - 1)) * HD, ROW_BYTES,
-                    &bars[stage]);
-    } else {
-      // Outside the split: zeros, so that a probability of zero times this row stays zero.
-#pragma unroll
-      for (int c = 0; c < HD / 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+      if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
+      if (lane < g)
+        bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
+                      a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
+                      ROW_BYTES, &qfull[qb]);
+      ++item_seq;
+      // The item's page ids in one go (one round trip to memory per item instead of one per tile).
+      const int* table = a.block_table + static_cast<size_t>(it.row) * a.max_blocks;
+      const int first_block = it.first_tile >> a.page_shift;
+      const int n_blocks = ((it.first_tile + it.n_tiles * DEC_TILE - 1) >> a.page_shift) - first_block + 1;
+      for (int i = lane; i < n_blocks; i += 32)
+        page_ids[i] = first_block + i < a.max_blocks ? table[first_block + i] : -1;
+      __syncwarp();
+      const __nv_bfloat16* base = a.kv_cache + static_cast<long long>(it.kvh) * page_size * HD;
+      const long long v_offset = static_cast<long long>(a.nkv) * page_size * HD;
+      // A tile's rows are copied in runs that are contiguous in the cache: a whole page at a time for
+      // pages of up to 32 positions, a 32-row piece of a page for larger ones.  One bulk copy for
+      // the keys of a run and one for its values: a handful of instructions move 16 KB.
+      const int run_rows = page_size < DEC_TILE ? page_size : DEC_TILE;
+      const int n_runs = DEC_TILE / run_rows;
+      for (int t = 0; t < it.n_tiles; ++t, ++tile_seq) {
+        const int slot = tile_seq % R;
+        if (!wait(&empty[slot], ((tile_seq / R) & 1) ^ 1)) {
+          if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -2, it.row);
+          abort_flag = 1;
+          return;
+        }
+        fence_proxy_async();   // the consumers' ordinary stores to the slot come before the copies into it
+        const int p0 = it.first_tile + t * DEC_TILE + lane * run_rows;     // first position of this lane's run
+        const bool copies = lane < n_runs && (p0 >> a.page_shift) < a.max_blocks;
+        if (copies) {
+          int page = page_ids[(p0 >> a.page_shift) - first_block];
+          if (page <= 0 || page >= a.num_pages) {
+            // Fine for a run nobody wants (a page given back behind a window, the tail of the table);
+            // an error if one of its positions is in the item.  Either way the bytes must arrive.
+            if (p0 + run_rows > it.begin && p0 < it.end) report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, it.row);
+            page = 0;
+          }
+          const __nv_bfloat16* src = base + page * page_stride + (p0 & (page_size - 1)) * HD;
+          __nv_bfloat16* dst = ring + static_cast<size_t>(slot) * SLOT + lane * run_rows * HD;
+          // Self-check: both copies lie inside the cache.  One that does not is reported and replaced
+          // by a copy from the null page.
+          const long long src_off = src - a.kv_cache, cache_elems = static_cast<long long>(a.num_pages) * page_stride;
+          if (src_off < 0 || src_off + v_offset + run_rows * HD > cache_elems) {
+            report(a.status, STATUS_INTERNAL_CHECK, static_cast<int>(src_off >> 10), it.row);
+            src = base;
+          }
+          bulk_copy_g2s(dst, src, run_rows * ROW_BYTES, &full[slot]);
+          bulk_copy_g2s(dst + DEC_TILE * HD, src + v_offset, run_rows * ROW_BYTES, &full[slot]);
+        }
+        const unsigned copied_runs = __popc(__ballot_sync(0xffffffffu, copies));
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], copied_runs * run_rows * 2u * ROW_BYTES);
+      }
+      __syncwarp();            // every lane is done with this item's page ids before the next item's overwrite them
     }
-  };
-
-#pragma unroll
-  for (int t = 0; t < DEC_STAGES - 1; ++t)
-    if (t < n_tiles) load_tile(t, lookup(t));
-  int next_page = lookup(DEC_STAGES - 1);
-
-  // The group's queries as the A operand (heads on the 16 rows; rows past the group are zero).
-  unsigned qa[HD / 16][4];
-  {
-    const __nv_bfloat16* qrow = a.q + (static_cast<size_t>(a.row_q_start[row]) * a.nh + static_cast<size_t>(kvh) * g) * HD;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-      const int c = ks * 16 + quad_col;
-      const unsigned* lo_row = reinterpret_cast<const unsigned*>(qrow + static_cast<size_t>(quad_row) * HD + c);
-      const unsigned* hi_row = reinterpret_cast<const unsigned*>(qrow + static_cast<size_t>(quad_row + 8) * HD + c);
-      qa[ks][0] = quad_row < g ? lo_row[0] : 0u;
-      qa[ks][1] = quad_row + 8 < g ? hi_row[0] : 0u;
-      qa[ks][2] = quad_row < g ? lo_row[4] : 0u;       // columns + 8
-      qa[ks][3] = quad_row + 8 < g ? hi_row[4] : 0u;
-    }
+    return;
   }
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  float o[HD / 8][4];
-#pragma unroll
-  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-
-  for (int t = 0; t < n_tiles; ++t) {
-    const bool landed = mbar_wait(&bars[t % DEC_STAGES], (t / DEC_STAGES) & 1, DEC_WAIT_LIMIT);
-    // All threads agree (and all are done with tile t-1, whose stage the next load reuses).
-    if (!__syncthreads_and(landed)) {
-      if (threadIdx.x == 0) report(a.status, STATUS_COPY_TIMEOUT, t, row);
-      // Give copies still in flight one more bounded chance to land before this CTA's shared memory goes away.
-      for (int st = 0; st < DEC_STAGES; ++st) mbar_wait(&bars[st], ((t + st) / DEC_STAGES) & 1, 1 << 16);
-      return;
+  // ---------------------------------------------------------------------------- the consumers
+  const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
+  const int ctid = threadIdx.x;                       // 0..127 among the consumers
+  int tile_base = 0, item_seq = 0;
+  for (int id = blockIdx.x; id < n_items; id += gridDim.x) {
+    DecodeItem it;
+    if (!decode_item(a, id, it)) {
+      if (ctid == 0 && (it.row < 0 || it.row >= a.num_rows)) report(a.status, STATUS_ROW_OUT_OF_RANGE, it.row, it.r);
+      continue;
     }
-    fence_proxy_async();
-    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, next_page);
-    next_page = lookup(t + DEC_STAGES);
-
-    const __nv_bfloat16* ks = tiles + (t % DEC_STAGES) * STAGE;
-    const __nv_bfloat16* vs = ks + DEC_TILE * KROW;
-    const int key0 = first_tile + t * DEC_TILE + warp * 16;   // this warp's 16 keys
-    if (key0 >= end || key0 + 16 <= begin) continue;          // uniform over the warp
-
-    // Scores: two n-tiles of 8 keys.  Four independent accumulator chains (n-tile x k-step parity)
-    // instead of two keep the tensor core busy while a product is in flight.
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const int qb = item_seq & 1;
+    // A consumer whose wait runs out reports, raises the abort flag and keeps walking the items
+    // without computing: the consumer barriers below need all four warps to the very end.
+    if (!wait(&qfull[qb], (item_seq >> 1) & 1)) {
+      if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, -3, it.row);
+      abort_flag = 1;
+    }
+    ++item_seq;
+    // The group's queries as the A operand (heads on the 16 rows; rows past the group are zero).
+    unsigned qa[HD / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < HD / 32; ++kk) {
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ldmatrix_x4(qa[ks], qbuf + (qb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + ks * 16 + (lane >> 4) * 8);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&qempty[qb]);
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        unsigned b[4];
-        ldmatrix_x4(b, ks + (warp * 16 + nt * 8 + (lane & 7)) * KROW + kk * 32 + (lane >> 3) * 8);
-        mma_bf16_16816(s[nt], qa[2 * kk], b[0], b[1]);
-        mma_bf16_16816(s_odd[nt], qa[2 * kk + 1], b[2], b[3]);
+    for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+    for (int j = warp; j < it.n_tiles; j += DEC_CONSUMERS) {
+      const int seq = tile_base + j, slot = seq % R;
+      if (abort_flag || !wait(&full[slot], (seq / R) & 1)) {
+        if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, j, it.row);
+        abort_flag = 1;
+        break;
       }
-    }
+      __nv_bfloat16* ks_tile = ring + static_cast<size_t>(slot) * SLOT;
+      __nv_bfloat16* vs_tile = ks_tile + DEC_TILE * HD;
+      const int key0 = it.first_tile + j * DEC_TILE;
+      if (key0 < it.begin || key0 + DEC_TILE > it.end) {
+        // The tile reaches past the item: those rows came along with their page and may hold
+        // anything (another request's old values, NaN).  Their scores are masked below; their value
+        // rows are cleared so that a probability of zero times such a row stays zero.
+        const int pos = key0 + lane;
+        if (pos < it.begin || pos >= it.end) {
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) s[nt][c] += s_odd[nt][c];
-
-    // Mask, running maximum, probabilities.
-    float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int pos = key0 + nt * 8 + quad_col + (c & 1);
-        const bool valid = pos >= begin && pos < end;
-        s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
-        tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
+          for (int c = 0; c < CHUNKS; ++c) *reinterpret_cast<uint4*>(vs_tile + lane * HD + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
       }
+      const int swz = kv_swizzle(lane & 7, CHUNKS);      // a tile starts at a multiple of 32: row bits = lane bits
+
+      // Scores of the tile's 32 keys: four n-tiles of 8, each its own accumulator chain.
+      float s[DEC_TILE / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 32; ++kk) {
+          unsigned b[4];
+          ldmatrix_x4(b, ks_tile + (nt * 8 + (lane & 7)) * HD + (((kk * 4 + (lane >> 3)) ^ swz) << 3));
+          mma_bf16_16816(s[nt], qa[2 * kk], b[0], b[1]);
+          mma_bf16_16816(s[nt], qa[2 * kk + 1], b[2], b[3]);
+        }
+      }
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int pos = key0 + nt * 8 + quad_col + (c & 1);
+          const bool valid = pos >= it.begin && pos < it.end;
+          s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
+          tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
+        }
+      }
+      float corr[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+        const float new_m = fmaxf(m_run[h], tile_max[h]);     // finite: every tile of an item holds a wanted key
+        corr[h] = exp2f(m_run[h] - new_m);
+        m_run[h] = new_m;
+      }
+      float row_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          s[nt][c] = exp2f(s[nt][c] - m_run[c >> 1]);          // exp2(-inf) = 0 for masked keys
+          row_sum[c >> 1] += s[nt][c];
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+        row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+        l_run[h] = l_run[h] * corr[h] + row_sum[h];
+      }
+      // Once the running maximum has settled, corr is exactly 1 for every row and nothing is rescaled.
+      if (!__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f)) {
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+          o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
+      }
+#pragma unroll
+      for (int ks = 0; ks < DEC_TILE / 16; ++ks) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+        pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+        pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+        pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < HD / 16; ++n2) {
+          unsigned b[4];
+          ldmatrix_x4_trans(b, vs_tile + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HD +
+                                   (((n2 * 2 + (lane >> 4)) ^ swz) << 3));
+          mma_bf16_16816(o[2 * n2], pa, b[0], b[1]);
+          mma_bf16_16816(o[2 * n2 + 1], pa, b[2], b[3]);
+        }
+      }
+      __syncwarp();            // every lane has read the tile
+      if (lane == 0) mbar_arrive(&empty[slot]);
     }
-    float corr[2];
+    tile_base += it.n_tiles;
+
+    // Merge the four consumers (each saw its own tiles).  Only the group's rows are kept.
+    consumer_barrier();        // the merge buffers of the previous item are no longer read
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
-      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
-      const float new_m = fmaxf(m_run[h], tile_max[h]);       // finite: the warp's keys hold a visible one
-      corr[h] = exp2f(m_run[h] - new_m);
-      m_run[h] = new_m;
-    }
-    float row_sum[2] = {0.0f, 0.0f};
+      const int head = quad_row + 8 * h;
+      if (head < g) {
+        float* dst = merge_o + (warp * g + head) * HD + quad_col;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        s[nt][c] = exp2f(s[nt][c] - m_run[c >> 1]);          // exp2(-inf) = 0 for masked keys
-        row_sum[c >> 1] += s[nt][c];
+        for (int n = 0; n < HD / 8; ++n) {
+          dst[n * 8] = o[n][2 * h];
+          dst[n * 8 + 1] = o[n][2 * h + 1];
+        }
+        if ((lane & 3) == 0) {
+          merge_ml[(warp * g + head) * 2] = m_run[h];
+          merge_ml[(warp * g + head) * 2 + 1] = l_run[h];
+        }
       }
     }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
-      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
-      l_run[h] = l_run[h] * corr[h] + row_sum[h];
-    }
-    unsigned pa[4];
-    pa[0] = pack_bf16(s[0][0], s[0][1]);
-    pa[1] = pack_bf16(s[0][2], s[0][3]);
-    pa[2] = pack_bf16(s[1][0], s[1][1]);
-    pa[3] = pack_bf16(s[1][2], s[1][3]);
+    consumer_barrier();
 
-    // O = O * corr + P V over this warp's 16 keys.  Once the running maximum has settled, corr is
-    // exactly 1 for every row of the warp and the rescaling is skipped.
-    if (!__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f)) {
+    const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
+    const int first_split = lo / a.split_size, last_split = (it.ctx_total - 1) / a.split_size;
+    const bool alone = first_split == last_split;
+    const size_t out_base = (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g) * HD;
+    for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
+      const int h = e / HD, d = e - h * HD;
+      float mx = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < HD / 8; ++n) {
-        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      for (int w = 0; w < DEC_CONSUMERS; ++w) mx = fmaxf(mx, merge_ml[(w * g + h) * 2]);
+      float acc = 0.0f, l = 0.0f;
+#pragma unroll
+      for (int w = 0; w < DEC_CONSUMERS; ++w) {
+        const float mw = merge_ml[(w * g + h) * 2];
+        const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mx);    // a consumer without a tile of this item
+        acc += merge_o[(w * g + h) * HD + d] * f;
+        l += merge_ml[(w * g + h) * 2 + 1] * f;
+      }
+      if (alone) {               // the only split of its row: this is the result
+        a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+      } else {
+        const size_t slot = (static_cast<size_t>(it.r) * a.nh + static_cast<size_t>(it.kvh) * g + h) * a.max_splits + it.split;
+        a.part_o[slot * HD + d] = acc;
+        if (d == 0) {
+          a.part_ml[slot * 2] = mx;
+          a.part_ml[slot * 2 + 1] = l;
+        }
       }
     }
-#pragma unroll
-    for (int n2 = 0; n2 < HD / 16; ++n2) {
-      unsigned b[4];
-      ldmatrix_x4_trans(b, vs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8);
-      mma_bf16_16816(o[2 * n2], pa, b[0], b[1]);
-      mma_bf16_16816(o[2 * n2 + 1], pa, b[2], b[3]);
+    if (alone) continue;
+
+    // Whoever arrives last finds every split's partial result written and merges them.
+    __threadfence();
+    consumer_barrier();
+    if (ctid == 0) {
+      const int arrived = atomicAdd(&a.counters[it.r * a.nkv + it.kvh], 1);
+      is_last = arrived == last_split - first_split;
     }
-  }
-  __syncthreads();              // every warp is done with the tiles (all copies have landed); reuse them
-
-  // Merge the four warps (each saw its own keys).
-  float* merge_o = reinterpret_cast<float*>(smem_raw);               // [DEC_WARPS][16][HD]
-  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                   // [DEC_WARPS][16][2]
-#pragma unroll
-  for (int n = 0; n < HD / 8; ++n) {
-    float* base = merge_o + (warp * 16 + quad_row) * HD + n * 8 + quad_col;
-    base[0] = o[n][0]; base[1] = o[n][1];
-    base[8 * HD] = o[n][2]; base[8 * HD + 1] = o[n][3];
-  }
-  if ((lane & 3) == 0) {
-    merge_ml[(warp * 16 + quad_row) * 2] = m_run[0];
-    merge_ml[(warp * 16 + quad_row) * 2 + 1] = l_run[0];
-    merge_ml[(warp * 16 + quad_row + 8) * 2] = m_run[1];
-    merge_ml[(warp * 16 + quad_row + 8) * 2 + 1] = l_run[1];
-  }
-  __syncthreads();
-
-  // How many splits of this row hold keys (the others returned at the top).
-  const int lo = a.window > 0 ? max(0, ctx_total - a.window) : 0;
-  const int first_split = lo / a.split_size, last_split = (ctx_total - 1) / a.split_size;
-  const bool alone = first_split == last_split;
-  const size_t out_base = (static_cast<size_t>(a.row_q_start[row]) * a.nh + static_cast<size_t>(kvh) * g) * HD;
-
-  for (int e = threadIdx.x; e < g * HD; e += DEC_WARPS * 32) {
-    const int h = e / HD, d = e - h * HD;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, merge_ml[(w * 16 + h) * 2]);
-    float acc = 0.0f, l = 0.0f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
-      const float mw = merge_ml[(w * 16 + h) * 2];
-      const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mx);
-      acc += merge_o[(w * 16 + h) * HD + d] * f;
-      l += merge_ml[(w * 16 + h) * 2 + 1] * f;
-    }
-    if (alone) {                 // the only split of its row: this is the result
+    consumer_barrier();
+    if (!is_last) continue;
+    __threadfence();
+    for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
+      const int h = e / HD, d = e - h * HD;
+      const size_t base = (static_cast<size_t>(it.r) * a.nh + static_cast<size_t>(it.kvh) * g + h) * a.max_splits;
+      float mx = -INFINITY;
+      for (int sp = first_split; sp <= last_split; ++sp) mx = fmaxf(mx, __ldcg(&a.part_ml[(base + sp) * 2]));
+      float acc = 0.0f, l = 0.0f;
+      for (int sp = first_split; sp <= last_split; ++sp) {
+        const float f = exp2f(__ldcg(&a.part_ml[(base + sp) * 2]) - mx);
+        acc += __ldcg(&a.part_o[(base + sp) * HD + d]) * f;
+        l += __ldcg(&a.part_ml[(base + sp) * 2 + 1]) * f;
+      }
       a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
-    } else {
-      const size_t slot = (static_cast<size_t>(r) * a.nh + static_cast<size_t>(kvh) * g + h) * a.max_splits + split;
-      a.part_o[slot * HD + d] = acc;
-      if (d == 0) {
-        a.part_ml[slot * 2] = mx;
-        a.part_ml[slot * 2 + 1] = l;
-      }
     }
+    if (ctid == 0) a.counters[it.r * a.nkv + it.kvh] = 0;    // left as it was found, for the next call
   }
-  if (alone) return;
-
-  // Whoever arrives last finds every split's partial result written and merges them.
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int arrived = atomicAdd(&a.counters[r * a.nkv + kvh], 1);
-    is_last = arrived == last_split - first_split;
+  if (abort_flag) {
+    // Something went wrong.  Give copies that are still in flight a bounded chance to land before
+    // this CTA's shared memory is handed to another.
+    for (int s = warp; s < R; s += DEC_CONSUMERS)
+      for (int i = 0; i < (1 << 14) && !mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1); ++i) {}
   }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int e = threadIdx.x; e < g * HD; e += DEC_WARPS * 32) {
-    const int h = e / HD, d = e - h * HD;
-    const size_t base = (static_cast<size_t>(r) * a.nh + static_cast<size_t>(kvh) * g + h) * a.max_splits;
-    float mx = -INFINITY;
-    for (int sp = first_split; sp <= last_split; ++sp) mx = fmaxf(mx, __ldcg(&a.part_ml[(base + sp) * 2]));
-    float acc = 0.0f, l = 0.0f;
-    for (int sp = first_split; sp <= last_split; ++sp) {
-      const float f = exp2f(__ldcg(&a.part_ml[(base + sp) * 2]) - mx);
-      acc += __ldcg(&a.part_o[(base + sp) * HD + d]) * f;
-      l += __ldcg(&a.part_ml[(base + sp) * 2 + 1]) * f;
-    }
-    a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
-  }
-  if (threadIdx.x == 0) a.counters[r * a.nkv + kvh] = 0;      // left as it was found, for the next call
 }
 
-template <int HD> size_t decode_smem_bytes() {
-  const size_t ring = static_cast<size_t>(DEC_STAGES) * 2 * DEC_TILE * (HD + 8) * sizeof(__nv_bfloat16) +
-                      DEC_STAGES * sizeof(unsigned long long);
-  const size_t merge = static_cast<size_t>(DEC_WARPS) * 16 * (HD + 2) * sizeof(float);
-  return ring > merge ? ring : merge;
+// Shared memory of one CTA with `slots` ring slots, and the most slots that fit.
+template <int HD> size_t decode_smem_bytes(int slots, int g, int item_pages) {
+  return static_cast<size_t>(item_pages) * sizeof(int)                                     // the item's page ids
+         + static_cast<size_t>(slots) * 2 * DEC_TILE * HD * sizeof(__nv_bfloat16)         // ring
+         + 2 * 16 * (HD + 8) * sizeof(__nv_bfloat16)                                       // queries, two items
+         + static_cast<size_t>(DEC_CONSUMERS) * g * (HD + 2) * sizeof(float)               // merge buffers
+         + (2 * static_cast<size_t>(slots) + 4) * sizeof(unsigned long long);              // barriers
 }
 
 template <int HD>
-int decode_launch(const DecodeArgs& a, int n_rows, cudaStream_t stream) {
-  const size_t smem = decode_smem_bytes<HD>();
-  auto kernel = paged_decode_split_kernel<HD>;
+int decode_launch(DecodeArgs& a, cudaStream_t stream) {
+  const int g = a.nh / a.nkv;
+  const int item_pages = ((a.split_size + DEC_TILE) >> a.page_shift) + 2;
+  if (decode_smem_bytes<HD>(2, g, item_pages) > static_cast<size_t>(DEC_SMEM_BUDGET)) return ERR_UNSUPPORTED;
+  int slots = 2;
+  while (decode_smem_bytes<HD>(slots + 1, g, item_pages) <= static_cast<size_t>(DEC_SMEM_BUDGET)) ++slots;
+  a.ring_slots = slots;
+  const size_t smem = decode_smem_bytes<HD>(slots, g, item_pages);
+  auto kernel = paged_decode_kernel<HD>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<dim3(a.max_splits, a.nkv, n_rows), DEC_WARPS * 32, smem, stream>>>(a);
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    return ERR_CUDA;
+  const long long items = static_cast<long long>(a.n_rows) * a.nkv * a.max_splits;
+  const int grid = static_cast<int>(items < sms ? items : sms);     // one persistent CTA per SM
+  kernel<<<grid, DEC_THREADS, smem, stream>>>(a);
   return launch_result();
 }
 
@@ -359,7 +465,7 @@ ZB_API long long zb_paged_decode_scratch_floats(int n_rows, int nh, int hd, int 
 // Attention of `n_rows` single new tokens over their paged context.  `scratch` holds
 // zb_paged_decode_scratch_floats(...) floats (contents irrelevant); `counters` holds n_rows * nkv
 // ints that are zero on entry and are left zero.  max_splits >= ceil((longest context + 1) /
-// split_size); split_size is a multiple of 64; page_size is a power of two.
+// split_size); split_size is a multiple of 32; page_size is a power of two.
 ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
                            int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
                            const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
@@ -370,7 +476,7 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_decode_supported(nh, nkv, hd, DTYPE_BF16) || (page_size & (page_size - 1)) != 0) return ERR_UNSUPPORTED;
   if (n_rows == 0) return OK;
-  if (n_rows > 65535 || nkv > 65535) return ERR_UNSUPPORTED;
+  if (static_cast<long long>(n_rows) * nkv * max_splits > 0x7fffffffLL) return ERR_UNSUPPORTED;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   DecodeArgs a;
@@ -382,15 +488,17 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
   a.part_ml = scratch + static_cast<size_t>(n_rows) * nh * max_splits * hd;
   a.counters = counters;
   a.max_blocks = max_blocks; a.page_shift = page_shift; a.num_pages = num_pages; a.num_rows = num_rows;
+  a.n_rows = n_rows;
   a.nh = nh; a.nkv = nkv; a.window = window; a.split_size = split_size; a.max_splits = max_splits;
+  a.ring_slots = 0;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   switch (hd) {
-    case 32: return decode_launch<32>(a, n_rows, s);
-    case 64: return decode_launch<64>(a, n_rows, s);
-    case 96: return decode_launch<96>(a, n_rows, s);
-    default: return decode_launch<128>(a, n_rows, s);
+    case 32: return decode_launch<32>(a, s);
+    case 64: return decode_launch<64>(a, s);
+    case 96: return decode_launch<96>(a, s);
+    default: return decode_launch<128>(a, s);
   }
 }
 

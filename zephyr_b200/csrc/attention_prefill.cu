@@ -88,7 +88,9 @@ paged_prefill_kernel(const PrefillArgs a) {
           report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
           ok = false;
         } else {
-          src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD + c;
+          // logical chunk c / 8 of the row sits at the permuted chunk (common.cuh: kv_swizzle)
+          src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD +
+                 (((c >> 3) ^ kv_swizzle(pos, CHUNKS)) << 3);
         }
       }
       cp_async_16(ks + j * KROW + c, src, ok);

@@ -103,7 +103,9 @@ paged_attention_simt_kernel(const AttentionArgs a) {
           report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
           ok = false;
         } else {
-          base = ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd + d;
+          // logical chunk d / vec of the row sits at the permuted chunk (common.cuh: kv_swizzle)
+          base = ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd +
+                 (((d / vec) ^ kv_swizzle(pos, chunks_per_row)) * vec);
         }
       }
       // Positions outside [lo, hi) hold zeros: a page that was given back, or one that another

@@ -27,6 +27,7 @@ constexpr int STATUS_PAGE_OUT_OF_RANGE = 3;
 constexpr int STATUS_ROW_OUT_OF_RANGE = 4;
 constexpr int STATUS_BAD_LOGIT = 5;
 constexpr int STATUS_COPY_TIMEOUT = 6;    // an asynchronous copy did not complete within the wait limit
+constexpr int STATUS_INTERNAL_CHECK = 7;  // a kernel's own check of an address or size failed
 
 __device__ __forceinline__ void report(int* status, int code, int detail, int index) {
   if (status != nullptr && atomicCAS(status, STATUS_OK, code) == STATUS_OK) {
@@ -76,6 +77,28 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// ---- The cache's row layout ------------------------------------------------------------------------
+// A cache row (the head_dim values of one position and head) is stored with its 16-byte chunks
+// permuted: logical chunk c of the row at position `pos` lives at chunk c ^ kv_swizzle(pos, chunks).
+// The permutation is chosen so that a page copied to shared memory as it is, rows back to back
+// with no padding (one bulk copy), can be read by ldmatrix without bank conflicts: eight
+// consecutive rows at the same logical chunk then fall into eight different 16-byte bank groups.
+// `chunks` = row bytes / 16.  The permutation only swaps chunks inside aligned groups of 8, 4 or 2,
+// so it stays inside the row for every head size that is a multiple of 16 bytes.
+__host__ __device__ __forceinline__ int kv_swizzle(int pos, int chunks) {
+  const int step = chunks & 7;                 // bank-group stride between consecutive rows
+  if (step == 0) return pos & 7;
+  if (step == 4) return (pos >> 1) & 3;
+  if (step == 2 || step == 6) return (pos >> 2) & 1;
+  return 0;                                    // odd strides are conflict-free as they are
+}
+// Index of logical element `i` of a row inside the stored row, for elements of `elem_bytes` bytes.
+__host__ __device__ __forceinline__ int kv_element_index(int i, int pos, int head_dim, int elem_bytes) {
+  const int per_chunk = 16 / elem_bytes;
+  const int chunk = i / per_chunk;
+  return ((chunk ^ kv_swizzle(pos, head_dim * elem_bytes / 16)) * per_chunk) + (i - chunk * per_chunk);
 }
 
 inline int launch_result() {

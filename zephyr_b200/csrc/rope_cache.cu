@@ -10,7 +10,8 @@
 // rounds to the storage type after the norm and after each product of the rotation, everything
 // here is float32 until the single store.
 //
-// Cache layout of one cache: [num_pages][2 (k, v)][num_kv_heads][page_size][head_dim].
+// Cache layout of one cache: [num_pages][2 (k, v)][num_kv_heads][page_size][head_dim], each row with
+// its 16-byte chunks permuted by kv_swizzle(position) (common.cuh).
 #include "common.cuh"
 
 namespace zb {
@@ -114,12 +115,15 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
       }
     }
   }
+  // q goes out as it is; cache rows are stored with their 16-byte chunks permuted (kv_swizzle).
 #pragma unroll
   for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
     const int i = lane + 32 * k;
     if (i < half) {
-      dst[i] = from_float<T>(x[k]);
-      dst[i + half] = from_float<T>(y[k]);
+      const int lo = is_q ? i : kv_element_index(i, pos, hd, sizeof(T));
+      const int hi = is_q ? i + half : kv_element_index(i + half, pos, hd, sizeof(T));
+      dst[lo] = from_float<T>(x[k]);
+      dst[hi] = from_float<T>(y[k]);
     }
   }
 }
@@ -162,7 +166,7 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
       const T* src = (sel == 0 ? k + static_cast<size_t>(t) * k_stride : v + static_cast<size_t>(t) * v_stride) +
                      static_cast<size_t>(kvh) * hd;
       T* dst = static_cast<T*>(cache.base) + off;
-      for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+      for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[kv_element_index(i, pos, hd, sizeof(T))] = src[i];
     }
   }
 }

@@ -29,6 +29,7 @@ STATUS_TEXT = {
     4: "a request row or block index outside the step's tables",
     5: "NaN or +inf among the logits",
     6: "an asynchronous copy into shared memory that did not complete within the wait limit",
+    7: "an address or size that failed a kernel's own check (a bug in this package)",
 }
 
 
@@ -235,6 +236,30 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bo
 
 
 # ------------------------------------------------------------------ position and cache
+def kv_swizzle(pos: int, chunks: int) -> int:
+    """By how much the 16-byte chunks of the cache row at position ``pos`` are permuted: logical chunk
+    c lives at chunk ``c ^ kv_swizzle(pos, chunks)``, with ``chunks`` = row bytes / 16.  (The same
+    function as in csrc/common.cuh; tools and tests that read or fill a cache by hand need it.)"""
+    step = chunks & 7
+    if step == 0:
+        return pos & 7
+    if step == 4:
+        return (pos >> 1) & 3
+    if step in (2, 6):
+        return (pos >> 2) & 1
+    return 0
+
+
+def kv_row_permutation(pos: int, head_dim: int, dtype: torch.dtype) -> torch.Tensor:
+    """``perm`` with ``stored_row[perm[i]] == logical_row[i]`` for the cache row at position ``pos``."""
+    size = torch.empty((), dtype=dtype).element_size()
+    per_chunk = 16 // size
+    chunks = head_dim * size // 16
+    index = torch.arange(head_dim)
+    return ((index // per_chunk) ^ kv_swizzle(pos, chunks)) * per_chunk + index % per_chunk
+
+
+
 def _check_cache(kv_cache: torch.Tensor, nkv: int, hd: int, dtype: torch.dtype) -> tuple[int, int]:
     _require(kv_cache.dim() == 5 and kv_cache.is_contiguous() and kv_cache.shape[1] == 2
              and kv_cache.shape[2] == nkv and kv_cache.shape[4] == hd and kv_cache.dtype == dtype,
@@ -361,13 +386,24 @@ def _decode_workspace(device: torch.device, floats: int, counters: int) -> tuple
 
 
 def decode_split_size(n_rows: int, nkv: int, max_context: int) -> int:
-    """Positions per split: as long as possible (fewer partial results to merge, less start-up cost
-    per CTA) while the grid still fills the GPU.  It depends on the batch, so the split points of a
-    row, and with them the last bits of its result, depend on what else is decoded beside it."""
+    """Positions per work item of the decode kernel.  Long items cost less per position (one merge
+    and one partial result per item); short ones spread a small batch over all SMs.  The size
+    depends on the batch, so the split points of a row, and with them the last bits of its
+    result, depend on what else is decoded beside it."""
     split = 1024
-    while split > 128 and n_rows * nkv * math.ceil(max_context / split) < 256:
+    while split > 128 and n_rows * nkv * math.ceil(max_context / split) < _sm_count() - 20:
         split //= 2
     return split
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    device = torch.cuda.current_device()
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[device]
 
 
 def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
