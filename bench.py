@@ -296,11 +296,93 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
-    """The unmodified reference, installed under baseline/_ref, through its own Python API."""
+    """The unmodified reference, installed under baseline/_ref, through its own public Python API
+    (``zephyr.Engine(EngineOptions).execute([GenerationRequest ...])``) on the same shape: seeded
+    random weights written to a model folder, seeded random prompts.  Its API returns tokens only when
+    requests finish, so decode time is taken as the difference of two runs on prompts of the same
+    lengths (fresh random ids each, so that its prefix cache cannot help): one that generates a
+    single token per sequence, and one that generates ``steps`` more."""
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "zephyr").is_dir():
         return {"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (zephyr) package"}
-    return {"impl": "reference", "unavailable": "reference arm not wired up yet"}
+    import tempfile
+
+    import torch
+
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    sys.path.insert(0, str(ref))
+    try:
+        import zephyr
+        from zephyr import _C
+    except Exception as error:      # the reference's own import chain (tokenizer front end, native module)
+        return {"impl": "reference", "unavailable": f"cannot import the installed reference: {type(error).__name__}: {error}"[:300]}
+
+    from zephyr_b200 import Qwen3Config, write_random_model
+
+    sizes = dict(SHAPES[args.shape])
+    full_layers = sizes["num_hidden_layers"]
+    if args.layers:
+        sizes["num_hidden_layers"] = args.layers
+    config = Qwen3Config(max_position_embeddings=max(args.context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0,
+                         layer_windows=tuple(0 for _ in range(sizes["num_hidden_layers"])), **sizes)
+    rng = random.Random(77)
+    steps, batch = args.steps, args.batch
+    start = args.context - steps - 1
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(config, 0, folder, dtype=torch.bfloat16)
+        try:
+            options = _C.EngineOptions(folder, devices=[0], dtype="bfloat16", max_seq_len=args.context,
+                                       scheduler=_C.PagedSchedulerConfig(max_num_seqs=batch,
+                                                                         max_num_batched_tokens=PREFILL_TOKENS,
+                                                                         max_prefill_chunk_tokens=PREFILL_TOKENS),
+                                       eos_token_ids=[])
+            engine = zephyr.Engine(options, kv_cache=_C.KvCacheOptions(block_size=PAGE_SIZE))
+        except Exception as error:
+            return {"impl": "reference", "unavailable": f"the reference engine did not start: {type(error).__name__}: {error}"[:300]}
+
+        def run(new_tokens: int, count: int, length: int) -> float:
+            requests = [_C.GenerationRequest([rng.randrange(config.vocab_size) for _ in range(length)],
+                                             sampling=_C.SamplingParams(temperature=0.0), max_new_tokens=new_tokens,
+                                             ignore_eos=True) for _ in range(count)]
+            torch.cuda.synchronize()
+            began = time.perf_counter()
+            outputs = engine.execute(requests)
+            seconds = time.perf_counter() - began
+            assert all(len(o.result[0].tokens) == new_tokens for o in outputs)
+            return seconds
+
+        clock = ClockSampler()
+        try:
+            for _ in range(max(1, args.warmup // 3)):
+                run(2, batch, start)
+            clock.start()
+            short = run(1, batch, start)
+            long = run(steps + 1, batch, start)
+            clocks = clock.stop()
+            prefill_runs = [run(1, 1, PREFILL_TOKENS) for _ in range(4)]
+        except Exception as error:
+            clock.stop()
+            return {"impl": "reference", "unavailable": f"the reference failed while generating: {type(error).__name__}: {error}"[:300]}
+        finally:
+            engine.close()
+    decode_seconds = max(long - short, 1e-9)
+    value = batch * steps / decode_seconds
+    prefill_ms = statistics.median(prefill_runs[1:]) * 1e3
+    return {
+        "metric": f"decode tok/s @ batch {batch}, context {args.context} ({args.shape})", "value": round(value, 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": round(decode_seconds / steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "impl": "reference",
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "global_batch": batch, "seq_len": args.context,
+                   "parallelism": "single GPU", "layers": config.num_hidden_layers, "layers_full": full_layers,
+                   "kv_page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
+                   "timing": "wall clock of Engine.execute; decode = (steps+1)-token run minus 1-token run"},
+        "e2e": {"value": round(value, 1), "unit": "tok/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+        "clocks": clocks,
+        "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)},
+    }
 
 
 def main() -> int:

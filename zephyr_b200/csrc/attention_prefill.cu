@@ -47,7 +47,10 @@ paged_prefill_kernel(const PrefillArgs a) {
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [PRE_BM][KROW]
   __nv_bfloat16* ring = q_s + PRE_BM * KROW;                             // [2][keys, values][PRE_BN][KROW]
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // The tile list runs through each request's new tokens front to back, and under the causal mask
+  // later tiles have more keys to visit: take the list back to front, the long tiles first, so
+  // that the short ones fill the gaps at the end instead of the other way round.
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);

@@ -43,6 +43,31 @@ __device__ __forceinline__ long long cache_row_offset(const CacheView& c, int ro
   return (((static_cast<long long>(page) * 2 + kv_sel) * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
 }
 
+// Two adjacent elements as one load or store.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  using type = float2;
+  static __device__ __forceinline__ void load(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+  }
+};
+template <> struct Pair<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float& a, float& b) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+};
+
+// One warp per (token, head).  Lane l of pass k owns the adjacent elements 2(l + 32k), +1 of the
+// first half of the head and their partners in the second half (the rotation pairs i, i + hd/2).
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, long long qkv_stride,
                                           const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
@@ -50,6 +75,7 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
                                           const float* __restrict__ sin_table, int max_positions,
                                           const int* __restrict__ positions, const int* __restrict__ token_row,
                                           CacheView cache, int nh, int nkv, int hd, int* status) {
+  constexpr int PASSES = MAX_PAIRS_PER_LANE / 2;      // 64 elements of a half per pass: head sizes up to 256
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5);
@@ -60,16 +86,16 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
   const T* src = qkv + static_cast<size_t>(t) * qkv_stride + static_cast<size_t>(head) * hd;
 
-  float x[MAX_PAIRS_PER_LANE], y[MAX_PAIRS_PER_LANE];
+  float x[PASSES][2], y[PASSES][2];
   float ss = 0.0f;
 #pragma unroll
-  for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
-    const int i = lane + 32 * k;
-    x[k] = y[k] = 0.0f;
+  for (int k = 0; k < PASSES; ++k) {
+    const int i = 2 * (lane + 32 * k);
+    x[k][0] = x[k][1] = y[k][0] = y[k][1] = 0.0f;
     if (i < half) {
-      x[k] = to_float(src[i]);
-      y[k] = to_float(src[i + half]);
-      ss += x[k] * x[k] + y[k] * y[k];
+      Pair<T>::load(src + i, x[k][0], x[k][1]);
+      Pair<T>::load(src + i + half, y[k][0], y[k][1]);
+      ss += x[k][0] * x[k][0] + x[k][1] * x[k][1] + y[k][0] * y[k][0] + y[k][1] * y[k][1];
     }
   }
 
@@ -88,11 +114,14 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
     if (w != nullptr) {
       const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(hd) + eps);
 #pragma unroll
-      for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
-        const int i = lane + 32 * k;
+      for (int k = 0; k < PASSES; ++k) {
+        const int i = 2 * (lane + 32 * k);
         if (i < half) {
-          x[k] *= inv * load_scale(w, w_dtype, i);
-          y[k] *= inv * load_scale(w, w_dtype, i + half);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            x[k][u] *= inv * load_scale(w, w_dtype, i + u);
+            y[k][u] *= inv * load_scale(w, w_dtype, i + u + half);
+          }
         }
       }
     }
@@ -104,26 +133,32 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
       const float* c = cos_table + static_cast<size_t>(pos) * half;
       const float* s = sin_table + static_cast<size_t>(pos) * half;
 #pragma unroll
-      for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
-        const int i = lane + 32 * k;
+      for (int k = 0; k < PASSES; ++k) {
+        const int i = 2 * (lane + 32 * k);
         if (i < half) {
-          const float xr = x[k] * c[i] - y[k] * s[i];
-          const float yr = y[k] * c[i] + x[k] * s[i];
-          x[k] = xr;
-          y[k] = yr;
+          const float2 cv = *reinterpret_cast<const float2*>(c + i), sv = *reinterpret_cast<const float2*>(s + i);
+          const float cs[2] = {cv.x, cv.y}, sn[2] = {sv.x, sv.y};
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float xr = x[k][u] * cs[u] - y[k][u] * sn[u];
+            const float yr = y[k][u] * cs[u] + x[k][u] * sn[u];
+            x[k][u] = xr;
+            y[k][u] = yr;
+          }
         }
       }
     }
   }
-  // q goes out as it is; cache rows are stored with their 16-byte chunks permuted (kv_swizzle).
+  // q goes out as it is; cache rows are stored with their 16-byte chunks permuted (kv_swizzle); two
+  // adjacent elements never straddle a chunk.
 #pragma unroll
-  for (int k = 0; k < MAX_PAIRS_PER_LANE; ++k) {
-    const int i = lane + 32 * k;
+  for (int k = 0; k < PASSES; ++k) {
+    const int i = 2 * (lane + 32 * k);
     if (i < half) {
       const int lo = is_q ? i : kv_element_index(i, pos, hd, sizeof(T));
       const int hi = is_q ? i + half : kv_element_index(i + half, pos, hd, sizeof(T));
-      dst[lo] = from_float<T>(x[k]);
-      dst[hi] = from_float<T>(y[k]);
+      Pair<T>::store(dst + lo, x[k][0], x[k][1]);
+      Pair<T>::store(dst + hi, y[k][0], y[k][1]);
     }
   }
 }

@@ -60,9 +60,11 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   const int per = (V + blockDim.x - 1) / blockDim.x;
   const int begin = min(V, static_cast<int>(threadIdx.x) * per), end = min(V, begin + per);
 
+  // The maximum does not care in which order the row is visited (equal maxima go to the lowest
+  // index whatever the order), so this pass strides through the row with coalesced loads.
   MaxIdx mine{0.0f, -1};
   bool bad = false;
-  for (int i = begin; i < end; ++i) {
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float v = x[i];
     if (isnan(v) || (isinf(v) && v > 0.0f)) bad = true;
     mine = better(mine, MaxIdx{v, i});
