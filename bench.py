@@ -297,11 +297,10 @@ def run_ours(args) -> dict:
 
 def run_reference(args) -> dict:
     """The unmodified reference, installed under baseline/_ref, through its own public Python API
-    (``zephyr.Engine(EngineOptions).execute([GenerationRequest ...])``) on the same shape: seeded
-    random weights written to a model folder, seeded random prompts.  Its API returns tokens only when
-    requests finish, so decode time is taken as the difference of two runs on prompts of the same
-    lengths (fresh random ids each, so that its prefix cache cannot help): one that generates a
-    single token per sequence, and one that generates ``steps`` more."""
+    (``zephyr._C.Engine``: ``submit`` / ``wait_for_outputs``) on the same shape: seeded random weights
+    written to a model folder, seeded random prompts (fresh ids for every run, so that its prefix
+    cache cannot help).  Decode throughput is counted over the token increments it publishes, from
+    the moment every sequence has produced its first token to the end of the run."""
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "zephyr").is_dir():
         return {"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (zephyr) package"}
@@ -313,7 +312,6 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": "no CUDA device"}
     sys.path.insert(0, str(ref))
     try:
-        import zephyr
         from zephyr import _C
     except Exception as error:      # the reference's own import chain (tokenizer front end, native module)
         return {"impl": "reference", "unavailable": f"cannot import the installed reference: {type(error).__name__}: {error}"[:300]}
@@ -337,48 +335,60 @@ def run_reference(args) -> dict:
                                                                          max_num_batched_tokens=PREFILL_TOKENS,
                                                                          max_prefill_chunk_tokens=PREFILL_TOKENS),
                                        eos_token_ids=[])
-            engine = zephyr.Engine(options, kv_cache=_C.KvCacheOptions(block_size=PAGE_SIZE))
         except Exception as error:
             return {"impl": "reference", "unavailable": f"the reference engine did not start: {type(error).__name__}: {error}"[:300]}
 
-        def run(new_tokens: int, count: int, length: int) -> float:
+        native = _C.Engine(options, kv_cache=_C.KvCacheOptions(block_size=PAGE_SIZE))
+
+        def run(new_tokens: int, count: int, length: int):
+            """Submit ``count`` requests and follow the token increments as they come out.  Returns
+            (seconds in all, seconds from the moment every sequence has its first token to the end,
+            tokens produced in that second stretch)."""
             requests = [_C.GenerationRequest([rng.randrange(config.vocab_size) for _ in range(length)],
                                              sampling=_C.SamplingParams(temperature=0.0), max_new_tokens=new_tokens,
                                              ignore_eos=True) for _ in range(count)]
             torch.cuda.synchronize()
             began = time.perf_counter()
-            outputs = engine.execute(requests)
-            seconds = time.perf_counter() - began
-            assert all(len(o.result[0].tokens) == new_tokens for o in outputs)
-            return seconds
+            produced = {native.submit(request): 0 for request in requests}
+            finished, all_started, tokens_at_start = 0, None, 0
+            while finished < count:
+                for output in native.wait_for_outputs():
+                    produced[output.request_id] += sum(len(choice.tokens) for choice in output.result)
+                    if output.status is not None:
+                        if output.status != _C.RequestStatus.COMPLETED:
+                            raise RuntimeError(f"request ended with {output.status}: {output.error_message}")
+                        finished += 1
+                if all_started is None and all(n >= 1 for n in produced.values()):
+                    all_started, tokens_at_start = time.perf_counter(), sum(produced.values())
+            ended = time.perf_counter()
+            assert all(n == new_tokens for n in produced.values())
+            return ended - began, ended - (all_started or ended), sum(produced.values()) - tokens_at_start
 
         clock = ClockSampler()
         try:
-            for _ in range(max(1, args.warmup // 3)):
-                run(2, batch, start)
+            run(2, batch, start)
             clock.start()
-            short = run(1, batch, start)
-            long = run(steps + 1, batch, start)
+            _, decode_seconds, decode_tokens = run(steps + 1, batch, start)
             clocks = clock.stop()
-            prefill_runs = [run(1, 1, PREFILL_TOKENS) for _ in range(4)]
+            prefill_runs = [run(1, 1, PREFILL_TOKENS)[0] for _ in range(3)]
         except Exception as error:
             clock.stop()
             return {"impl": "reference", "unavailable": f"the reference failed while generating: {type(error).__name__}: {error}"[:300]}
         finally:
-            engine.close()
-    decode_seconds = max(long - short, 1e-9)
-    value = batch * steps / decode_seconds
+            native.close()
+    value = decode_tokens / max(decode_seconds, 1e-9)
+    steps_timed = max(decode_tokens / batch, 1e-9)
     prefill_ms = statistics.median(prefill_runs[1:]) * 1e3
     return {
         "metric": f"decode tok/s @ batch {batch}, context {args.context} ({args.shape})", "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
-        "ms_per_step": round(decode_seconds / steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(decode_seconds / steps_timed * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "reference",
         "config": {"model": f"Qwen3-{args.shape.upper()} shape", "global_batch": batch, "seq_len": args.context,
                    "parallelism": "single GPU", "layers": config.num_hidden_layers, "layers_full": full_layers,
                    "kv_page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-                   "timing": "wall clock of Engine.execute; decode = (steps+1)-token run minus 1-token run"},
+                   "timing": "wall clock over _C.Engine token increments, from every sequence's first token to the end"},
         "e2e": {"value": round(value, 1), "unit": "tok/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
         "clocks": clocks,
         "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)},
