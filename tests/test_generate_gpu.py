@@ -108,6 +108,78 @@ def test_workload_b_four_requests_temperature(model_folders, cuda_device):
             assert got[0] == index
 
 
+def test_filters_penalties_and_reports_match_the_plain_sampler(model_folders, cuda_device):
+    """Tiny B (float32), four requests with different sampling settings in one batch: every token is
+    the one that the plain model's logits, the plain sampler and the request's own generator give,
+    and the reported log-probabilities are those of the adjusted, scaled logits."""
+    import plain_sampler
+    from zephyr_b200 import GenerationParams
+    from zephyr_b200.sampling import MT19937_64
+
+    folder = model_folders("B", "float32")
+    config, weights = load_model_folder(folder)
+    vocab = config["vocab_size"]
+    prompts = [random_tokens(vocab, n, seed=50 + n) for n in (6, 13, 21, 4)]
+    settings = [dict(temperature=0.9, top_k=12, top_logprobs=3),
+                dict(temperature=0.7, top_p=0.85, min_p=0.01, frequency_penalty=0.5, presence_penalty=0.25),
+                dict(temperature=0.0, repetition_penalty=1.8, logit_bias={5: 4.0, 9: float("-inf")}, top_logprobs=0),
+                dict(temperature=1.1, min_p=0.05, repetition_penalty=1.3, top_logprobs=vocab)]
+    engine = make_engine(folder, "B", "float32", max_num_seqs=4, max_num_batched_tokens=32, max_prefill_chunk_tokens=8)
+    ids = [engine.add_request(p, GenerationParams(max_tokens=6, seed=7 + i, ignore_eos=True, **s))
+           for i, (p, s) in enumerate(zip(prompts, settings))]
+    while engine.has_unfinished():
+        engine.step()
+    outputs = [engine.take_output(i) for i in ids]
+    compared = 0
+    for i, (prompt, setting, output) in enumerate(zip(prompts, settings, outputs)):
+        choice = output.choices[0]
+        assert len(choice.token_ids) == 6
+        assert (choice.logprobs is None) == ("top_logprobs" not in setting)
+        generator = MT19937_64(7 + i)
+        tokens = list(prompt)
+        for step, got in enumerate(choice.token_ids):
+            logits = plain_forward(config, weights, tokens)[-1].to(torch.float32)
+            adjusted = plain_sampler.adjust(logits, tokens, len(prompt), setting.get("frequency_penalty", 0.0),
+                                            setting.get("presence_penalty", 0.0), setting.get("repetition_penalty", 1.0),
+                                            setting.get("logit_bias"))
+            temperature = setting["temperature"]
+            u = generator.next_uniform() if temperature >= 1e-7 else 0.0
+            want, margin = plain_sampler.sample(adjusted, temperature, u, setting.get("top_k", -1),
+                                                setting.get("top_p", 1.0), setting.get("min_p", 0.0))
+            if temperature < 1e-7:
+                top = torch.topk(adjusted, 2).values
+                margin = float(top[0] - top[1])
+            if margin <= 1e-4:
+                break                                   # a near tie: the sequences may fairly part here
+            assert got == want, (i, step, got, want, margin)
+            compared += 1
+            if choice.logprobs is not None:
+                count = min(setting["top_logprobs"], vocab)
+                chosen, best = plain_sampler.report(adjusted, temperature, got, count)
+                report = choice.logprobs[step]
+                assert abs(report.logprob - chosen) <= 1e-4 * max(1.0, abs(chosen))
+                assert len(report.top_logprobs) == count
+                for entry, (token, value) in zip(report.top_logprobs, best):
+                    assert abs(entry.logprob - value) <= 1e-4 * max(1.0, abs(value))
+                # Equal ranks may swap where two log-probabilities differ by less than the engine's error.
+                assert sorted(e.token_id for e in report.top_logprobs) == sorted(t for t, _ in best) or count < vocab
+            tokens.append(got)
+    assert compared >= 20
+    assert 9 not in outputs[2].choices[0].token_ids              # a bias of -inf bans the token
+
+
+def test_top_k_one_is_greedy_and_seeds_repeat(model_folders, cuda_device):
+    folder = model_folders("A", "bfloat16")
+    engine = make_engine(folder, "A", "bfloat16", max_num_seqs=2, max_num_batched_tokens=16, max_prefill_chunk_tokens=16)
+    prompt = random_tokens(256, 9, seed=3)
+    greedy = engine.generate(prompt, max_tokens=10, temperature=0.0, ignore_eos=True).token_ids
+    assert engine.generate(prompt, max_tokens=10, temperature=0.8, top_k=1, seed=1, ignore_eos=True).token_ids == greedy
+    one = engine.generate(prompt, max_tokens=10, temperature=0.9, top_p=0.9, seed=5, ignore_eos=True).token_ids
+    two = engine.generate(prompt, max_tokens=10, temperature=0.9, top_p=0.9, seed=5, ignore_eos=True).token_ids
+    other = engine.generate(prompt, max_tokens=10, temperature=0.9, top_p=0.9, seed=6, ignore_eos=True).token_ids
+    assert one == two and one != other
+
+
 def test_small_pool_preempts_and_tokens_do_not_change(model_folders, cuda_device):
     folder = model_folders("A", "float32")
     prompts = [random_tokens(256, n, seed=30 + n) for n in (10, 9, 14)]

@@ -531,7 +531,8 @@ def test_argmax_lowest_index_on_ties(ops, cuda_device):
     logits[1, 151935] = 0.5
     logits[2, 0] = 0.0
     status = ops.new_status(cuda_device)
-    assert ops.sample(logits, None, None, status).tolist() == [77, 151935, 0]
+    assert ops.sample(logits, status).tolist() == [77, 151935, 0]
+    assert ops.sample(logits, status).tolist() == [77, 151935, 0]       # the arrival counters were left at zero
     ops.check_status(status)
 
 
@@ -541,32 +542,158 @@ def test_temperature_sampling_follows_the_prefix_sums(ops, cuda_device):
     for V in (311, 5000, 151936):
         g = torch.Generator().manual_seed(V)
         logits = (torch.randn((16, V), generator=g) * 2).to(cuda_device)
-        temperature = torch.tensor([0.7, 1.0, 0.3, 1.5] * 4, device=cuda_device)
+        temperature = [0.7, 1.0, 0.3, 1.5] * 4
         temperature[5] = 0.0            # a greedy row among sampled ones
-        uniform = torch.rand(16, generator=g).to(cuda_device)
+        uniform = torch.rand(16, generator=g).tolist()
         status = ops.new_status(cuda_device)
-        got = ops.sample(logits, temperature, uniform, status).tolist()
+        rows = [ops.SampleRow(temperature=t, uniform=u) for t, u in zip(temperature, uniform)]
+        got = ops.sample_rows(logits, rows, status).ids.tolist()
         ops.check_status(status)
         for r in range(16):
             if r == 5:
                 assert got[r] == int(logits[r].argmax())
                 continue
-            index, margin = plain_sample(logits[r].cpu(), float(temperature[r]), float(uniform[r]))
+            index, margin = plain_sample(logits[r].cpu(), temperature[r], uniform[r])
             if margin > 1e-4:
                 assert got[r] == index, (V, r, got[r], index, margin)
             # Always: u * total lies in the chosen token's interval of the exact prefix sums, give or
             # take what float32 prefix sums over V terms can differ by.
-            z = (logits[r].double().cpu() - logits[r].double().max().cpu()) / float(temperature[r])
+            z = (logits[r].double().cpu() - logits[r].double().max().cpu()) / temperature[r]
             cdf = torch.cumsum(torch.exp(z), 0)
-            target, slack = float(uniform[r]) * float(cdf[-1]), 1e-4 * float(cdf[-1])
+            target, slack = uniform[r] * float(cdf[-1]), 1e-4 * float(cdf[-1])
             assert float(cdf[got[r]]) >= target - slack
             assert (float(cdf[got[r] - 1]) if got[r] > 0 else 0.0) <= target + slack
+
+
+FILTERS = [dict(top_k=1), dict(top_k=7), dict(top_k=300), dict(top_p=0.9), dict(top_p=0.3), dict(top_k=40, top_p=0.8),
+           dict(min_p=0.05), dict(top_k=50, min_p=0.1), dict(top_p=0.95, min_p=0.02), dict(top_k=20, top_p=0.5, min_p=0.2),
+           dict(top_k=10 ** 9), dict(top_p=0.999)]
+
+
+def test_filtered_sampling_matches_the_plain_sampler(ops, cuda_device):
+    """top-k, top-p and min-p, alone and together, at three vocabulary sizes.  A row is compared
+    token for token unless the plain sampler says that one of its decisions was a near tie."""
+    import plain_sampler
+
+    compared = 0
+    for V, spread in ((311, 2.0), (5000, 3.0), (151936, 4.0)):
+        g = torch.Generator().manual_seed(V + 1)
+        logits = (torch.randn((len(FILTERS) * 2, V), generator=g) * spread)
+        uniform = torch.rand(logits.shape[0], generator=g).tolist()
+        rows = []
+        for r in range(logits.shape[0]):
+            f = FILTERS[r % len(FILTERS)]
+            rows.append(ops.SampleRow(temperature=0.6 + 0.1 * (r % 7), uniform=uniform[r],
+                                      top_k=min(f.get("top_k", 0), V), top_p=f.get("top_p", 0.0),
+                                      min_p=f.get("min_p", 0.0)))
+        status = ops.new_status(cuda_device)
+        got = ops.sample_rows(logits.to(cuda_device), rows, status).ids.tolist()
+        ops.check_status(status)
+        for r, row in enumerate(rows):
+            want, margin = plain_sampler.sample(logits[r], row.temperature, row.uniform, row.top_k, row.top_p or 1.0,
+                                                row.min_p)
+            if margin > 1e-5:
+                assert got[r] == want, (V, r, FILTERS[r % len(FILTERS)], got[r], want, margin)
+                compared += 1
+            # Always: the token lies inside what the filters keep, give or take a near tie at the edge.
+            p = torch.softmax(plain_sampler.scale(logits[r], row.temperature), 0)
+            order = plain_sampler.rank(p).tolist()
+            if row.top_k:
+                assert order.index(got[r]) < row.top_k
+            if row.min_p:
+                assert float(p[got[r]]) > row.min_p * float(p.max()) * (1 - 1e-5)
+    assert compared >= 0.75 * 3 * 2 * len(FILTERS)        # most rows were decided clearly and compared exactly
+
+
+def test_ranked_draw_takes_equal_weights_in_index_order(ops, cuda_device):
+    """Five tokens share the largest logit.  With top_k = 5 each holds a fifth of the mass, and the
+    draw walks them by ascending index whatever their place in the vocabulary."""
+    V = 70000
+    tied = [69999, 3, 40000, 512, 4097]
+    logits = torch.full((5, V), -20.0)
+    logits[:, tied] = 1.5
+    rows = [ops.SampleRow(temperature=1.0, uniform=0.1 + 0.2 * r, top_k=5) for r in range(5)]
+    status = ops.new_status(cuda_device)
+    got = ops.sample_rows(logits.to(cuda_device), rows, status).ids.tolist()
+    ops.check_status(status)
+    assert got == sorted(tied)
+
+
+def test_ranking_is_a_stable_sort_of_the_whole_vocabulary(ops, cuda_device):
+    """A report of as many tokens as the vocabulary has shows the whole ranking: by value,
+    descending, equal values by index; values that underflow as probabilities still rank by z."""
+    import plain_sampler
+
+    for V in (33, 1000, 4097, 50001):
+        g = torch.Generator().manual_seed(V)
+        logits = torch.randn((2, V), generator=g) * 3
+        logits[0] = torch.round(logits[0] * 2) / 2            # many equal values
+        logits[1, ::3] -= 200.0                               # exp underflows to zero for a third of the row
+        rows = [ops.SampleRow(temperature=0.0, num_logprobs=V), ops.SampleRow(temperature=0.5, uniform=0.3, num_logprobs=V)]
+        status = ops.new_status(cuda_device)
+        out = ops.sample_rows(logits.to(cuda_device), rows, status)
+        ops.check_status(status)
+        ids, values = out.ids.tolist(), out.logprobs.tolist()
+        for r, row in enumerate(rows):
+            at = out.offsets[r]
+            chosen, best = plain_sampler.report(logits[r], row.temperature, ids[at], V)
+            assert ids[at + 1:at + 1 + V] == [token for token, _ in best], (V, r)
+            assert abs(values[at] - chosen) <= 1e-4 * max(1.0, abs(chosen))
+            for got, (_, want) in zip(values[at + 1:at + 1 + V], best):
+                assert abs(got - want) <= 1e-4 * max(1.0, abs(want))
+        assert out.offsets == [0, V + 1]
+
+
+def test_penalties_and_biases(ops, cuda_device):
+    """Adjustments change the logits in place, once per token, before anything else looks at them."""
+    import plain_sampler
+
+    V = 5000
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn((3, V), generator=g) * 2
+    histories = [torch.randint(0, V, (60,), generator=g).tolist() for _ in range(3)]
+    histories[1] += histories[1][-5:] * 3                      # tokens generated several times
+    prompt_lengths = [20, 10, 60]
+    settings = [dict(frequency_penalty=0.4, presence_penalty=0.3), dict(repetition_penalty=1.7, frequency_penalty=0.2),
+                dict(repetition_penalty=0.8)]
+    biases = [{7: 50.0, histories[0][30]: -3.0}, {}, {11: float("-inf"), 12: 2.5}]
+    want = [plain_sampler.adjust(logits[r], histories[r], prompt_lengths[r], bias=biases[r], **settings[r]) for r in range(3)]
+    adjustments = []
+    for r in range(3):
+        merged = {}
+        for position, token in enumerate(histories[r]):
+            entry = merged.setdefault(token, [0, True, 0.0])
+            entry[0] += position >= prompt_lengths[r]
+        for token, bias in biases[r].items():
+            merged.setdefault(token, [0, False, 0.0])[2] = bias
+        adjustments += [ops.TokenAdjustment(r, t, c, s, b) for t, (c, s, b) in merged.items()]
+    rows = [ops.SampleRow(temperature=0.0, num_logprobs=3, **settings[r]) for r in range(3)]
+    device_logits = logits.to(cuda_device)
+    status = ops.new_status(cuda_device)
+    out = ops.sample_rows(device_logits, rows, status, adjustments)
+    ops.check_status(status)
+    torch.testing.assert_close(device_logits.cpu(), torch.stack(want), rtol=1e-6, atol=1e-6)
+    ids, values = out.ids.tolist(), out.logprobs.tolist()
+    for r in range(3):
+        at = out.offsets[r]
+        assert ids[at] == int(plain_sampler.rank(want[r].double())[0])
+        chosen, best = plain_sampler.report(want[r], 0.0, ids[at], 3)
+        assert ids[at + 1:at + 4] == [t for t, _ in best]
+        assert abs(values[at] - chosen) <= 1e-4
+    assert ids[out.offsets[0]] == 7                            # the bias of +50 wins its row
 
 
 def test_sampling_reports_nan(ops, cuda_device):
     logits = torch.zeros((2, 100), device=cuda_device)
     logits[1, 7] = float("nan")
     status = ops.new_status(cuda_device)
-    ops.sample(logits, None, None, status)
+    ops.sample(logits, status)
     with pytest.raises(ops.KernelError, match="NaN"):
+        ops.check_status(status)
+    # A row that a bias of -inf everywhere leaves without a finite maximum is reported too, and the
+    # kernels that follow leave it alone instead of dividing by an empty mass.
+    logits = torch.full((1, 64), float("-inf"), device=cuda_device)
+    status = ops.new_status(cuda_device)
+    ops.sample_rows(logits, [ops.SampleRow(temperature=0.8, uniform=0.5, top_k=5, num_logprobs=2)], status)
+    with pytest.raises(ops.KernelError):
         ops.check_status(status)

@@ -26,8 +26,12 @@ def test_parameters():
     assert SamplingParams(temperature=0.0).greedy and SamplingParams(temperature=GREEDY_TEMPERATURE / 2).greedy
     assert not SamplingParams(temperature=0.7).greedy
     SamplingParams(temperature=0.7).validate(100)
-    SamplingParams(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0).validate(100)      # inactive filters are fine
+    SamplingParams(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0).validate(100)
+    SamplingParams(temperature=0.9, top_p=0.9, top_k=40, min_p=0.05, frequency_penalty=0.1, presence_penalty=-0.1,
+                   repetition_penalty=1.2, logits_bias={3: -float("inf")}, top_logprobs=5).validate(100)
+    assert SamplingParams(repetition_penalty=1.1).uses_history and not SamplingParams(top_k=3).uses_history
     for bad in (dict(temperature=-1.0), dict(temperature=float("nan")), dict(repetition_penalty=0.0),
-                dict(logits_bias={100: 1.0}), dict(logits_bias={1: float("inf")})):
+                dict(logits_bias={100: 1.0}), dict(logits_bias={1: float("inf")}), dict(top_logprobs=-1),
+                dict(top_p=float("inf"))):
         with pytest.raises(InvalidArgumentError):
             SamplingParams(**bad).validate(100)

@@ -48,6 +48,11 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--top-k", type=int, default=None)
     gen.add_argument("--top-p", type=float, default=None)
     gen.add_argument("--min-p", type=float, default=None)
+    gen.add_argument("--frequency-penalty", type=float, default=None)
+    gen.add_argument("--presence-penalty", type=float, default=None)
+    gen.add_argument("--repetition-penalty", type=float, default=None)
+    gen.add_argument("--top-logprobs", type=int, default=None,
+                     help="report each token's log-probability and this many of the most probable tokens (with --json)")
     gen.add_argument("--seed", type=int, default=None, help="sampling seed of each request")
     gen.add_argument("--stop-token-ids", type=_ids, default=[])
     gen.add_argument("--ignore-eos", action="store_true")
@@ -102,7 +107,9 @@ def _generate(args, parser) -> int:
                         scheduler=PagedSchedulerConfig(**scheduler_args),
                         kv_cache=KvCacheOptions(block_size=args.kv_block_size, num_blocks=args.num_kv_blocks))
         params = GenerationParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
-                                  top_p=args.top_p, min_p=args.min_p, seed=args.seed,
+                                  top_p=args.top_p, min_p=args.min_p, frequency_penalty=args.frequency_penalty,
+                                  presence_penalty=args.presence_penalty, repetition_penalty=args.repetition_penalty,
+                                  top_logprobs=args.top_logprobs, seed=args.seed,
                                   stop_token_ids=args.stop_token_ids, ignore_eos=args.ignore_eos)
         outputs = engine.generate(prompts, params)
     except (ZephyrError, ValueError, OSError) as error:
@@ -111,10 +118,14 @@ def _generate(args, parser) -> int:
     for output in outputs:
         choice = output.choices[0]
         if args.json:
-            print(json.dumps({"request_id": output.request_id, "prompt_token_ids": list(output.prompt_token_ids),
-                              "token_ids": list(choice.token_ids),
-                              "finish_reason": choice.finish_reason.value if choice.finish_reason else None,
-                              "status": output.status.value if output.status else None}))
+            record = {"request_id": output.request_id, "prompt_token_ids": list(output.prompt_token_ids),
+                      "token_ids": list(choice.token_ids),
+                      "finish_reason": choice.finish_reason.value if choice.finish_reason else None,
+                      "status": output.status.value if output.status else None}
+            if choice.logprobs is not None:
+                record["logprobs"] = [{"logprob": r.logprob, "top_logprobs": [[t.token_id, t.logprob] for t in r.top_logprobs]}
+                                      for r in choice.logprobs]
+            print(json.dumps(record))
         else:
             print(" ".join(str(t) for t in choice.token_ids))
     return 0

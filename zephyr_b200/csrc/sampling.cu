@@ -1,19 +1,66 @@
-// Token selection from float32 logits: greedy (lowest index among equal maxima) and temperature
-// sampling over the whole vocabulary.
+// Token selection from float32 logits: greedy, temperature, top-k, top-p and min-p sampling,
+// penalties and biases from the request's history, and log-probability reports.
 //
-// Definitions (reference): a temperature below 1e-7 means greedy (src/sampler/sampler.cpp:36,
-// 316-324); argmax ties go to the lowest index (deps/ttl reduction_operations.cuh:108-131);
-// z = (x - max) / T is formed in double and stored as float (src/sampler/sampler.cu:82-83);
-// p = exp(z) (softmax with maximum 0); the inclusive prefix sums run in index order and the token is
-// the first index with positive weight whose prefix sum exceeds min(u * total, the float below
-// total), else the last index with positive weight (sampler.cu:150-167).  NaN or +inf in a row is
-// reported in the status word (sampler.cu:77-80).
+// Definitions (reference, src/sampler/sampler.cpp and src/sampler/sampler.cu):
+//   * adjustments (sampler.cu:28-56): for a token of the history, score -= frequency_penalty * (times
+//     generated) + presence_penalty if it was generated; score = score > 0 ? score / repetition_penalty
+//     : score * repetition_penalty if it occurs anywhere in the history; then score += bias;
+//   * a temperature below 1e-7 means greedy (sampler.cpp:36, 300-309): argmax, the lowest index among
+//     equal maxima (deps/ttl reduction_operations.cuh:108-131);
+//   * z = (x - max) / T in double, stored as float (sampler.cu:82-83), T = 1 for greedy rows;
+//     p = softmax(z), here kept unnormalised as exp(z) (max z = 0): every rule below is a ratio;
+//   * top-k or top-p rows rank the vocabulary by p, descending, equal values by ascending index
+//     (deps/ttl/include/ttl/ops/topk.hpp:27-29); rank r stays if r < k, if the mass before r is
+//     below top_p times the mass of the first k (the candidate that reaches the threshold stays; rank
+//     0 always stays), and if p > min_p * max p (sampler.cu:99-118); the draw runs over the ranks;
+//   * other rows draw over the vocabulary in index order (min-p applied in place);
+//   * the draw (sampler.cu:150-167): inclusive prefix sums of the kept weights, the first candidate
+//     with positive weight whose prefix sum exceeds min(u * total, the float below total), else the
+//     last candidate with positive weight;
+//   * reports (sampler.cu:178-194): log-softmax of z over the whole vocabulary, before any filter:
+//     the chosen token's value and the top-n tokens ranked by z, descending, ties by index.
+// NaN or +inf in a row, or a row without a finite maximum, is reported in the status word
+// (sampler.cu:71-80).
+//
+// How it runs: passes over a row are spread over many CTAs (chunks of 4096 logits) and meet through
+// small per-chunk partial results, merged in chunk order so that a row's result does not depend on
+// the batch around it; the chunk that arrives last finishes the row's maximum.  Ranking is a
+// stable least-significant-digit radix sort, one CTA per row.
 #include "common.cuh"
 
 namespace zb {
 
-constexpr int SAMPLE_THREADS = 1024;
-constexpr float GREEDY_TEMPERATURE = 1e-7f;
+constexpr int SAMPLE_CHUNK = 4096;          // logits per CTA of the chunked passes
+constexpr int CHUNK_THREADS = 256;
+constexpr int ROW_THREADS = 1024;           // CTAs that own a whole row
+constexpr double GREEDY_TEMPERATURE = 1e-7;
+constexpr int SAMPLE_MAX_VOCAB = 1 << 22;
+
+// One row's parameters, as the host packs them (64 bytes).
+struct SampleRow {
+  double temperature;          // below 1e-7: greedy
+  double top_p;                // 0: off
+  double min_p;                // 0: off
+  float uniform;               // the row's draw in [0, 1)
+  float frequency_penalty, presence_penalty, repetition_penalty;
+  int top_k;                   // 0: off
+  int num_logprobs;            // -1: no report; n >= 0: the chosen token's log-probability and the top n
+  int result_offset;           // where the row's results start in the outputs
+  int sort_slot;               // sort job that ranks this row by weight, or -1
+  int report_slot;             // sort job that ranks this row by z, or -1
+  int reserved;
+};
+static_assert(sizeof(SampleRow) == 64, "the host packs 64 bytes per row");
+
+struct TokenAdjustment {       // 20 bytes
+  int row, token, generated_count, seen;
+  float bias;
+};
+
+struct SortJob {               // 8 bytes
+  int row;
+  int by_z;                    // 0: by weight, descending; 1: by z, descending
+};
 
 struct MaxIdx { float v; int i; };
 
@@ -22,116 +69,481 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
   return a;
 }
 
-__device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+__device__ __forceinline__ MaxIdx warp_argmax(MaxIdx mine) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     MaxIdx other{__shfl_xor_sync(0xffffffffu, mine.v, o), __shfl_xor_sync(0xffffffffu, mine.i, o)};
     mine = better(mine, other);
   }
+  return mine;
+}
+
+__device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  mine = warp_argmax(mine);
   __syncthreads();
   if (lane == 0) scratch[warp] = mine;
   __syncthreads();
   if (warp == 0) {
-    MaxIdx t = lane < nwarps ? scratch[lane] : MaxIdx{0.0f, -1};
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      MaxIdx other{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
-      t = better(t, other);
-    }
+    MaxIdx t = warp_argmax(lane < nwarps ? scratch[lane] : MaxIdx{0.0f, -1});
     if (lane == 0) scratch[32] = t;
   }
   __syncthreads();
   return scratch[32];
 }
 
-// One block per row.  temperature[r] < 1e-7: out[r] = argmax.  Otherwise sample with uniform[r] in [0, 1).
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride, int V,
-              const float* __restrict__ temperature, const float* __restrict__ uniform, int* status) {
-  __shared__ MaxIdx mscratch[33];
-  __shared__ float fscratch[33];
-  __shared__ float chunk_sum[SAMPLE_THREADS];
-  __shared__ int found, last_positive;
-  const int r = blockIdx.x;
+// Exclusive prefix of `v` over the block's threads in thread order; `total` gets the block's sum.
+// `scratch` holds 33 values.
+template <typename T>
+__device__ T block_exclusive_scan(T v, T* scratch, T& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  T inclusive = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const T below = __shfl_up_sync(0xffffffffu, inclusive, o);
+    if (lane >= o) inclusive += below;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    const T mine = lane < nwarps ? scratch[lane] : T(0);
+    T run = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const T below = __shfl_up_sync(0xffffffffu, run, o);
+      if (lane >= o) run += below;
+    }
+    scratch[lane] = run - mine;
+    if (lane == 31) scratch[32] = run;
+  }
+  __syncthreads();
+  total = scratch[32];
+  return scratch[warp] + inclusive - v;
+}
+
+__device__ __forceinline__ bool is_greedy(const SampleRow* rows, int r) {
+  return rows == nullptr || rows[r].temperature < GREEDY_TEMPERATURE;
+}
+__device__ __forceinline__ bool is_ranked(const SampleRow& p) {
+  return p.temperature >= GREEDY_TEMPERATURE && (p.top_k > 0 || p.top_p > 0.0);
+}
+__device__ __forceinline__ float scaled(float x, float maximum, double temperature) {
+  return static_cast<float>((static_cast<double>(x) - static_cast<double>(maximum)) / temperature);
+}
+__device__ __forceinline__ double scaling_temperature(const SampleRow& p) {
+  return p.temperature < GREEDY_TEMPERATURE ? 1.0 : p.temperature;
+}
+
+// ---------------------------------------------------------------------------------- adjustments
+__global__ void sample_adjust_kernel(float* __restrict__ logits, long long row_stride, int rows_n, int V,
+                                     const SampleRow* __restrict__ rows, const TokenAdjustment* __restrict__ adjustments,
+                                     int count, int* status) {
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x) {
+    const TokenAdjustment a = adjustments[e];
+    if (a.row < 0 || a.row >= rows_n || a.token < 0 || a.token >= V) {
+      report(status, STATUS_TOKEN_OUT_OF_RANGE, a.token, a.row);
+      continue;
+    }
+    const SampleRow& row = rows[a.row];
+    float* cell = logits + static_cast<size_t>(a.row) * row_stride + a.token;
+    float score = *cell;
+    if (a.generated_count > 0) {
+      score -= row.frequency_penalty * static_cast<float>(a.generated_count);
+      score -= row.presence_penalty;
+    }
+    if (a.seen && row.repetition_penalty != 1.0f)
+      score = score > 0.0f ? score / row.repetition_penalty : score * row.repetition_penalty;
+    score += a.bias;
+    *cell = score;       // a NaN or +inf made here is found by the pass over the row that follows
+  }
+}
+
+// ----------------------------------------------------------------------- maximum and argmax
+// Grid (chunks, rows).  The last chunk of a row to finish merges the row's partial maxima.
+__global__ void __launch_bounds__(CHUNK_THREADS)
+sample_max_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunks,
+                  const SampleRow* __restrict__ rows, float* part_max, int* part_idx, int* counters,
+                  float* row_max, int* row_arg, int* out_ids, int* status) {
+  __shared__ MaxIdx scratch[33];
+  __shared__ int last;
+  const int c = blockIdx.x, r = blockIdx.y;
   const float* x = logits + static_cast<size_t>(r) * row_stride;
-
-  // Each thread owns a contiguous chunk, so that prefix sums follow index order.
-  const int per = (V + blockDim.x - 1) / blockDim.x;
-  const int begin = min(V, static_cast<int>(threadIdx.x) * per), end = min(V, begin + per);
-
-  // The maximum does not care in which order the row is visited (equal maxima go to the lowest
-  // index whatever the order), so this pass strides through the row with coalesced loads.
+  const int begin = c * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
   MaxIdx mine{0.0f, -1};
-  bool bad = false;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int bad = -1;
+  for (int i = begin + threadIdx.x; i < end; i += CHUNK_THREADS) {
     const float v = x[i];
-    if (isnan(v) || (isinf(v) && v > 0.0f)) bad = true;
+    if (isnan(v) || (isinf(v) && v > 0.0f)) bad = i;
     mine = better(mine, MaxIdx{v, i});
   }
-  if (bad) report(status, STATUS_BAD_LOGIT, r, begin);
-  const MaxIdx top = block_argmax(mine, mscratch);
-  const float T = temperature != nullptr ? temperature[r] : 0.0f;
-  if (T < GREEDY_TEMPERATURE || top.i < 0 || !isfinite(top.v)) {
-    if (threadIdx.x == 0) out[r] = top.i < 0 ? 0 : top.i;
+  if (bad >= 0) report(status, STATUS_BAD_LOGIT, r, bad);
+  const MaxIdx top = block_argmax(mine, scratch);
+  if (threadIdx.x == 0) {
+    part_max[r * chunks + c] = top.v;
+    part_idx[r * chunks + c] = top.i;
+    __threadfence();
+    last = atomicAdd(&counters[r], 1) == chunks - 1;
+  }
+  __syncthreads();
+  if (!last || threadIdx.x >= 32) return;
+  __threadfence();
+  MaxIdx t{0.0f, -1};
+  for (int k = threadIdx.x; k < chunks; k += 32)
+    t = better(t, MaxIdx{__ldcg(&part_max[r * chunks + k]), __ldcg(&part_idx[r * chunks + k])});
+  t = warp_argmax(t);
+  if (threadIdx.x == 0) {
+    const bool usable = t.i >= 0 && isfinite(t.v);
+    if (!usable) report(status, STATUS_BAD_LOGIT, r, t.i);
+    row_max[r] = usable ? t.v : -INFINITY;        // -inf tells the later passes to leave the row alone
+    row_arg[r] = t.i >= 0 ? t.i : 0;
+    if (is_greedy(rows, r)) out_ids[rows != nullptr ? rows[r].result_offset : r] = t.i >= 0 ? t.i : 0;
+    counters[r] = 0;                               // left as it was found, for the next call
+  }
+}
+
+// ------------------------------------------------------------------------ weights and their sums
+// Grid (chunks, rows).  weights[r][i] = exp(z_i), zero where min-p removes the token from a row
+// that draws in index order.  part_all: the chunk's sum of exp(z); part_kept: of the weights.
+__global__ void __launch_bounds__(CHUNK_THREADS)
+sample_exp_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunks,
+                  const SampleRow* __restrict__ rows, const float* __restrict__ row_max, float* __restrict__ weights,
+                  float* part_all, float* part_kept) {
+  __shared__ float scratch_a[33], scratch_b[33];
+  const int c = blockIdx.x, r = blockIdx.y;
+  const SampleRow p = rows[r];
+  const bool greedy = p.temperature < GREEDY_TEMPERATURE;
+  if (greedy && p.num_logprobs < 0) return;
+  const float maximum = row_max[r];
+  if (!isfinite(maximum)) return;
+  const double T = scaling_temperature(p);
+  const bool filter = !greedy && !is_ranked(p) && p.min_p > 0.0;
+  const float* x = logits + static_cast<size_t>(r) * row_stride;
+  float* w = weights + static_cast<size_t>(r) * V;
+  const int begin = c * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
+  float all = 0.0f, kept = 0.0f;
+  for (int i = begin + threadIdx.x; i < end; i += CHUNK_THREADS) {
+    const float e = expf(scaled(x[i], maximum, T));
+    // The largest probability is exp(0) = 1 before normalisation.
+    const float k = filter && !(static_cast<double>(e) > p.min_p) ? 0.0f : e;
+    all += e;
+    kept += k;
+    if (!greedy) w[i] = k;
+  }
+  all = block_sum(all, scratch_a);
+  kept = block_sum(kept, scratch_b);
+  if (threadIdx.x == 0) {
+    part_all[r * chunks + c] = all;
+    part_kept[r * chunks + c] = kept;
+  }
+}
+
+// ------------------------------------------------------------------- the draw in index order
+// One CTA per row.  The chunk sums locate the chunk in which the prefix sum crosses the target; the
+// CTA then scans that chunk.
+__global__ void __launch_bounds__(ROW_THREADS)
+sample_select_kernel(const float* __restrict__ weights, int V, int chunks, const SampleRow* __restrict__ rows,
+                     const float* __restrict__ part_kept, const float* __restrict__ row_max,
+                     const int* __restrict__ row_arg, int* out_ids) {
+  __shared__ float scratch[33];
+  __shared__ float s_base, s_target;
+  __shared__ int s_chunk, s_exact, s_first, s_last;
+  const int r = blockIdx.x;
+  const SampleRow p = rows[r];
+  if (p.temperature < GREEDY_TEMPERATURE || is_ranked(p)) return;
+  if (!isfinite(row_max[r])) {
+    if (threadIdx.x == 0) out_ids[p.result_offset] = row_arg[r];
     return;
   }
-
-  const double dmax = static_cast<double>(top.v), dT = static_cast<double>(T);
-  float sum = 0.0f;
-  for (int i = begin; i < end; ++i)
-    sum += expf(static_cast<float>((static_cast<double>(x[i]) - dmax) / dT));
-  chunk_sum[threadIdx.x] = sum;
-  if (threadIdx.x == 0) { found = V; last_positive = -1; }
-  __syncthreads();
-  // Prefix of this thread's chunk: the chunk sums before it, added in index order by one warp in
-  // a fixed pattern (each lane sums 32 consecutive chunks, then a serial pass over the 32 lanes).
-  __shared__ float lane_prefix[33];
-  if (threadIdx.x < 32) {
-    float s = 0.0f;
-    for (int k = 0; k < 32; ++k) s += chunk_sum[threadIdx.x * 32 + k];
-    fscratch[threadIdx.x] = s;
-  }
-  __syncthreads();
   if (threadIdx.x == 0) {
-    float s = 0.0f;
-    for (int k = 0; k < 32; ++k) { lane_prefix[k] = s; s += fscratch[k]; }
-    lane_prefix[32] = s;
+    const float* sums = part_kept + r * chunks;
+    float total = 0.0f;
+    for (int c = 0; c < chunks; ++c) total += sums[c];
+    const float target = fminf(p.uniform * total, nextafterf(total, 0.0f));
+    float run = 0.0f, base = 0.0f;
+    int chosen = -1, last_positive = -1;
+    for (int c = 0; c < chunks; ++c) {
+      const float s = sums[c];
+      if (s > 0.0f) {
+        last_positive = c;
+        if (chosen < 0 && run + s > target) { chosen = c; base = run; }
+      }
+      run += s;
+    }
+    s_exact = chosen >= 0;
+    s_chunk = chosen >= 0 ? chosen : last_positive;
+    s_base = base;
+    s_target = target;
+    s_first = V;
+    s_last = -1;
   }
   __syncthreads();
-  const float total = lane_prefix[32];
-  float prefix = lane_prefix[threadIdx.x >> 5];
-  for (int k = (threadIdx.x >> 5) * 32; k < static_cast<int>(threadIdx.x); ++k) prefix += chunk_sum[k];
-
-  const float target = fminf(uniform[r] * total, nextafterf(total, 0.0f));
-  float run = prefix;
-  int my_found = V, my_last = -1;
-  for (int i = begin; i < end; ++i) {
-    const float p = expf(static_cast<float>((static_cast<double>(x[i]) - dmax) / dT));
-    run += p;
-    if (p > 0.0f) {
-      my_last = i;
-      if (my_found == V && run > target) my_found = i;
+  if (s_chunk < 0) {            // no weight at all: cannot happen for a finite maximum; stay defined
+    if (threadIdx.x == 0) out_ids[p.result_offset] = row_arg[r];
+    return;
+  }
+  constexpr int PER = SAMPLE_CHUNK / ROW_THREADS;
+  const float* w = weights + static_cast<size_t>(r) * V;
+  const int begin = s_chunk * SAMPLE_CHUNK + threadIdx.x * PER;
+  float mine[PER], local = 0.0f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    mine[j] = begin + j < V ? w[begin + j] : 0.0f;
+    local += mine[j];
+  }
+  float total;
+  float run = s_base + block_exclusive_scan(local, scratch, total);
+  int first = V, last = -1;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    run += mine[j];
+    if (mine[j] > 0.0f) {
+      last = begin + j;
+      if (first == V && s_exact && run > s_target) first = begin + j;
     }
   }
-  if (my_found < V) atomicMin(&found, my_found);
-  if (my_last >= 0) atomicMax(&last_positive, my_last);
+  if (first < V) atomicMin(&s_first, first);
+  if (last >= 0) atomicMax(&s_last, last);
   __syncthreads();
-  if (threadIdx.x == 0) out[r] = found < V ? found : (last_positive >= 0 ? last_positive : top.i);
+  if (threadIdx.x == 0) out_ids[p.result_offset] = s_first < V ? s_first : (s_last >= 0 ? s_last : row_arg[r]);
+}
+
+// ------------------------------------------------------------------------------------- ranking
+// One CTA per job: a stable radix sort of a row's keys, 8 bits a pass, between the job's two
+// buffers; the result lies in the second buffer.  Each warp owns a contiguous stretch of the input,
+// counts its digits, and after a scan over (digit, warp) scatters its stretch in order, so equal
+// keys keep their index order.
+__device__ __forceinline__ unsigned sort_key(const SortJob& job, int i, const float* x, const float* w, float maximum,
+                                             double T) {
+  // Ascending keys: weights descending (the bit pattern of a non-negative float grows with it),
+  // or |z| ascending, which is z descending because z <= 0.
+  return job.by_z ? __float_as_uint(fabsf(scaled(x[i], maximum, T))) : ~__float_as_uint(w[i]);
+}
+
+__global__ void __launch_bounds__(ROW_THREADS)
+sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
+                   const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
+                   const float* __restrict__ weights, unsigned* keys, int* idx) {
+  __shared__ int hist[256 * 32];
+  __shared__ int scratch[33];
+  const SortJob job = jobs[blockIdx.x];
+  const int r = job.row;
+  const float maximum = row_max[r];
+  if (!isfinite(maximum)) return;
+  const double T = scaling_temperature(rows[r]);
+  const float* x = logits + static_cast<size_t>(r) * row_stride;
+  const float* w = weights + static_cast<size_t>(r) * V;
+  unsigned* key_buf[2] = {keys + static_cast<size_t>(blockIdx.x) * 2 * V, keys + (static_cast<size_t>(blockIdx.x) * 2 + 1) * V};
+  int* idx_buf[2] = {idx + static_cast<size_t>(blockIdx.x) * 2 * V, idx + (static_cast<size_t>(blockIdx.x) * 2 + 1) * V};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_warp = ((V + 31) / 32 + 31) / 32 * 32;
+  const int w_begin = min(V, warp * per_warp), w_end = min(V, w_begin + per_warp);
+  const unsigned lanes_below = (1u << lane) - 1u;
+
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 8 * pass;
+    const unsigned* src_key = pass == 0 ? nullptr : key_buf[(pass - 1) & 1];
+    const int* src_idx = pass == 0 ? nullptr : idx_buf[(pass - 1) & 1];
+    unsigned* dst_key = key_buf[pass & 1];
+    int* dst_idx = idx_buf[pass & 1];
+    for (int e = threadIdx.x; e < 256 * 32; e += ROW_THREADS) hist[e] = 0;
+    __syncthreads();
+    for (int i = w_begin; i < w_end; i += 32) {
+      const int e = i + lane;
+      const bool valid = e < w_end;
+      const unsigned key = !valid ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
+      const int digit = valid ? static_cast<int>((key >> shift) & 255u) : 256;
+      const unsigned peers = __match_any_sync(0xffffffffu, digit);
+      if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    {   // exclusive scan over the 8192 counters in (digit, warp) order
+      constexpr int PER = 256 * 32 / ROW_THREADS;
+      int mine[PER], local = 0;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) { mine[j] = hist[threadIdx.x * PER + j]; local += mine[j]; }
+      int total;
+      int run = block_exclusive_scan(local, scratch, total);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) { hist[threadIdx.x * PER + j] = run; run += mine[j]; }
+    }
+    __syncthreads();
+    for (int i = w_begin; i < w_end; i += 32) {
+      const int e = i + lane;
+      const bool valid = e < w_end;
+      const unsigned key = !valid ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
+      const int source = !valid ? 0 : (pass == 0 ? e : src_idx[e]);
+      const int digit = valid ? static_cast<int>((key >> shift) & 255u) : 256;
+      const unsigned peers = __match_any_sync(0xffffffffu, digit);
+      if (valid) {
+        const int at = hist[digit * 32 + warp] + __popc(peers & lanes_below);
+        dst_key[at] = key;
+        dst_idx[at] = source;
+      }
+      __syncwarp();
+      if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();            // this pass's stores are visible to the whole CTA before the next reads them
+  }
+}
+
+// ---------------------------------------------------------------------- the draw over the ranks
+// One CTA per row.  `keys`/`idx`: the job's sorted second buffer; its first buffer is reused for
+// the prefix sums that the top-p rule looks at.
+__global__ void __launch_bounds__(ROW_THREADS)
+sample_select_sorted_kernel(int V, const SampleRow* __restrict__ rows, unsigned* keys, const int* __restrict__ idx,
+                            const float* __restrict__ row_max, const int* __restrict__ row_arg, int* out_ids) {
+  __shared__ float scratch[33];
+  __shared__ int s_first, s_last;
+  const int r = blockIdx.x;
+  const SampleRow p = rows[r];
+  if (!is_ranked(p) || p.sort_slot < 0) return;
+  if (!isfinite(row_max[r])) {
+    if (threadIdx.x == 0) out_ids[p.result_offset] = row_arg[r];
+    return;
+  }
+  const unsigned* sorted = keys + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
+  const int* source = idx + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
+  float* prefix = reinterpret_cast<float*>(keys + static_cast<size_t>(p.sort_slot) * 2 * V);
+  const int k = p.top_k > 0 ? min(p.top_k, V) : V;
+  const int per = (k + ROW_THREADS - 1) / ROW_THREADS;
+  const int begin = min(k, static_cast<int>(threadIdx.x) * per), end = min(k, begin + per);
+  auto weight = [&](int i) { return __uint_as_float(~sorted[i]); };
+  if (threadIdx.x == 0) { s_first = k; s_last = -1; }
+
+  float mass = 0.0f;            // of the first k ranks, as the prefix sums give it
+  if (p.top_p > 0.0) {
+    float local = 0.0f;
+    for (int i = begin; i < end; ++i) local += weight(i);
+    float total;
+    float run = block_exclusive_scan(local, scratch, total);
+    for (int i = begin; i < end; ++i) { run += weight(i); prefix[i] = run; }
+    __syncthreads();
+    mass = prefix[k - 1];
+  }
+  const float largest = weight(0);
+  auto kept_weight = [&](int i) -> float {
+    const float wi = weight(i);
+    if (p.top_p > 0.0 && i > 0 && !(static_cast<double>(prefix[i - 1]) < p.top_p * static_cast<double>(mass))) return 0.0f;
+    if (p.min_p > 0.0 && !(static_cast<double>(wi) > p.min_p * static_cast<double>(largest))) return 0.0f;
+    return wi;
+  };
+  float local = 0.0f;
+  for (int i = begin; i < end; ++i) local += kept_weight(i);
+  float total;
+  float run = block_exclusive_scan(local, scratch, total);
+  const float target = fminf(p.uniform * total, nextafterf(total, 0.0f));
+  int first = k, last = -1;
+  for (int i = begin; i < end; ++i) {
+    const float wi = kept_weight(i);
+    run += wi;
+    if (wi > 0.0f) {
+      last = i;
+      if (first == k && run > target) first = i;
+    }
+  }
+  if (first < k) atomicMin(&s_first, first);
+  if (last >= 0) atomicMax(&s_last, last);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int rank = s_first < k ? s_first : s_last;
+    out_ids[p.result_offset] = rank >= 0 ? source[rank] : row_arg[r];
+  }
+}
+
+// ---------------------------------------------------------------------------------- reports
+// One CTA per row: log-probabilities of the chosen token and of the row's top tokens.
+__global__ void __launch_bounds__(CHUNK_THREADS)
+sample_report_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunks,
+                     const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
+                     const float* __restrict__ part_all, const int* __restrict__ idx, int* out_ids,
+                     float* out_logprobs) {
+  __shared__ float s_log_total;
+  const int r = blockIdx.x;
+  const SampleRow p = rows[r];
+  if (p.num_logprobs < 0) return;
+  const float maximum = row_max[r];
+  const bool usable = isfinite(maximum);
+  if (threadIdx.x == 0) {
+    float total = 0.0f;
+    for (int c = 0; c < chunks && usable; ++c) total += part_all[r * chunks + c];
+    s_log_total = usable ? logf(total) : 0.0f;
+  }
+  __syncthreads();
+  const double T = scaling_temperature(p);
+  const float* x = logits + static_cast<size_t>(r) * row_stride;
+  if (threadIdx.x == 0) {
+    const int token = out_ids[p.result_offset];
+    out_logprobs[p.result_offset] = usable && token >= 0 && token < V ? scaled(x[token], maximum, T) - s_log_total : 0.0f;
+  }
+  if (p.num_logprobs == 0 || p.report_slot < 0) return;
+  const int* ranked = idx + (static_cast<size_t>(p.report_slot) * 2 + 1) * V;
+  for (int rank = threadIdx.x; rank < p.num_logprobs && rank < V; rank += CHUNK_THREADS) {
+    const int token = usable ? ranked[rank] : rank;
+    out_ids[p.result_offset + 1 + rank] = token;
+    out_logprobs[p.result_offset + 1 + rank] = usable ? scaled(x[token], maximum, T) - s_log_total : 0.0f;
+  }
 }
 
 }  // namespace zb
 
 using namespace zb;
 
-// out[r] = selected token of row r.  `temperature` may be null (all rows greedy); `uniform` is read
-// only for rows with temperature >= 1e-7.
-ZB_API int zb_sample(int* out, const float* logits, long long row_stride, int rows, int V, const float* temperature,
-                     const float* uniform, int* status, void* stream) {
-  if (rows < 0 || V <= 0 || row_stride < V) return ERR_BAD_ARGUMENT;
-  if (temperature != nullptr && uniform == nullptr) return ERR_BAD_ARGUMENT;
+// Chunks a row of V logits is cut into; the partial-result buffers hold rows * chunks entries.
+ZB_API int zb_sample_chunks(int V) { return (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK; }
+
+// Phases of zb_sample beyond adjustments, maximum and sorting, which follow from the arguments.
+constexpr int PHASE_WEIGHTS = 1;        // some row draws or reports
+constexpr int PHASE_DRAW_INDEXED = 2;   // some row draws in index order
+constexpr int PHASE_DRAW_RANKED = 4;    // some row draws over ranks
+constexpr int PHASE_REPORT = 8;         // some row reports log-probabilities
+
+// Selects one token per row of `logits` [rows, V] (float32, rows `row_stride` apart; adjusted in
+// place when there are adjustments).
+//   row_params   null: every row greedy, out_ids[r] = argmax of row r.  Else one SampleRow per row; a row's
+//                results start at its result_offset: the chosen token, then its top tokens if it reports.
+//   out_logprobs parallel to out_ids, written for reporting rows only; may be null without PHASE_REPORT.
+//   jobs         the rows to rank, by weight (draws with top-k or top-p) or by z (reports with n > 0);
+//                sort_keys and sort_idx hold 2 * n_jobs * V entries each.
+//   part_f       3 * rows * chunks floats; part_i rows * chunks ints; counters: rows ints, zero on entry and
+//                on exit; row_max, row_arg: rows entries; weights: rows * V floats (unused without PHASE_WEIGHTS).
+ZB_API int zb_sample(int* out_ids, float* out_logprobs, float* logits, long long row_stride, int rows, int V,
+                     const void* row_params, const void* adjustments, int n_adjustments, const void* jobs, int n_jobs,
+                     int phases, float* part_f, int* part_i, int* counters, float* row_max, int* row_arg,
+                     float* weights, unsigned* sort_keys, int* sort_idx, int* status, void* stream) {
+  if (rows < 0 || V <= 0 || row_stride < V || n_adjustments < 0 || n_jobs < 0) return ERR_BAD_ARGUMENT;
+  if (V > SAMPLE_MAX_VOCAB || rows > 65535) return ERR_UNSUPPORTED;
   if (rows == 0) return OK;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(out, logits, row_stride, V,
-                                                                                temperature, uniform, status);
+  if (row_params == nullptr && (phases != 0 || n_adjustments > 0 || n_jobs > 0)) return ERR_BAD_ARGUMENT;
+  if ((phases & PHASE_REPORT) && out_logprobs == nullptr) return ERR_BAD_ARGUMENT;
+  if (phases != 0 && weights == nullptr) return ERR_BAD_ARGUMENT;
+  if (n_jobs > 0 && (sort_keys == nullptr || sort_idx == nullptr || jobs == nullptr)) return ERR_BAD_ARGUMENT;
+  auto s = static_cast<cudaStream_t>(stream);
+  const auto* params = static_cast<const SampleRow*>(row_params);
+  const int chunks = zb_sample_chunks(V);
+  float* part_max = part_f;
+  float* part_all = part_f + static_cast<size_t>(rows) * chunks;
+  float* part_kept = part_all + static_cast<size_t>(rows) * chunks;
+  const dim3 chunk_grid(chunks, rows);
+  if (n_adjustments > 0)
+    sample_adjust_kernel<<<(n_adjustments + 255) / 256, 256, 0, s>>>(
+        logits, row_stride, rows, V, params, static_cast<const TokenAdjustment*>(adjustments), n_adjustments, status);
+  sample_max_kernel<<<chunk_grid, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, part_max, part_i,
+                                                        counters, row_max, row_arg, out_ids, status);
+  if (phases & PHASE_WEIGHTS)
+    sample_exp_kernel<<<chunk_grid, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, row_max, weights,
+                                                          part_all, part_kept);
+  if (n_jobs > 0)
+    sample_sort_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, params,
+                                                     row_max, weights, sort_keys, sort_idx);
+  if (phases & PHASE_DRAW_INDEXED)
+    sample_select_kernel<<<rows, ROW_THREADS, 0, s>>>(weights, V, chunks, params, part_kept, row_max, row_arg, out_ids);
+  if (phases & PHASE_DRAW_RANKED)
+    sample_select_sorted_kernel<<<rows, ROW_THREADS, 0, s>>>(V, params, sort_keys, sort_idx, row_max, row_arg, out_ids);
+  if (phases & PHASE_REPORT)
+    sample_report_kernel<<<rows, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, row_max, part_all,
+                                                       sort_idx, out_ids, out_logprobs);
   return launch_result();
 }

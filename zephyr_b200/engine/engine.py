@@ -120,6 +120,7 @@ class Engine:
         self.scheduler = Scheduler(self.scheduler_config, self.sequences, _RunnerCache(self.runner))
         self._requests: dict[int, _Request] = {}
         self._generators: dict[tuple[int, int], MT19937_64] = {}
+        self._logprobs: dict[tuple[int, int], list] = {}
         self._seed_source = MT19937_64(0)     # seeds for requests that bring none (engine.hpp:162)
         self._next_request_id = 0
         self.stats = EngineStats()
@@ -247,11 +248,15 @@ class Engine:
         if sampled:
             params = [self._requests[i.sequence_id[0]].sampling for i in sampled]
             generators = [self._generators[i.sequence_id] for i in sampled]
-            ids = self.sampler.sample(logits, params, generators)
+            sequences = [self.sequences[i.sequence_id] for i in sampled]
+            results = self.sampler.sample(logits, params, generators, [s.token_ids for s in sequences],
+                                          [s.prompt_length for s in sequences])
             self.runner.check()
-            for item, token in zip(sampled, ids):
-                self._append_token(item.sequence_id, int(token))
-            self.stats.generated_tokens += len(ids)
+            for item, result in zip(sampled, results):
+                if result.logprobs is not None:
+                    self._logprobs.setdefault(item.sequence_id, []).append(result.logprobs)
+                self._append_token(item.sequence_id, int(result.token_id))
+            self.stats.generated_tokens += len(results)
         self.stats.steps += 1
         self.stats.preemptions = self.scheduler.num_preemptions
         self.stats.step_seconds += time.perf_counter() - started
@@ -296,8 +301,10 @@ class Engine:
             sequence = self.sequences.pop(key)
             self._generators.pop(key, None)
             states.append(sequence.state)
+            reports = self._logprobs.pop(key, None)
             choices.append(Choice(key[1], tuple(sequence.token_ids[sequence.prompt_length:]),
-                                  request.finish_reasons[key[1]], request.stop_reasons[key[1]]))
+                                  request.finish_reasons[key[1]], request.stop_reasons[key[1]],
+                                  logprobs=tuple(reports) if reports is not None else None))
         if any(s == SequenceState.REJECTED for s in states):
             status = RequestStatus.REJECTED
         elif any(s == SequenceState.ERROR for s in states):

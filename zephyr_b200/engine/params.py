@@ -86,6 +86,7 @@ class Choice:
     finish_reason: FinishReason | None = None
     stop_reason: int | None = None
     text: str = ""                    # always empty: no tokenizer is loaded
+    logprobs: tuple | None = None     # one SamplingLogprobs per generated token, if top_logprobs was set
 
 
 @dataclass(frozen=True)

@@ -9,8 +9,11 @@ from __future__ import annotations
 
 import ctypes
 import math
+import struct
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
+from dataclasses import dataclass
+from typing import Sequence
 
 import torch
 
@@ -71,7 +74,10 @@ _SIGNATURES = {
                       c_int, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
-    "zb_sample": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "zb_sample_chunks": [c_int],
+    "zb_sample": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                  c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p],
 }
 
 
@@ -531,17 +537,153 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 
 # ------------------------------------------------------------------------------ sampling
-def sample(logits: torch.Tensor, temperature: torch.Tensor | None, uniform: torch.Tensor | None,
-           status: torch.Tensor) -> torch.Tensor:
-    """One token per row of float32 logits: argmax where temperature < 1e-7 (or is absent), else a
-    draw from softmax(logits / temperature) with the row's uniform number."""
-    _cuda(logits, temperature, uniform, status)
-    _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 [rows, V]")
-    rows, V = logits.shape
-    for t in (temperature, uniform):
-        if t is not None:
-            _require(t.dtype == torch.float32 and t.numel() == rows and t.is_contiguous(), "one float32 value per row")
-    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    _check(library().zb_sample(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(uniform),
-                               _ptr(status), _stream()), "sample")
-    return out
+@dataclass(frozen=True)
+class SampleRow:
+    """How one row of logits is turned into a token (the kernel's record of a row).
+
+    ``temperature`` below 1e-7 means greedy.  ``top_k`` 0, ``top_p`` 0 and ``min_p`` 0 switch those
+    filters off.  ``num_logprobs`` -1 asks for no report; n >= 0 for the chosen token's
+    log-probability and the n most probable tokens."""
+
+    temperature: float = 0.0
+    uniform: float = 0.0
+    top_k: int = 0
+    top_p: float = 0.0
+    min_p: float = 0.0
+    num_logprobs: int = -1
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature < 1e-7
+
+    @property
+    def ranked(self) -> bool:
+        return not self.greedy and (self.top_k > 0 or self.top_p > 0.0)
+
+
+@dataclass(frozen=True)
+class TokenAdjustment:
+    """What a row's history and biases do to one token's logit."""
+
+    row: int
+    token: int
+    generated_count: int = 0
+    seen: bool = False
+    bias: float = 0.0
+
+
+@dataclass
+class SampleOutput:
+    """Device results of ``sample_rows``: row r's chosen token is ``ids[offsets[r]]``, followed by its
+    top tokens if it reports; ``logprobs`` runs parallel to ``ids`` (None if no row reports)."""
+
+    ids: torch.Tensor
+    logprobs: torch.Tensor | None
+    offsets: list[int]
+
+
+_ROW_FORMAT = struct.Struct("<dddffffiiiiii")
+_ADJUSTMENT_FORMAT = struct.Struct("<iiiif")
+_JOB_FORMAT = struct.Struct("<ii")
+_PHASE_WEIGHTS, _PHASE_DRAW_INDEXED, _PHASE_DRAW_RANKED, _PHASE_REPORT = 1, 2, 4, 8
+
+# Work buffers of the sampling kernels, kept per device and only ever grown.  The counters are zero
+# between calls: the kernel leaves them as it found them.
+_sample_buffers: dict[tuple[torch.device, str], torch.Tensor] = {}
+
+
+def _sample_buffer(device: torch.device, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+    have = _sample_buffers.get((device, name))
+    if have is None or have.numel() < numel:
+        size = max(numel, 1024)
+        have = (torch.zeros if zero else torch.empty)(size, dtype=dtype, device=device)
+        _sample_buffers[(device, name)] = have
+    return have
+
+
+def sample_chunks(vocab: int) -> int:
+    return int(library().zb_sample_chunks(int(vocab)))
+
+
+def sample_rows(logits: torch.Tensor, rows: Sequence[SampleRow] | None, status: torch.Tensor,
+                adjustments: Sequence[TokenAdjustment] = ()) -> SampleOutput:
+    """One token per row of float32 logits [rows, V], chosen as each row's ``SampleRow`` says
+    (``rows`` None: argmax everywhere).  Adjustments are applied to ``logits`` in place first."""
+    _cuda(logits, status)
+    _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1,
+             "logits must be float32 [rows, V]")
+    R, V = logits.shape
+    device = logits.device
+    chunks = sample_chunks(V)
+    part_f = _sample_buffer(device, "part_f", 3 * R * chunks, torch.float32)
+    part_i = _sample_buffer(device, "part_i", R * chunks, torch.int32)
+    counters = _sample_buffer(device, "counters", R, torch.int32, zero=True)
+    row_max = _sample_buffer(device, "row_max", R, torch.float32)
+    row_arg = _sample_buffer(device, "row_arg", R, torch.int32)
+    if rows is None:
+        _require(not adjustments, "adjustments need row parameters")
+        ids = torch.empty(R, dtype=torch.int32, device=device)
+        _check(library().zb_sample(_ptr(ids), None, _ptr(logits), logits.stride(0), R, V, None, None, 0, None, 0, 0,
+                                   _ptr(part_f), _ptr(part_i), _ptr(counters), _ptr(row_max), _ptr(row_arg), None,
+                                   None, None, _ptr(status), _stream()), "sample")
+        return SampleOutput(ids, None, list(range(R)))
+    _require(len(rows) == R, "one SampleRow per row of logits")
+
+    # Pack the rows, the sort jobs they need and the adjustments into one upload.
+    jobs: list[tuple[int, int]] = []
+    offsets: list[int] = []
+    packed_rows = bytearray()
+    results, phases = 0, 0
+    for r, row in enumerate(rows):
+        sort_slot = report_slot = -1
+        if not row.greedy or row.num_logprobs >= 0:
+            phases |= _PHASE_WEIGHTS
+        if row.ranked:
+            sort_slot = len(jobs)
+            jobs.append((r, 0))
+            phases |= _PHASE_DRAW_RANKED
+        elif not row.greedy:
+            phases |= _PHASE_DRAW_INDEXED
+        num_logprobs = min(int(row.num_logprobs), V)
+        if num_logprobs >= 0:
+            phases |= _PHASE_REPORT
+            if num_logprobs > 0:
+                report_slot = len(jobs)
+                jobs.append((r, 1))
+        offsets.append(results)
+        packed_rows += _ROW_FORMAT.pack(row.temperature, row.top_p, row.min_p, row.uniform, row.frequency_penalty,
+                                        row.presence_penalty, row.repetition_penalty, min(int(row.top_k), V),
+                                        num_logprobs, results, sort_slot, report_slot, 0)
+        results += 1 + max(num_logprobs, 0)
+    for a in adjustments:
+        _require(0 <= a.row < R and 0 <= a.token < V, "an adjustment names a row and a token of the logits")
+    packed_adjustments = b"".join(_ADJUSTMENT_FORMAT.pack(a.row, a.token, a.generated_count, int(a.seen), a.bias)
+                                  for a in adjustments)
+    packed_jobs = b"".join(_JOB_FORMAT.pack(*job) for job in jobs)
+    at_adjustments = len(packed_rows)
+    at_jobs = (at_adjustments + len(packed_adjustments) + 15) // 16 * 16
+    blob = bytes(packed_rows) + packed_adjustments + bytes(at_jobs - at_adjustments - len(packed_adjustments)) + packed_jobs
+    host = torch.frombuffer(bytearray(blob), dtype=torch.uint8).pin_memory()
+    uploaded = host.to(device, non_blocking=True)
+    base = uploaded.data_ptr()
+
+    ids = torch.empty(results, dtype=torch.int32, device=device)
+    logprobs = torch.zeros(results, dtype=torch.float32, device=device) if phases & _PHASE_REPORT else None
+    weights = _sample_buffer(device, "weights", R * V, torch.float32) if phases else None
+    sort_keys = _sample_buffer(device, "sort_keys", 2 * len(jobs) * V, torch.int32) if jobs else None
+    sort_idx = _sample_buffer(device, "sort_idx", 2 * len(jobs) * V, torch.int32) if jobs else None
+    _check(library().zb_sample(
+        _ptr(ids), _ptr(logprobs), _ptr(logits), logits.stride(0), R, V, base,
+        base + at_adjustments if adjustments else None, len(adjustments), base + at_jobs if jobs else None, len(jobs),
+        phases, _ptr(part_f), _ptr(part_i), _ptr(counters), _ptr(row_max), _ptr(row_arg), _ptr(weights),
+        _ptr(sort_keys), _ptr(sort_idx), _ptr(status), _stream()),
+        "sample", kernels=1 + bool(adjustments) + bool(jobs) + bin(phases).count("1"))
+    return SampleOutput(ids, logprobs, offsets)
+
+
+def sample(logits: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """The argmax of every row of float32 logits, the lowest index among equal maxima."""
+    return sample_rows(logits, None, status).ids

@@ -1,0 +1,185 @@
+"""Times one kernel of this package alone, on synthetic inputs, and prints what it achieves.
+
+    python -m zephyr_b200.kernels.timing decode_attention --batch 8 --context 4096
+    python -m zephyr_b200.kernels.timing prefill_attention --tokens 2048
+    python -m zephyr_b200.kernels.timing gemm_small --rows 8 --n 6144 --k 1024 [--swiglu]
+    python -m zephyr_b200.kernels.timing sample --rows 8 --vocab 151936
+
+Each case rotates over several copies of its large operands, together larger than the L2 cache, so
+that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
+events around a CUDA graph of ``--iters`` launches, after ``--warmup`` plain launches.  The line printed is JSON: the
+kernel, its sizes, microseconds per launch, and GB/s over the bytes the kernel has to read, or
+TFLOP/s over the products it has to form.  This is also the small program that a profiler is
+pointed at when one kernel is to be looked at by itself.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+from . import ops
+
+L2_BYTES = 126 << 20
+
+
+def _time(run, warmup: int, iters: int) -> float:
+    """Microseconds per call of ``run(i)``.  The timed calls are captured in one CUDA graph, so that
+    a kernel of a few microseconds is not timed against the host's launch rate."""
+    for i in range(warmup):
+        run(i)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(iters):
+                run(warmup + i)
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        graph.replay()
+        end.record(stream)
+        torch.cuda.synchronize()
+    return begin.elapsed_time(end) / iters * 1e3
+
+
+def _copies(bytes_each: int) -> int:
+    return max(2, min(16, math.ceil(2 * L2_BYTES / max(bytes_each, 1))))
+
+
+def _paged_inputs(batch: int, context: int, nkv: int, hd: int, page: int, device):
+    pages_per = math.ceil(context / page)
+    num_pages = batch * pages_per + 1
+    cache_bytes = num_pages * 2 * nkv * page * hd * 2
+    caches = [torch.randn((num_pages, 2, nkv, page, hd), device=device, dtype=torch.bfloat16)
+              for _ in range(_copies(cache_bytes))]
+    table = (torch.randperm(num_pages - 1, device=device)[: batch * pages_per] + 1).int().view(batch, pages_per)
+    return caches, table.contiguous()
+
+
+def decode_attention(args) -> dict:
+    device = torch.device("cuda")
+    nh, nkv, hd, B, ctx = args.heads, args.kv_heads, args.head_dim, args.batch, args.context
+    caches, table = _paged_inputs(B, ctx, nkv, hd, args.page_size, device)
+    q = torch.randn((B, nh * hd), device=device, dtype=torch.bfloat16)
+    rows = torch.arange(B, dtype=torch.int32, device=device)
+    row_ctx = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
+    status, out = ops.new_status(device), torch.empty_like(q)
+    split = args.split or ops.decode_split_size(B, nkv, ctx)
+
+    def run(i):
+        ops.paged_decode(q, caches[i % len(caches)], table, rows, rows, row_ctx, ctx, nh, nkv, hd, args.window,
+                         1 / math.sqrt(hd), status, out=out, split_size=split)
+    us = _time(run, args.warmup, args.iters)
+    ops.check_status(status, "decode_attention")
+    live = min(ctx, args.window) if args.window else ctx
+    read = B * live * nkv * hd * 2 * 2
+    return {"kernel": "paged_decode_kernel", "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+            "page_size": args.page_size, "window": args.window, "split_size": split, "us": round(us, 2),
+            "bytes_read": read, "gbs": round(read / us / 1e3, 1)}
+
+
+def prefill_attention(args) -> dict:
+    device = torch.device("cuda")
+    nh, nkv, hd, T = args.heads, args.kv_heads, args.head_dim, args.tokens
+    caches, table = _paged_inputs(1, T, nkv, hd, args.page_size, device)
+    q = torch.randn((T, nh * hd), device=device, dtype=torch.bfloat16)
+    tile = ops.paged_prefill_tile_tokens()
+    n_tiles = math.ceil(T / tile)
+    tile_row = torch.zeros(n_tiles, dtype=torch.int32, device=device)
+    tile_q0 = (torch.arange(n_tiles, dtype=torch.int32, device=device) * tile).contiguous()
+    zero = torch.zeros(1, dtype=torch.int32, device=device)
+    q_len = torch.full((1,), T, dtype=torch.int32, device=device)
+    status, out = ops.new_status(device), torch.empty_like(q)
+
+    def run(i):
+        ops.paged_prefill(q, caches[i % len(caches)], table, tile_row, tile_q0, zero, q_len, zero, nh, nkv, hd,
+                          args.window, 1 / math.sqrt(hd), status, out=out)
+    us = _time(run, args.warmup, args.iters)
+    ops.check_status(status, "prefill_attention")
+    # Two products of 2 * hd flops per (query, visible key) pair and head.
+    pairs = sum(min(t + 1, args.window) if args.window else t + 1 for t in range(T))
+    flops = 4 * hd * pairs * nh
+    return {"kernel": "paged_prefill_kernel", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+            "page_size": args.page_size, "window": args.window, "us": round(us, 2), "flops": flops,
+            "tflops": round(flops / us / 1e6, 1)}
+
+
+def gemm_small(args) -> dict:
+    device = torch.device("cuda")
+    M, N, K = args.rows, args.n, args.k
+    weights = [torch.randn((N, K), device=device, dtype=torch.bfloat16) for _ in range(_copies(N * K * 2))]
+    x = torch.randn((M, K), device=device, dtype=torch.bfloat16)
+    out_dtype = torch.float32 if args.float_out else torch.bfloat16
+
+    def run(i):
+        ops.gemm_small(x, weights[i % len(weights)], out_dtype=out_dtype, swiglu=args.swiglu)
+    us = _time(run, args.warmup, args.iters)
+    read = N * K * 2
+    return {"kernel": "gemm_small_kernel", "rows": M, "n": N, "k": K, "swiglu": bool(args.swiglu),
+            "out": str(out_dtype).replace("torch.", ""), "us": round(us, 2), "bytes_read": read,
+            "gbs": round(read / us / 1e3, 1)}
+
+
+def sample(args) -> dict:
+    device = torch.device("cuda")
+    R, V = args.rows, args.vocab
+    logits = [torch.randn((R, V), device=device, dtype=torch.float32) for _ in range(_copies(R * V * 4))]
+    rows = None
+    if args.temperature >= 1e-7 or args.top_logprobs >= 0:
+        rows = [ops.SampleRow(temperature=args.temperature, uniform=0.1 + 0.8 * r / R, top_k=args.top_k,
+                              top_p=args.top_p, min_p=args.min_p, num_logprobs=args.top_logprobs) for r in range(R)]
+    status = ops.new_status(device)
+
+    def run(i):
+        ops.sample_rows(logits[i % len(logits)], rows, status)
+    us = _time(run, args.warmup, args.iters)
+    ops.check_status(status, "sample")
+    return {"kernel": "sample kernels", "rows": R, "vocab": V, "temperature": args.temperature, "top_k": args.top_k,
+            "top_p": args.top_p, "min_p": args.min_p, "top_logprobs": args.top_logprobs, "us": round(us, 2)}
+
+
+CASES = {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
+         "sample": sample}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="python -m zephyr_b200.kernels.timing", description=__doc__.split("\n")[0])
+    parser.add_argument("case", choices=sorted(CASES))
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--iters", type=int, default=40)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--tokens", type=int, default=2048)
+    parser.add_argument("--heads", type=int, default=16)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--page-size", type=int, default=16)
+    parser.add_argument("--window", type=int, default=0)
+    parser.add_argument("--split", type=int, default=0, help="positions per work item of the decode kernel (0: its own choice)")
+    parser.add_argument("--rows", type=int, default=8)
+    parser.add_argument("--n", type=int, default=6144)
+    parser.add_argument("--k", type=int, default=1024)
+    parser.add_argument("--swiglu", action="store_true")
+    parser.add_argument("--float-out", action="store_true")
+    parser.add_argument("--vocab", type=int, default=151936)
+    parser.add_argument("--temperature", type=float, default=0.0)
+    parser.add_argument("--top-k", type=int, default=0)
+    parser.add_argument("--top-p", type=float, default=0.0)
+    parser.add_argument("--min-p", type=float, default=0.0)
+    parser.add_argument("--top-logprobs", type=int, default=-1)
+    args = parser.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("a CUDA device is needed", file=sys.stderr)
+        return 2
+    print(json.dumps(CASES[args.case](args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,12 +1,17 @@
 """Choosing the next token from float32 logits.
 
-``SamplingParams`` carries the reference's names (src/include/sampler/sampler.hpp:20-34).  Built:
-greedy (temperature < 1e-7: argmax, lowest index among equals, the generator is not advanced) and
-temperature sampling over the whole vocabulary (p = softmax((x - max) / T), inclusive prefix sums
-in index order, the first index whose sum exceeds u * total; one draw
-u = (next 64 random bits >> 40) * 2^-24 per sampled token from the request's own MT19937-64;
-src/sampler/sampler.cpp:316-333, src/sampler/sampler.cu:82-83,150-167).  The reference's other
-filters (top-k, top-p, min-p, penalties, logit bias, logprobs) are refused with a clear error.
+``SamplingParams`` carries the reference's names and meanings (src/include/sampler/sampler.hpp:20-34,
+python/zephyr/_C.pyi:405-442).  Built, all on the device (kernels/ops.sample_rows, csrc/sampling.cu):
+  * penalties and biases from the request's history (src/sampler/sampler.cpp:112-139,
+    src/sampler/sampler.cu:28-56);
+  * greedy (temperature < 1e-7: argmax, lowest index among equals, the generator is not advanced);
+  * temperature sampling, p = softmax((x - max) / T), with top-k, top-p and min-p
+    (src/sampler/sampler.cu:99-118): rows with top-k or top-p draw over the tokens ranked by
+    probability, the others over the vocabulary in index order; one draw
+    u = (next 64 random bits >> 40) * 2^-24 per sampled token from the request's own MT19937-64
+    (src/sampler/sampler.cpp:316-333);
+  * ``top_logprobs``: the chosen token's log-probability and the n most probable tokens, measured
+    after penalties and temperature and before the filters (src/sampler/sampler.cu:178-194).
 """
 
 from __future__ import annotations
@@ -27,7 +32,7 @@ GREEDY_TEMPERATURE = 1e-7
 @dataclass(frozen=True)
 class SamplingParams:
     temperature: float = 1.0
-    top_k: int = 0
+    top_k: int = -1
     top_p: float = 1.0
     min_p: float = 0.0
     frequency_penalty: float = 0.0
@@ -41,8 +46,7 @@ class SamplingParams:
         return self.temperature < GREEDY_TEMPERATURE
 
     def validate(self, vocab_size: int) -> None:
-        """The checks of ValidateSamplingParams (src/sampler/sampler.cpp:278-294), then this engine's
-        own: filters it does not implement are refused rather than ignored."""
+        """The checks of ValidateSamplingParams (src/sampler/sampler.cpp:278-294)."""
         numbers = (self.temperature, self.top_p, self.min_p, self.frequency_penalty, self.presence_penalty,
                    self.repetition_penalty)
         if any(not math.isfinite(v) for v in numbers) or self.temperature < 0.0 or self.repetition_penalty <= 0.0:
@@ -51,56 +55,114 @@ class SamplingParams:
         for token, bias in self.logits_bias.items():
             if not 0 <= token < vocab_size or math.isnan(bias) or bias == math.inf:
                 raise InvalidArgumentError("logits bias requires a valid token and a finite or negative-infinite bias")
-        unsupported = []
-        if self.top_k > 0:
-            unsupported.append("top_k")
-        if 0.0 < self.top_p < 1.0:
-            unsupported.append("top_p")
-        if 0.0 < self.min_p < 1.0:
-            unsupported.append("min_p")
-        if self.frequency_penalty != 0.0 or self.presence_penalty != 0.0 or self.repetition_penalty != 1.0:
-            unsupported.append("penalties")
-        if self.logits_bias:
-            unsupported.append("logits_bias")
-        if self.top_logprobs is not None:
-            unsupported.append("top_logprobs")
-        if unsupported:
-            raise InvalidArgumentError(
-                "this engine samples greedily or by temperature over the whole vocabulary; not supported: "
-                + ", ".join(unsupported))
+        if self.top_logprobs is not None and self.top_logprobs < 0:
+            raise InvalidArgumentError("top_logprobs must not be negative")
+
+    @property
+    def uses_history(self) -> bool:
+        return self.frequency_penalty != 0.0 or self.presence_penalty != 0.0 or self.repetition_penalty != 1.0
+
+
+@dataclass(frozen=True)
+class TokenLogprob:
+    token_id: int
+    logprob: float
+
+
+@dataclass(frozen=True)
+class SamplingLogprobs:
+    """The chosen token's log-probability and the most probable tokens, best first."""
+
+    logprob: float
+    top_logprobs: tuple[TokenLogprob, ...] = ()
+
+
+@dataclass(frozen=True)
+class SamplingResult:
+    token_id: int
+    logprobs: SamplingLogprobs | None = None
 
 
 class Sampler:
-    """Selects tokens on the device; only the chosen ids come back to the host."""
+    """Selects tokens on the device; only the chosen ids (and the reports asked for) come back."""
 
     def __init__(self, device: torch.device | str):
         self.device = torch.device(device)
         self.status = ops.new_status(self.device)
 
-    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-                     generators: Sequence[MT19937_64 | None]) -> torch.Tensor:
-        """Launch the selection; returns int32 ids on the device.  Draws are taken in row order, one per
-        non-greedy row."""
-        rows = logits.shape[0]
+    def _launch(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None,
+                prompt_lengths: Sequence[int] | None) -> ops.SampleOutput:
+        rows, vocab = logits.shape
         if rows != len(params) or rows != len(generators):
             raise InvalidArgumentError("one SamplingParams and one generator per row of logits")
-        if all(p.greedy for p in params):
-            return ops.sample(logits, None, None, self.status)
-        temperature = [0.0 if p.greedy else float(p.temperature) for p in params]
-        uniform = []
-        for p, g in zip(params, generators):
-            if p.greedy:
-                uniform.append(0.0)
-            else:
+        if all(p.greedy and p.top_logprobs is None and not p.uses_history and not p.logits_bias for p in params):
+            return ops.sample_rows(logits, None, self.status)
+        records, adjustments = [], []
+        # Draws are taken in row order, one per non-greedy row (src/sampler/sampler.cpp:326-333).
+        for r, (p, g) in enumerate(zip(params, generators)):
+            uniform = 0.0
+            if not p.greedy:
                 if g is None:
                     raise InvalidArgumentError("a sampled row needs a generator")
-                uniform.append(g.next_uniform())
-        host = torch.tensor([temperature, uniform], dtype=torch.float32).pin_memory()
-        device = host.to(self.device, non_blocking=True)
-        return ops.sample(logits, device[0], device[1], self.status)
+                uniform = g.next_uniform()
+            records.append(ops.SampleRow(
+                temperature=float(p.temperature), uniform=uniform,
+                top_k=min(p.top_k, vocab) if p.top_k > 0 else 0,
+                top_p=float(p.top_p) if not p.greedy and 0.0 < p.top_p < 1.0 else 0.0,
+                min_p=float(p.min_p) if not p.greedy and 0.0 < p.min_p < 1.0 else 0.0,
+                num_logprobs=-1 if p.top_logprobs is None else min(int(p.top_logprobs), vocab),
+                frequency_penalty=float(p.frequency_penalty), presence_penalty=float(p.presence_penalty),
+                repetition_penalty=float(p.repetition_penalty)))
+            # History and biases merge into one record per token (src/sampler/sampler.cpp:112-139):
+            # how often the token was generated, whether it occurs at all, and its bias.
+            merged: dict[int, list] = {}
+            if p.uses_history:
+                if histories is None or prompt_lengths is None:
+                    raise InvalidArgumentError("penalties need the request's token history and prompt length")
+                history, prompt_length = histories[r], prompt_lengths[r]
+                if prompt_length > len(history):
+                    raise InvalidArgumentError("sampling history must include the complete prompt")
+                for position, token in enumerate(history):
+                    if not 0 <= token < vocab:
+                        continue
+                    entry = merged.setdefault(token, [0, False, 0.0])
+                    entry[1] = True
+                    if position >= prompt_length:
+                        entry[0] += 1
+            for token, bias in p.logits_bias.items():
+                merged.setdefault(int(token), [0, False, 0.0])[2] = float(bias)
+            adjustments.extend(ops.TokenAdjustment(r, token, count, seen, bias)
+                               for token, (count, seen, bias) in merged.items())
+        return ops.sample_rows(logits, records, self.status, adjustments)
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None = None,
+                     prompt_lengths: Sequence[int] | None = None) -> torch.Tensor:
+        """Launch the selection; returns the rows' chosen ids, int32, on the device.  For rows that
+        ask for no report.  Penalties and biases change ``logits`` in place."""
+        if any(p.top_logprobs is not None for p in params):
+            raise InvalidArgumentError("sample_async returns ids only; use sample() for rows that report")
+        return self._launch(logits, params, generators, histories, prompt_lengths).ids
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               generators: Sequence[MT19937_64 | None]) -> list[int]:
-        ids = self.sample_async(logits, params, generators).tolist()
+               generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None = None,
+               prompt_lengths: Sequence[int] | None = None) -> list[SamplingResult]:
+        """One ``SamplingResult`` per row.  ``histories`` (prompt and generated tokens) and
+        ``prompt_lengths`` are needed for rows with penalties.  Penalties and biases change
+        ``logits`` in place."""
+        for p in params:
+            p.validate(logits.shape[1])
+        out = self._launch(logits, params, generators, histories, prompt_lengths)
+        ids = out.ids.tolist()
+        values = out.logprobs.tolist() if out.logprobs is not None else None
         ops.check_status(self.status, "sampling")
-        return ids
+        results = []
+        for p, at in zip(params, out.offsets):
+            report = None
+            if p.top_logprobs is not None:
+                n = min(int(p.top_logprobs), logits.shape[1])
+                report = SamplingLogprobs(values[at], tuple(TokenLogprob(ids[at + 1 + k], values[at + 1 + k])
+                                                             for k in range(n)))
+            results.append(SamplingResult(ids[at], report))
+        return results
