@@ -524,6 +524,73 @@ def test_kernels_refuse_what_they_do_not_take(ops, cuda_device):
         ops.rmsnorm(torch.zeros(4, 4), torch.ones(4), 1e-6)               # CPU tensors: no CPU path
 
 
+# ------------------------------------------------------------------ chains of small products
+def _plain_rmsnorm(x, w, eps):
+    x = x.float()
+    return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float())
+
+
+@pytest.mark.parametrize("M,d,q,ffn,qkv", [(1, 1024, 2048, 3072, 4096), (8, 1024, 2048, 3072, 4096), (16, 320, 256, 880, 384),
+                                           (5, 2056, 1032, 4112, 136), (13, 64, 2304, 48, 8)])
+def test_fused_chain_matches_plain(ops, cuda_device, M, d, q, ffn, qkv):
+    """A layer's tail as one chain: output projection; residual add, norm, gate/up with silu * up;
+    down projection; residual add, norm, the next projection.  Against float64 products of the same
+    bfloat16 inputs, with the roundings the chain makes (every stored tensor is bfloat16)."""
+    g = torch.Generator().manual_seed(M * 1000 + d)
+    rnd = lambda *shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(cuda_device)
+    attn, residual = rnd(M, q), rnd(M, d)
+    w_o, w_gu, w_down, w_qkv = rnd(d, q, scale=q ** -0.5), rnd(2 * ffn, d, scale=d ** -0.5), rnd(d, ffn, scale=ffn ** -0.5), rnd(qkv, d, scale=d ** -0.5)
+    norm1 = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16).to(cuda_device)
+    norm2 = (1 + 0.1 * torch.randn(d, generator=g)).to(cuda_device)          # a float32 scale
+    eps1, eps2 = 1e-6, 3e-5
+    empty = lambda *shape: torch.full(shape, float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    o, act, down, out = empty(M, d), empty(M, ffn), empty(M, d), empty(M, qkv)
+    residual1, residual2 = empty(M, d), empty(M, d)
+    stages = [ops.ChainStage(w=w_o, y=o, x=attn),
+              ops.ChainStage(w=w_gu, y=act, residual_in=residual, residual_out=residual1, delta=o, norm_w=norm1, eps=eps1, swiglu=True),
+              ops.ChainStage(w=w_down, y=down, x=act),
+              ops.ChainStage(w=w_qkv, y=out, residual_in=residual1, residual_out=residual2, delta=down, norm_w=norm2, eps=eps2)]
+    for stage, normed in zip(stages, (False, True, False, True)):
+        assert ops.fused_chain_stage_supported(M, stage.w, normed, stage.swiglu)
+    status = ops.new_status(cuda_device)
+    for _ in range(3):                                   # the barrier's counters are left at zero each time
+        ops.fused_chain(stages, M, status)
+    ops.check_status(status)
+
+    bf = lambda t: t.to(torch.bfloat16)
+    mm = lambda x, w: (x.double() @ w.double().t()).float()
+    want_o = bf(mm(attn, w_o))
+    want_r1 = bf(residual.float() + want_o.float())
+    x1 = bf(_plain_rmsnorm(want_r1, norm1, eps1))
+    gu = mm(x1, w_gu).view(M, ffn // 8, 2, 8)
+    want_act = bf((torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, ffn))
+    want_down = bf(mm(want_act, w_down))
+    want_r2 = bf(want_r1.float() + want_down.float())
+    x2 = bf(_plain_rmsnorm(want_r2, norm2, eps2))
+    want_out = bf(mm(x2, w_qkv))
+    # bfloat16 stores: one unit in the last place of a value, and a little more where an input
+    # rounded the other way upstream.
+    for got, want, name in ((o, want_o, "o"), (residual1, want_r1, "residual1"), (act, want_act, "act"),
+                            (down, want_down, "down"), (residual2, want_r2, "residual2"), (out, want_out, "out")):
+        assert torch.isfinite(got.float()).all(), name
+        scale = float(want.float().abs().max())
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2 * scale, msg=lambda m: f"{name}: {m}")
+
+
+def test_fused_chain_refuses_what_it_cannot_run(ops, cuda_device):
+    w = torch.zeros((24, 64), dtype=torch.bfloat16, device=cuda_device)
+    assert ops.fused_chain_stage_supported(4, w, False, False)
+    assert not ops.fused_chain_stage_supported(4, w, False, True)          # 24 rows are no whole gate/up blocks
+    assert not ops.fused_chain_stage_supported(17, w, False, False)
+    assert not ops.fused_chain_stage_supported(4, w[:, :60], False, False)
+    big = torch.zeros((8, 65536), dtype=torch.bfloat16, device=cuda_device)
+    assert not ops.fused_chain_stage_supported(16, big, True, False)       # the normalised rows would not fit
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device=cuda_device)
+    y = torch.zeros((4, 20), dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ops.KernelError):
+        ops.fused_chain([ops.ChainStage(w=w[:20], y=y, x=x)], 4, ops.new_status(cuda_device))
+
+
 # ---------------------------------------------------------------------- sampling
 def test_argmax_lowest_index_on_ties(ops, cuda_device):
     logits = torch.full((3, 151936), -1.0, device=cuda_device)

@@ -28,6 +28,7 @@ constexpr int STATUS_ROW_OUT_OF_RANGE = 4;
 constexpr int STATUS_BAD_LOGIT = 5;
 constexpr int STATUS_COPY_TIMEOUT = 6;    // an asynchronous copy did not complete within the wait limit
 constexpr int STATUS_INTERNAL_CHECK = 7;  // a kernel's own check of an address or size failed
+constexpr int STATUS_BARRIER_TIMEOUT = 8; // a barrier across the grid did not complete within the wait limit
 
 __device__ __forceinline__ void report(int* status, int code, int detail, int index) {
   if (status != nullptr && atomicCAS(status, STATUS_OK, code) == STATUS_OK) {

@@ -35,6 +35,7 @@ constexpr int CHUNK_THREADS = 256;
 constexpr int ROW_THREADS = 1024;           // CTAs that own a whole row
 constexpr double GREEDY_TEMPERATURE = 1e-7;
 constexpr int SAMPLE_MAX_VOCAB = 1 << 22;
+constexpr int SORT_UNROLL = 8;              // loads in flight per lane of the ranking kernel
 
 // One row's parameters, as the host packs them (64 bytes).
 struct SampleRow {
@@ -348,14 +349,22 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
     int* dst_idx = idx_buf[pass & 1];
     for (int e = threadIdx.x; e < 256 * 32; e += ROW_THREADS) hist[e] = 0;
     __syncthreads();
-    for (int i = w_begin; i < w_end; i += 32) {
-      const int e = i + lane;
-      const bool valid = e < w_end;
-      const unsigned key = !valid ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
-      const int digit = valid ? static_cast<int>((key >> shift) & 255u) : 256;
-      const unsigned peers = __match_any_sync(0xffffffffu, digit);
-      if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
-      __syncwarp();
+    // Loads run SORT_UNROLL steps ahead of their use: a step's work is short, a load's latency is not.
+    for (int i = w_begin; i < w_end; i += 32 * SORT_UNROLL) {
+      unsigned key[SORT_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SORT_UNROLL; ++u) {
+        const int e = i + u * 32 + lane;
+        key[u] = e >= w_end ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
+      }
+#pragma unroll
+      for (int u = 0; u < SORT_UNROLL; ++u) {
+        const bool valid = i + u * 32 + lane < w_end;
+        const int digit = valid ? static_cast<int>((key[u] >> shift) & 255u) : 256;
+        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
+        __syncwarp();
+      }
     }
     __syncthreads();
     {   // exclusive scan over the 8192 counters in (digit, warp) order
@@ -369,21 +378,29 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
       for (int j = 0; j < PER; ++j) { hist[threadIdx.x * PER + j] = run; run += mine[j]; }
     }
     __syncthreads();
-    for (int i = w_begin; i < w_end; i += 32) {
-      const int e = i + lane;
-      const bool valid = e < w_end;
-      const unsigned key = !valid ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
-      const int source = !valid ? 0 : (pass == 0 ? e : src_idx[e]);
-      const int digit = valid ? static_cast<int>((key >> shift) & 255u) : 256;
-      const unsigned peers = __match_any_sync(0xffffffffu, digit);
-      if (valid) {
-        const int at = hist[digit * 32 + warp] + __popc(peers & lanes_below);
-        dst_key[at] = key;
-        dst_idx[at] = source;
+    for (int i = w_begin; i < w_end; i += 32 * SORT_UNROLL) {
+      unsigned key[SORT_UNROLL];
+      int source[SORT_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SORT_UNROLL; ++u) {
+        const int e = i + u * 32 + lane;
+        key[u] = e >= w_end ? 0u : (pass == 0 ? sort_key(job, e, x, w, maximum, T) : src_key[e]);
+        source[u] = e >= w_end ? 0 : (pass == 0 ? e : src_idx[e]);
       }
-      __syncwarp();
-      if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
-      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < SORT_UNROLL; ++u) {
+        const bool valid = i + u * 32 + lane < w_end;
+        const int digit = valid ? static_cast<int>((key[u] >> shift) & 255u) : 256;
+        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        if (valid) {
+          const int at = hist[digit * 32 + warp] + __popc(peers & lanes_below);
+          dst_key[at] = key[u];
+          dst_idx[at] = source[u];
+        }
+        __syncwarp();
+        if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
+        __syncwarp();
+      }
     }
     __syncthreads();            // this pass's stores are visible to the whole CTA before the next reads them
   }

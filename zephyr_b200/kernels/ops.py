@@ -33,6 +33,7 @@ STATUS_TEXT = {
     5: "NaN or +inf among the logits",
     6: "an asynchronous copy into shared memory that did not complete within the wait limit",
     7: "an address or size that failed a kernel's own check (a bug in this package)",
+    8: "a barrier across the grid that did not complete within the wait limit",
 }
 
 
@@ -74,6 +75,9 @@ _SIGNATURES = {
                       c_int, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
+    "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
+    "zb_fused_chain_max_stages": [],
+    "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_sample_chunks": [c_int],
     "zb_sample": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -160,6 +164,8 @@ def check_status(status: torch.Tensor, where: str = "step") -> None:
         for pool in _decode_buffers.values():       # a kernel that gave up may have left counters behind
             for _, count in pool:
                 count.zero_()
+        for buffer in list(_chain_sync.values()) + [b for (_, name), b in _sample_buffers.items() if name == "counters"]:
+            buffer.zero_()
         raise KernelError(f"{where}: a kernel reported {STATUS_TEXT.get(code, f'error {code}')} "
                           f"(value {detail}, at element {index})")
 
@@ -519,6 +525,106 @@ def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     _check(library().zb_gemm_small(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                                    DTYPE_CODE[out_dtype], int(swiglu), _stream()), "gemm_small")
     return out
+
+
+# ------------------------------------------------------------------ chains of small products
+PROLOGUE_NONE, PROLOGUE_NORM, PROLOGUE_ADD_NORM = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
+FUSED_CHAIN_MAX_TOKENS = 16
+
+
+class _ChainStage(ctypes.Structure):
+    _fields_ = [("w", c_void_p), ("ldw", c_longlong), ("N", c_int), ("K", c_int), ("prologue", c_int),
+                ("epilogue", c_int), ("x", c_void_p), ("ldx", c_longlong), ("residual_in", c_void_p),
+                ("residual_out", c_void_p), ("delta", c_void_p), ("ldd", c_longlong), ("norm_w", c_void_p),
+                ("norm_w_dtype", c_int), ("eps", c_float), ("y", c_void_p), ("ldy", c_longlong)]
+
+
+@dataclass
+class ChainStage:
+    """One stage of ``fused_chain``: y = epilogue(prologue(...) w^T), bfloat16.
+
+    The input is ``x`` [M, K] as given, or, with ``norm_w``, the RMS norm of ``residual_in`` [M, K]
+    (after ``delta`` [M, K] has been added to it, if given; the sum goes to ``residual_out``).  With
+    ``swiglu`` the rows of ``w`` are blocks of 8 gate rows and their 8 up rows and y is [M, N / 2]."""
+
+    w: torch.Tensor
+    y: torch.Tensor
+    x: torch.Tensor | None = None
+    residual_in: torch.Tensor | None = None
+    residual_out: torch.Tensor | None = None
+    delta: torch.Tensor | None = None
+    norm_w: torch.Tensor | None = None
+    eps: float = 0.0
+    swiglu: bool = False
+
+    @property
+    def prologue(self) -> int:
+        if self.norm_w is None:
+            return PROLOGUE_NONE
+        return PROLOGUE_ADD_NORM if self.delta is not None else PROLOGUE_NORM
+
+
+def fused_chain_stage_supported(tokens: int, w: torch.Tensor, normed_input: bool, swiglu: bool) -> bool:
+    """True if a product with ``w`` [N, K] can be a stage of a chain for this many tokens."""
+    return (w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and w.data_ptr() % 16 == 0
+            and bool(library().zb_fused_chain_stage_supported(int(tokens), w.shape[0], w.shape[1],
+                                                              PROLOGUE_NORM if normed_input else PROLOGUE_NONE,
+                                                              EPILOGUE_SWIGLU if swiglu else EPILOGUE_NONE)))
+
+
+def fused_chain_max_stages() -> int:
+    return int(library().zb_fused_chain_max_stages())
+
+
+# The arrival counters of the chain kernel's barrier, per device: zero between launches.
+_chain_sync: dict[torch.device, torch.Tensor] = {}
+
+
+def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
+                trace: torch.Tensor | None = None) -> None:
+    """Run the stages one after the other in one cooperative launch (see csrc/fused_chain.cu).
+    Every tensor is bfloat16 on the device (a norm weight may be float32); rows are contiguous.
+    ``trace`` (int32, 4 per stage) receives one CTA's timeline in clock cycles: the stage's start,
+    its input in place, its products done, the barrier passed."""
+    _require(1 <= len(stages) <= fused_chain_max_stages(), "a chain has 1 to 8 stages")
+    _require(1 <= tokens <= FUSED_CHAIN_MAX_TOKENS, "a chain takes 1 to 16 tokens")
+    packed = (_ChainStage * len(stages))()
+    for slot, st in zip(packed, stages):
+        N, K = st.w.shape
+        _cuda(st.w, st.y, st.x, st.residual_in, st.residual_out, st.delta, st.norm_w)
+        for t in (st.w, st.y, st.x, st.residual_in, st.residual_out, st.delta):
+            _require(t is None or (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1), "bfloat16 matrices")
+        _require(st.y.shape == (tokens, N // 2 if st.swiglu else N), "y must be [tokens, N] ([tokens, N / 2] with swiglu)")
+        slot.w, slot.ldw, slot.N, slot.K = st.w.data_ptr(), st.w.stride(0), N, K
+        slot.prologue, slot.epilogue = st.prologue, EPILOGUE_SWIGLU if st.swiglu else EPILOGUE_NONE
+        slot.y, slot.ldy = st.y.data_ptr(), st.y.stride(0)
+        if st.norm_w is None:
+            _require(st.x is not None and st.x.shape == (tokens, K), "x must be [tokens, K]")
+            slot.x, slot.ldx = st.x.data_ptr(), st.x.stride(0)
+        else:
+            _require(st.residual_in is not None and st.residual_in.shape == (tokens, K) and st.residual_in.is_contiguous(),
+                     "residual_in must be contiguous [tokens, K]")
+            _require(st.norm_w.numel() == K and st.norm_w.dtype in DTYPE_CODE and st.norm_w.is_contiguous(), "norm weight [K]")
+            slot.residual_in, slot.norm_w = st.residual_in.data_ptr(), st.norm_w.data_ptr()
+            slot.norm_w_dtype, slot.eps = DTYPE_CODE[st.norm_w.dtype], float(st.eps)
+            if st.delta is not None:
+                _require(st.delta.shape == (tokens, K), "delta must be [tokens, K]")
+                _require(st.residual_out is not None and st.residual_out.shape == (tokens, K)
+                         and st.residual_out.is_contiguous() and st.residual_out.data_ptr() != st.residual_in.data_ptr(),
+                         "residual_out must be a second contiguous [tokens, K] buffer")
+                slot.delta, slot.ldd, slot.residual_out = st.delta.data_ptr(), st.delta.stride(0), st.residual_out.data_ptr()
+    device = stages[0].w.device
+    sync = _chain_sync.get(device)
+    if sync is None:
+        sync = _chain_sync[device] = torch.zeros(2, dtype=torch.int32, device=device)
+    if trace is not None:
+        _cuda(trace)
+        _require(trace.dtype == torch.int32 and trace.is_contiguous() and trace.numel() >= 4 * len(stages),
+                 "trace must hold 4 int32 values per stage")
+    _check(library().zb_fused_chain(ctypes.addressof(packed), len(stages), int(tokens), _ptr(sync), _ptr(status),
+                                    _ptr(trace), _stream()), "fused_chain")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:

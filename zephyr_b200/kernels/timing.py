@@ -3,6 +3,7 @@
     python -m zephyr_b200.kernels.timing decode_attention --batch 8 --context 4096
     python -m zephyr_b200.kernels.timing prefill_attention --tokens 2048
     python -m zephyr_b200.kernels.timing gemm_small --rows 8 --n 6144 --k 1024 [--swiglu]
+    python -m zephyr_b200.kernels.timing fused_chain --rows 8 --hidden 1024 --ffn 3072
     python -m zephyr_b200.kernels.timing sample --rows 8 --vocab 151936
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
@@ -48,7 +49,12 @@ def _time(run, warmup: int, iters: int) -> float:
     return begin.elapsed_time(end) / iters * 1e3
 
 
+RESIDENT = False      # --resident: one copy of every operand, so that a small one stays in L2
+
+
 def _copies(bytes_each: int) -> int:
+    if RESIDENT:
+        return 1
     return max(2, min(16, math.ceil(2 * L2_BYTES / max(bytes_each, 1))))
 
 
@@ -144,7 +150,36 @@ def sample(args) -> dict:
             "top_p": args.top_p, "min_p": args.min_p, "top_logprobs": args.top_logprobs, "us": round(us, 2)}
 
 
-CASES = {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
+def fused_chain(args) -> dict:
+    """A layer's tail as one chain: output projection, add + norm + gate/up + silu * up, down
+    projection, add + norm + the next layer's input projection."""
+    device = torch.device("cuda")
+    M, d, q, ffn, qkv = args.rows, args.hidden, args.heads * args.head_dim, args.ffn, (args.heads + 2 * args.kv_heads) * args.head_dim
+    layer_bytes = 2 * (d * q + 2 * ffn * d + d * ffn + qkv * d)
+    rnd = lambda *shape: torch.randn(shape, device=device, dtype=torch.bfloat16) * 0.05
+    layers = [(rnd(d, q), rnd(2 * ffn, d), rnd(d, ffn), rnd(qkv, d)) for _ in range(_copies(layer_bytes))]
+    norm = torch.ones(d, device=device, dtype=torch.bfloat16)
+    attn, residual = rnd(M, q), rnd(M, d)
+    buf = lambda n: torch.empty((M, n), device=device, dtype=torch.bfloat16)
+    o, act, down, out, r1, r2 = buf(d), buf(ffn), buf(d), buf(qkv), buf(d), buf(d)
+    status = ops.new_status(device)
+    trace = torch.zeros(16, dtype=torch.int32, device=device)
+
+    def run(i):
+        w_o, w_gu, w_down, w_qkv = layers[i % len(layers)]
+        ops.fused_chain([ops.ChainStage(w=w_o, y=o, x=attn),
+                         ops.ChainStage(w=w_gu, y=act, residual_in=residual, residual_out=r1, delta=o, norm_w=norm, eps=1e-6, swiglu=True),
+                         ops.ChainStage(w=w_down, y=down, x=act),
+                         ops.ChainStage(w=w_qkv, y=out, residual_in=r1, residual_out=r2, delta=down, norm_w=norm, eps=1e-6)],
+                        M, status, trace=trace)
+    us = _time(run, args.warmup, args.iters)
+    ops.check_status(status, "fused_chain")
+    return {"kernel": "fused_chain_kernel", "rows": M, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv, "us": round(us, 2),
+            "bytes_read": layer_bytes, "gbs": round(layer_bytes / us / 1e3, 1),
+            "cycles_start_input_products_barrier": trace.view(4, 4).tolist()}
+
+
+CASES = {"fused_chain": fused_chain, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
          "sample": sample}
 
 
@@ -165,6 +200,8 @@ def main(argv=None) -> int:
     parser.add_argument("--rows", type=int, default=8)
     parser.add_argument("--n", type=int, default=6144)
     parser.add_argument("--k", type=int, default=1024)
+    parser.add_argument("--hidden", type=int, default=1024)
+    parser.add_argument("--ffn", type=int, default=3072)
     parser.add_argument("--swiglu", action="store_true")
     parser.add_argument("--float-out", action="store_true")
     parser.add_argument("--vocab", type=int, default=151936)
@@ -173,7 +210,11 @@ def main(argv=None) -> int:
     parser.add_argument("--top-p", type=float, default=0.0)
     parser.add_argument("--min-p", type=float, default=0.0)
     parser.add_argument("--top-logprobs", type=int, default=-1)
+    parser.add_argument("--resident", action="store_true",
+                        help="do not rotate operands: what fits in L2 is read from L2")
     args = parser.parse_args(argv)
+    global RESIDENT
+    RESIDENT = args.resident
     if not torch.cuda.is_available():
         print("a CUDA device is needed", file=sys.stderr)
         return 2

@@ -90,20 +90,25 @@ class Attention(Mixer):
         return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (ops.paged_prefill_tile_tokens(), "multi")]
 
     # ------------------------------------------------------------------ forward
+    def _store_projected(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+        """Per-head norm, rotation and cache write in one kernel; returns the queries."""
+        nh, nkv, hd = self.nh, self.nkv, self.hd
+        table = ctx.block_table(call.cache)
+        cos = getattr(self.position, "cos", None)
+        sin = getattr(self.position, "sin", None)
+        if call.writes_cache:
+            return ops.qk_norm_rope_cache(projected, nh, nkv, hd, self.q_norm, self.k_norm, self.eps, cos, sin,
+                                          ctx.positions, ctx.token_row, ctx.caches[call.cache], table, ctx.status)
+        return ops.qk_norm_rope_cache(projected, nh, 1, hd, self.q_norm, self.k_norm, self.eps, cos, sin,
+                                      ctx.positions, ctx.token_row, None, table, ctx.status)
+
     def _project_and_store(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
         nh, nkv, hd = self.nh, self.nkv, self.hd
         cache = ctx.caches[call.cache]
         table = ctx.block_table(call.cache)
         if self.fused_position:
-            cos = getattr(self.position, "cos", None)
-            sin = getattr(self.position, "sin", None)
-            if call.writes_cache:
-                qkv = ops.linear(x, self.w_qkv)
-                return ops.qk_norm_rope_cache(qkv, nh, nkv, hd, self.q_norm, self.k_norm, self.eps, cos, sin,
-                                              ctx.positions, ctx.token_row, cache, table, ctx.status)
-            q = ops.linear(x, self.w_q)      # a layer that reads another layer's cache needs no k and v
-            return ops.qk_norm_rope_cache(q, nh, 1, hd, self.q_norm, self.k_norm, self.eps, cos, sin,
-                                          ctx.positions, ctx.token_row, None, table, ctx.status)
+            # A layer that reads another layer's cache needs no k and v.
+            return self._store_projected(ops.linear(x, self.w_qkv if call.writes_cache else self.w_q), ctx, call)
         # Any other position encoding: the parts one after the other.
         T = x.shape[0]
         if not call.writes_cache:
@@ -154,6 +159,14 @@ class Attention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
         q = self._project_and_store(x, ctx, call)
         return ops.linear(self.attend(q, ctx, call), self.w_o)
+
+    def projections(self, call: LayerCall) -> tuple[torch.Tensor, torch.Tensor] | None:
+        if not self.fused_position:
+            return None
+        return (self.w_qkv if call.writes_cache else self.w_q), self.w_o
+
+    def core(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+        return self.attend(self._store_projected(projected, ctx, call), ctx, call)
 
 
 register_mixer("attention", Attention)

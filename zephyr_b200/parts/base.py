@@ -93,6 +93,11 @@ class Norm(Part):
         residual.add_(delta)
         return self.forward(residual)
 
+    def as_rms_scale(self) -> tuple[torch.Tensor, float] | None:
+        """(scale vector, eps) if this norm is y = x * rsqrt(mean(x^2) + eps) * scale, so that a
+        fused kernel may apply it; None for any other norm."""
+        return None
+
 
 class PositionEncoding(Part):
     def __init__(self, spec: PositionSpec, dtype: torch.dtype, device: torch.device | str): ...
@@ -121,12 +126,27 @@ class Mixer(Part):
         """x [T, hidden] -> [T, hidden], reading and (if ``call.writes_cache``) writing cache ``call.cache``."""
         raise NotImplementedError
 
+    # A mixer of the form  out_weight( core( in_weight(x) ) )  may say so: a block can then run the
+    # two plain products inside a fused chain of products and call ``core`` in between.
+    def projections(self, call: LayerCall) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """(in_weight [P, hidden], out_weight [hidden, Q]) for this call, or None."""
+        return None
+
+    def core(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+        """[T, P] -> [T, Q]: what lies between the two products."""
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     def __init__(self, spec: FeedForwardSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """(gate_up weight [2I, hidden] in blocks of 8 gate rows and their 8 up rows, down weight
+        [hidden, I]) if this part is down(silu(gate(x)) * up(x)); None otherwise."""
+        return None
 
 
 @dataclass
@@ -151,6 +171,11 @@ class Block(Part):
 
     def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
         raise NotImplementedError
+
+    def chain_plan(self):
+        """What a fused chain of small products needs of this block (``fused.BlockPlan``), or None
+        if the block is not of the pre-norm residual form over parts that offer it."""
+        return None
 
 
 NORMS: dict[str, type] = {}

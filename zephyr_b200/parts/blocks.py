@@ -9,6 +9,7 @@ from __future__ import annotations
 
 from ..config.spec import LayerCall
 from .base import Block, FeedForward, Mixer, Norm, ResidualStream, StepContext, register_block
+from .fused import BlockPlan
 
 
 class PreNormResidual(Block):
@@ -29,6 +30,14 @@ class PreNormResidual(Block):
         normed = self.feed_forward_norm.add_forward(stream.hidden, mixed)
         stream.pending = self.feed_forward.forward(normed)
         return stream
+
+
+    def chain_plan(self) -> BlockPlan | None:
+        mixer_norm, ffn_norm = self.mixer_norm.as_rms_scale(), self.feed_forward_norm.as_rms_scale()
+        gated = self.feed_forward.as_gated_products()
+        if mixer_norm is None or ffn_norm is None or gated is None:
+            return None
+        return BlockPlan(self.mixer, mixer_norm, ffn_norm, gated[0], gated[1])
 
 
 register_block("prenorm_residual", PreNormResidual)

@@ -46,6 +46,9 @@ class SwiGLU(FeedForward):
             p["down_proj"]: WeightDecl((hidden, inter), ROLE_LINEAR),
         }
 
+    def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
+        return (self.w_gate_up, self.w_down) if self.blocked else None
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
             hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True)       # product and activation in one kernel

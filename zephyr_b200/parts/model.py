@@ -20,6 +20,7 @@ from ..config.spec import LayerSpec, ModelSpec
 from ..kernels import ops
 from ..weights.loader import ROLE_EMBEDDING, ROLE_LINEAR, WeightDecl, WeightStore, load_weights
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, ResidualStream, StepContext, lookup)
+from .fused import DecodeChains
 
 
 def _layer_classes(layer: LayerSpec):
@@ -98,6 +99,9 @@ class Model:
                       getattr(block.mixer, "position", None)]
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in parts if part is not None)
         self.tile_requests = tile_requests(spec)
+        # Steps of a few tokens run as fused chains of products where every block offers its pieces.
+        self.chains = DecodeChains.build(self.layers, spec.run_order, spec.hidden_size, dtype)
+        self.use_chains = True
 
     @classmethod
     def load(cls, spec: ModelSpec, store: WeightStore, dtype: torch.dtype, device: torch.device | str) -> "Model":
@@ -129,9 +133,12 @@ class Model:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
         hidden = ops.embedding(self.embedding, ctx.token_ids, ctx.status)
-        stream = ResidualStream(hidden)
-        for call in self.spec.run_order:
-            stream = self.layers[call.layer].forward(stream, ctx, call)
+        if self.use_chains and self.chains is not None and self.chains.supports(ctx.num_tokens):
+            stream = ResidualStream(*self.chains.forward(hidden, ctx))
+        else:
+            stream = ResidualStream(hidden)
+            for call in self.spec.run_order:
+                stream = self.layers[call.layer].forward(stream, ctx, call)
         wanted = ctx.logit_tokens
         if wanted.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)

@@ -32,5 +32,8 @@ class RMSNorm(Norm):
     def add_forward(self, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps)
 
+    def as_rms_scale(self) -> tuple[torch.Tensor, float]:
+        return self.weight, self.eps
+
 
 register_norm("rmsnorm", RMSNorm)
