@@ -4,7 +4,7 @@
 // The decode step is bound by reading the cache, so the kernel is built around the copy.  One
 // persistent CTA per SM walks a list of work items, an item being one (request, key/value head,
 // split of the context).  Inside the CTA the work is split by role:
-//   * one producer warp runs ahead through the items and streams their keys and values into a
+//   * three producer warps, taking tiles in turn, run ahead through the items and stream their keys and values into a
 //     ring of shared-memory tiles of 32 positions with bulk asynchronous copies (the TMA engine's
 //     untiled form, cp.async.bulk), one instruction per page of keys or values (the cache stores
 //     rows with permuted 16-byte chunks so that a page copied as it is can be read without bank
@@ -14,7 +14,8 @@
 //   * four consumer warps each take every fourth tile of the current item, whole: scores and
 //     probabilities-times-values run on tensor cores (m16n8k16, the group's query heads padded to
 //     the 16 rows), the softmax is online in float32; a consumer hands the slot back the moment
-//     it has read it.  No barrier spans the CTA inside an item.
+//     it has read it (rows it had to clear first are fenced towards the copy engine).  No barrier
+//     spans the CTA inside an item.
 // When an item's tiles are done the consumers merge their four states; the item's result is a
 // partial one unless the item covers its row's whole context.  The last item of a (request,
 // key/value head) to finish, found with an atomic counter, merges the splits' partial results, so
@@ -30,7 +31,8 @@
 namespace zb {
 
 constexpr int DEC_CONSUMERS = 4;
-constexpr int DEC_THREADS = (DEC_CONSUMERS + 1) * 32;   // consumers are warps 0..3, the producer is warp 4
+constexpr int DEC_PRODUCERS = 3;         // producer warps take tiles in turn: one warp cannot issue copies fast enough to fill the memory pipe
+constexpr int DEC_THREADS = (DEC_CONSUMERS + DEC_PRODUCERS) * 32;   // consumers are warps 0..3, producers the warps after them
 constexpr int DEC_TILE = 32;             // positions per tile: one consumer warp's unit of work
 constexpr int DEC_MAX_GROUP = 16;        // query heads per key/value head that fit one MMA tile
 constexpr int DEC_WAIT_LIMIT = 1 << 24;  // polls of an mbarrier before a warp gives up and reports
@@ -48,7 +50,7 @@ struct DecodeArgs {
   float* part_ml;                // [n_rows, nh, max_splits, 2]
   int* counters;                 // [n_rows, nkv] zero on entry, zero again on exit
   int max_blocks, page_shift, num_pages, num_rows, n_rows;
-  int nh, nkv, window, split_size, max_splits, ring_slots;
+  int nh, nkv, window, split_size, max_splits, ring_slots, item_pages;
   float scale_log2;              // scale * log2(e)
   int* status;
 };
@@ -106,7 +108,7 @@ paged_decode_kernel(const DecodeArgs a) {
   unsigned long long* empty = full + R;
   unsigned long long* qfull = empty + R;
   unsigned long long* qempty = qfull + 2;
-  int* page_ids = reinterpret_cast<int*>(qempty + 2);         // the current item's pages, for the producer
+  int* page_ids_all = reinterpret_cast<int*>(qempty + 2);     // the current item's pages, one list per producer warp
   __shared__ int is_last;
   __shared__ volatile int abort_flag;      // set by the first warp whose wait ran out; every later wait gives up at once
 
@@ -133,23 +135,29 @@ paged_decode_kernel(const DecodeArgs a) {
   const int page_size = 1 << a.page_shift;
   const long long page_stride = 2LL * a.nkv * page_size * HD;
 
-  if (warp == DEC_CONSUMERS) {
-    // ------------------------------------------------------------------------- the producer
+  if (warp >= DEC_CONSUMERS) {
+    // ------------------------------------------------------------------------ the producers
+    // Both walk the same items and tiles; a tile belongs to the producer its number names, and
+    // the first producer also fetches the queries.
+    const int me = warp - DEC_CONSUMERS;
+    int* page_ids = page_ids_all + me * a.item_pages;
     int tile_seq = 0, item_seq = 0;
     for (int id = blockIdx.x; id < n_items; id += gridDim.x) {
       DecodeItem it;
       if (!decode_item(a, id, it)) continue;
       const int qb = item_seq & 1;
-      if (!wait(&qempty[qb], ((item_seq >> 1) & 1) ^ 1)) {
-        if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -1, it.row);
-        abort_flag = 1;
-        return;
+      if (me == 0) {
+        if (!wait(&qempty[qb], ((item_seq >> 1) & 1) ^ 1)) {
+          if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -1, it.row);
+          abort_flag = 1;
+          return;
+        }
+        if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
+        if (lane < g)
+          bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
+                        a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
+                        ROW_BYTES, &qfull[qb]);
       }
-      if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
-      if (lane < g)
-        bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
-                      a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
-                      ROW_BYTES, &qfull[qb]);
       ++item_seq;
       // The item's page ids in one go (one round trip to memory per item instead of one per tile).
       const int* table = a.block_table + static_cast<size_t>(it.row) * a.max_blocks;
@@ -166,13 +174,13 @@ paged_decode_kernel(const DecodeArgs a) {
       const int run_rows = page_size < DEC_TILE ? page_size : DEC_TILE;
       const int n_runs = DEC_TILE / run_rows;
       for (int t = 0; t < it.n_tiles; ++t, ++tile_seq) {
+        if (tile_seq % DEC_PRODUCERS != me) continue;
         const int slot = tile_seq % R;
         if (!wait(&empty[slot], ((tile_seq / R) & 1) ^ 1)) {
           if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -2, it.row);
           abort_flag = 1;
           return;
         }
-        fence_proxy_async();   // the consumers' ordinary stores to the slot come before the copies into it
         const int p0 = it.first_tile + t * DEC_TILE + lane * run_rows;     // first position of this lane's run
         const bool copies = lane < n_runs && (p0 >> a.page_shift) < a.max_blocks;
         if (copies) {
@@ -249,9 +257,10 @@ paged_decode_kernel(const DecodeArgs a) {
         // anything (another request's old values, NaN).  Their scores are masked below; their value
         // rows are cleared so that a probability of zero times such a row stays zero.
         const int pos = key0 + lane;
-        if (pos < it.begin || pos >= it.end) {
+        if (lane < DEC_TILE && (pos < it.begin || pos >= it.end)) {
 #pragma unroll
           for (int c = 0; c < CHUNKS; ++c) *reinterpret_cast<uint4*>(vs_tile + lane * HD + c * 8) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async();   // these ordinary stores come before the next bulk copy into the slot
         }
         __syncwarp();
       }
@@ -418,7 +427,7 @@ paged_decode_kernel(const DecodeArgs a) {
 
 // Shared memory of one CTA with `slots` ring slots, and the most slots that fit.
 template <int HD> size_t decode_smem_bytes(int slots, int g, int item_pages) {
-  return static_cast<size_t>(item_pages) * sizeof(int)                                     // the item's page ids
+  return static_cast<size_t>(item_pages) * DEC_PRODUCERS * sizeof(int)                     // the item's page ids, per producer
          + static_cast<size_t>(slots) * 2 * DEC_TILE * HD * sizeof(__nv_bfloat16)         // ring
          + 2 * 16 * (HD + 8) * sizeof(__nv_bfloat16)                                       // queries, two items
          + static_cast<size_t>(DEC_CONSUMERS) * g * (HD + 2) * sizeof(float)               // merge buffers
@@ -433,6 +442,7 @@ int decode_launch(DecodeArgs& a, cudaStream_t stream) {
   int slots = 2;
   while (decode_smem_bytes<HD>(slots + 1, g, item_pages) <= static_cast<size_t>(DEC_SMEM_BUDGET)) ++slots;
   a.ring_slots = slots;
+  a.item_pages = item_pages;
   const size_t smem = decode_smem_bytes<HD>(slots, g, item_pages);
   auto kernel = paged_decode_kernel<HD>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)

@@ -58,13 +58,17 @@ def _copies(bytes_each: int) -> int:
     return max(2, min(16, math.ceil(2 * L2_BYTES / max(bytes_each, 1))))
 
 
+SEQUENTIAL_PAGES = False      # --sequential-pages: a request's pages lie behind one another in the pool
+
+
 def _paged_inputs(batch: int, context: int, nkv: int, hd: int, page: int, device):
     pages_per = math.ceil(context / page)
     num_pages = batch * pages_per + 1
     cache_bytes = num_pages * 2 * nkv * page * hd * 2
     caches = [torch.randn((num_pages, 2, nkv, page, hd), device=device, dtype=torch.bfloat16)
               for _ in range(_copies(cache_bytes))]
-    table = (torch.randperm(num_pages - 1, device=device)[: batch * pages_per] + 1).int().view(batch, pages_per)
+    order = torch.arange(num_pages - 1, device=device) if SEQUENTIAL_PAGES else torch.randperm(num_pages - 1, device=device)
+    table = (order[: batch * pages_per] + 1).int().view(batch, pages_per)
     return caches, table.contiguous()
 
 
@@ -210,11 +214,13 @@ def main(argv=None) -> int:
     parser.add_argument("--top-p", type=float, default=0.0)
     parser.add_argument("--min-p", type=float, default=0.0)
     parser.add_argument("--top-logprobs", type=int, default=-1)
+    parser.add_argument("--sequential-pages", action="store_true",
+                        help="block tables that walk the pool in order instead of a random permutation")
     parser.add_argument("--resident", action="store_true",
                         help="do not rotate operands: what fits in L2 is read from L2")
     args = parser.parse_args(argv)
-    global RESIDENT
-    RESIDENT = args.resident
+    global RESIDENT, SEQUENTIAL_PAGES
+    RESIDENT, SEQUENTIAL_PAGES = args.resident, args.sequential_pages
     if not torch.cuda.is_available():
         print("a CUDA device is needed", file=sys.stderr)
         return 2
