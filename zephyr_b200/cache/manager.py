@@ -18,6 +18,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Hashable, Iterable
 
+import numpy as np
+
 from ..config.errors import InvalidArgumentError, OutOfPagesError
 
 NULL_PAGE = 0
@@ -128,6 +130,7 @@ class _Request:
     reserved: list[int]                     # per group: pages promised at admission, not yet drawn
     length: int = 0                         # positions covered by the tables
     computed: int = 0                       # positions whose entries have been written
+    arrays: list = field(default_factory=list)   # the tables again as int32 arrays, grown in step with them
 
 
 class CacheManager:
@@ -191,6 +194,12 @@ class CacheManager:
     def block_table(self, request_id: Hashable, group: int = 0) -> list[int]:
         return self._requests[request_id].tables[group]
 
+    def block_table_array(self, request_id: Hashable, group: int = 0) -> np.ndarray:
+        """The same table as an int32 array (a view that the next change of the table may move):
+        what a step copies into its description without walking a Python list."""
+        request = self._requests[request_id]
+        return request.arrays[group][:len(request.tables[group])]
+
     def state_slot(self, request_id: Hashable) -> int:
         return self._requests[request_id].slot
 
@@ -219,7 +228,8 @@ class CacheManager:
                 return False
         self._requests[request_id] = _Request(
             slot=self.slots.acquire(), tables=[[] for _ in self.groups],
-            released_blocks=[0 for _ in self.groups], reserved=wanted)
+            released_blocks=[0 for _ in self.groups], reserved=wanted,
+            arrays=[np.zeros(16, dtype=np.int32) for _ in self.groups])
         return True
 
     def ensure_capacity(self, request_id: Hashable, length: int) -> bool:
@@ -238,7 +248,14 @@ class CacheManager:
             needs.append((extra, min(extra, request.reserved[index])))
         for index, (extra, from_reservation) in enumerate(needs):
             if extra > 0:
-                request.tables[index].extend(self.groups[index].pool.allocate(extra))
+                table = request.tables[index]
+                have = len(table)
+                table.extend(self.groups[index].pool.allocate(extra))
+                if len(table) > request.arrays[index].size:
+                    grown = np.zeros(max(len(table), 2 * request.arrays[index].size), dtype=np.int32)
+                    grown[:have] = request.arrays[index][:have]
+                    request.arrays[index] = grown
+                request.arrays[index][have:len(table)] = table[have:]
                 request.reserved[index] -= from_reservation
         request.length = length
         return True
@@ -261,6 +278,7 @@ class CacheManager:
                 group.pool.free(table[request.released_blocks[index]:dead])
                 for block in range(request.released_blocks[index], dead):
                     table[block] = NULL_PAGE
+                request.arrays[index][request.released_blocks[index]:dead] = NULL_PAGE
                 request.released_blocks[index] = dead
 
     def free_request(self, request_id: Hashable) -> None:
@@ -273,6 +291,9 @@ class CacheManager:
     # -------------------------------------------------------------- invariants
     def check_invariants(self) -> None:
         """No page lost, none held twice, none both free and held.  Raises AssertionError."""
+        for request in self._requests.values():
+            for table, array in zip(request.tables, request.arrays):
+                assert array[:len(table)].tolist() == table, "a table's array copy has drifted from the table"
         for index, group in enumerate(self.groups):
             held: dict[int, Hashable] = {}
             for request_id, request in self._requests.items():

@@ -115,7 +115,7 @@ class Engine:
             if not 0 <= token < self.vocab_size:
                 raise ConfigError(f"eos token id {token} lies outside the vocabulary")
 
-        self.sampler = Sampler(self.device)
+        self.sampler = Sampler(self.device, status=self.runner.status)
         self.sequences: dict[tuple[int, int], Seq] = {}
         self.scheduler = Scheduler(self.scheduler_config, self.sequences, _RunnerCache(self.runner))
         self._requests: dict[int, _Request] = {}
@@ -250,8 +250,7 @@ class Engine:
             generators = [self._generators[i.sequence_id] for i in sampled]
             sequences = [self.sequences[i.sequence_id] for i in sampled]
             results = self.sampler.sample(logits, params, generators, [s.token_ids for s in sequences],
-                                          [s.prompt_length for s in sequences])
-            self.runner.check()
+                                          [s.prompt_length for s in sequences])    # also reads the step's status
             for item, result in zip(sampled, results):
                 if result.logprobs is not None:
                     self._logprobs.setdefault(item.sequence_id, []).append(result.logprobs)

@@ -120,11 +120,11 @@ class ModelRunner:
         slots = np.asarray([manager.state_slot(e.request_id) for e in entries], dtype=np.int32)
         tables = []
         for group in range(len(manager.groups)):
-            rows = [manager.block_table(e.request_id, group) for e in entries]
-            width = table_width or max(1, max(len(r) for r in rows))
+            rows = [manager.block_table_array(e.request_id, group) for e in entries]
+            width = table_width or max(1, max(r.size for r in rows))
             table = np.zeros((R, width), dtype=np.int32)
             for i, r in enumerate(rows):
-                table[i, :len(r)] = r
+                table[i, :r.size] = r
             tables.append(table)
         logit_tokens = np.asarray([q_start[i] + int(p) for i, e in enumerate(entries) for p in e.want], dtype=np.int32)
         decode_rows = np.asarray([i for i, n in enumerate(q_len) if n == 1], dtype=np.int32)
@@ -194,23 +194,51 @@ class ModelRunner:
 
     def _step_with_graph(self, key, entries: Sequence[StepEntry]) -> tuple[torch.Tensor, dict]:
         width = self.manager.blocks_for(self.max_seq_len)
-        arrays, info = self._describe(entries, table_width=width)
-        info["max_decode_context"] = key[1]
-        sizes = [a.size for a in arrays]
-        total = sum(sizes)
         record = self._graphs.get(key)
         if record is None:
+            arrays, info = self._describe(entries, table_width=width)
+            info["max_decode_context"] = key[1]
+            sizes = [a.size for a in arrays]
+            total = sum(sizes)
             # A small ring of pinned buffers: the host may run ahead of the device, and a buffer must not
-            # be refilled before the copy that reads it has been done.
+            # be refilled before the copy that reads it has been done.  Every buffer starts as a copy of
+            # the first step's description: what depends only on the number of rows stays as it is, and
+            # later steps rewrite the rest in place (tokens, positions, contexts, slots, block tables).
+            template = np.concatenate(arrays)
+            offsets = np.concatenate([[0], np.cumsum(sizes)]).tolist()
             record = {"host": [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(4)],
-                      "copied": [None] * 4, "turn": 0,
+                      "copied": [None] * 4, "turn": 0, "sizes": sizes, "info": info, "offsets": offsets,
                       "device": torch.empty(total, dtype=torch.int32, device=self.device), "graph": None}
+            for buffer in record["host"]:
+                buffer.numpy()[:] = template
             self._graphs[key] = record
+        sizes, offsets, total = record["sizes"], record["offsets"], record["offsets"][-1]
         turn = record["turn"]
         record["turn"] = (turn + 1) % len(record["host"])
         if record["copied"][turn] is not None:
             record["copied"][turn].synchronize()
-        np.concatenate(arrays, out=record["host"][turn].numpy())
+        # The step's values, written into their places (the order of ``_describe``: 0 tokens, 1 positions,
+        # 5 contexts, 6 slots, 9.. one block table per group).
+        manager, R = self.manager, len(entries)
+        ctx_before = [manager.computed(e.request_id) for e in entries]
+        for entry, ctx in zip(entries, ctx_before):
+            if not manager.ensure_capacity(entry.request_id, ctx + 1):
+                raise OutOfPagesError(
+                    f"no pages left for request {entry.request_id!r} ({ctx} cached + 1 new token); "
+                    f"free pages per group: {[g.pool.num_free for g in manager.groups]}")
+        host = record["host"][turn].numpy()
+        host[offsets[0]:offsets[0] + R] = [e.tokens[0] for e in entries]
+        host[offsets[1]:offsets[1] + R] = ctx_before
+        host[offsets[5]:offsets[5] + R] = ctx_before
+        slots = [manager.state_slot(e.request_id) for e in entries]
+        host[offsets[6]:offsets[6] + R] = slots
+        for group in range(len(manager.groups)):
+            table = host[offsets[9 + group]:offsets[10 + group]].reshape(R, width)
+            table[:] = 0
+            for i, entry in enumerate(entries):
+                row = manager.block_table_array(entry.request_id, group)
+                table[i, :row.size] = row
+        info = dict(record["info"], ctx_before=ctx_before, slots=slots)
         record["device"].copy_(record["host"][turn], non_blocking=True)
         event = record["copied"][turn] or torch.cuda.Event()
         event.record()

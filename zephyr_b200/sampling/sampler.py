@@ -86,9 +86,11 @@ class SamplingResult:
 class Sampler:
     """Selects tokens on the device; only the chosen ids (and the reports asked for) come back."""
 
-    def __init__(self, device: torch.device | str):
+    def __init__(self, device: torch.device | str, status: torch.Tensor | None = None):
+        """``status``: the device status word the kernels report into; one of its own unless given
+        (sharing the model runner's lets a single read per step cover both)."""
         self.device = torch.device(device)
-        self.status = ops.new_status(self.device)
+        self.status = status if status is not None else ops.new_status(self.device)
 
     def _launch(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                 generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None,
@@ -154,9 +156,12 @@ class Sampler:
         for p in params:
             p.validate(logits.shape[1])
         out = self._launch(logits, params, generators, histories, prompt_lengths)
-        ids = out.ids.tolist()
+        # One read brings the ids and the status word: every wait for the device costs the step time.
+        ids = torch.cat([out.ids, self.status]).tolist()
+        if ids[-4] != 0:
+            ops.check_status(self.status, "step")
+        del ids[-4:]
         values = out.logprobs.tolist() if out.logprobs is not None else None
-        ops.check_status(self.status, "sampling")
         results = []
         for p, at in zip(params, out.offsets):
             report = None
