@@ -1,0 +1,463 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores: tcgen05.mma
+// with both operands in shared memory and the accumulators in tensor memory (TMEM).
+//
+// One CTA = up to 128 consecutive new tokens of one request x one query head, head size 128,
+// bfloat16.  Keys and values stream through a two-stage ring of 128-position tiles.  Roles:
+//   * four loader warps copy a tile's key and value rows from the cache pages with 16-byte
+//     asynchronous copies.  A cache row's 16-byte chunks are stored permuted with the position
+//     (common.cuh: kv_swizzle); for rows of 256 bytes that permutation IS the 128-byte swizzle of
+//     the tensor core's canonical shared-memory layout, so a row is copied as it lies, its first
+//     128 bytes to the tile's first half (head dims 0..63), the rest to the second half;
+//   * one thread issues the products: S = Q K^T (M 128 queries, N 128 keys, eight steps of K = 16
+//     over the head dims; both operands K-major) into TMEM columns 0..127, and O += P V (A = the
+//     probabilities, K-major over the keys; B = the values as they lie, MN-major) into columns
+//     128..255; completion is reported to mbarriers by tcgen05.commit;
+//   * four softmax warps own the 128 query rows, one row a thread (TMEM lane = row): they read a
+//     row of S with tcgen05.ld, keep the running maximum and sum in float32 in base 2, write the
+//     probabilities as bfloat16 into shared memory in the canonical layout, and rescale O in TMEM
+//     when a row's maximum has grown by more than 2^8 since the value the row last rescaled to
+//     (the softmax does not care which shift it is given as long as it is given everywhere; the
+//     bound keeps exp2 far from overflow).
+// Math and masking as in attention_prefill.cu and attention_simt.cu (causal, lower-right aligned on
+// the cached context, optional window; probabilities rounded to bfloat16 for the second product;
+// reference: src/layer/paged_attention.cpp:118-296, deps/ttl/src/kernels/attention/attention.cu:58-170).
+// Every wait is bounded and reports instead of hanging; TMEM is given back on every path.
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace zb {
+
+constexpr int TC_BM = 128;                 // query rows per CTA
+constexpr int TC_BN = 128;                 // positions per key/value tile
+constexpr int TC_HD = 128;
+constexpr int TC_SOFTMAX_WARPS = 4;        // warps 0..3: TMEM lanes 32 w .. 32 w + 31
+constexpr int TC_MMA_WARP = 4;
+constexpr int TC_LOADER_WARPS = 4;         // warps 5..8
+constexpr int TC_THREADS = (TC_SOFTMAX_WARPS + 1 + TC_LOADER_WARPS) * 32;
+constexpr int TC_HALF_BYTES = TC_BN * 128;             // a tile's 128 rows of one 64-dim half
+constexpr int TC_TILE_BYTES = 2 * TC_HALF_BYTES;       // 32 KB: both halves
+constexpr int TC_WAIT_LIMIT = 1 << 22;
+constexpr int TC_TMEM_COLUMNS = 256;
+constexpr float TC_RESCALE_THRESHOLD = 8.0f;
+
+struct PrefillTcArgs {
+  const __nv_bfloat16* q;        // [T, nh*hd]
+  __nv_bfloat16* out;            // [T, nh*hd]
+  const __nv_bfloat16* kv_cache; // [num_pages][2][nkv][page_size][hd]
+  const int* block_table;        // [R, max_blocks]
+  const int* tile_row;           // [n_tiles]
+  const int* tile_q0;            // [n_tiles]
+  const int* row_q_start;        // [R]
+  const int* row_q_len;          // [R]
+  const int* row_ctx;            // [R]
+  int max_blocks, page_shift, num_pages, num_rows;
+  int nh, nkv, window;
+  float scale_log2;
+  int* status;
+};
+
+// ---- tcgen05 in PTX --------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(unsigned* smem_result, unsigned columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned address, unsigned columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem]; `accumulate` 0 overwrites D.
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier gets one arrival when every product issued so far by this thread is complete.
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive columns of this thread's TMEM lane (the warp's 32 lanes start at `address`'s lane).
+__device__ __forceinline__ void tmem_ld32(unsigned address, unsigned (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(address) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned address, const unsigned (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+               ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptors (64 bits): start address >> 4 in bits 0..13, leading byte
+// offset >> 4 in 16..29, stride byte offset >> 4 in 32..45, version 1 in 46..47, layout type 2
+// (128-byte swizzle) in 61..63.  Rows of 128 bytes; groups of 8 rows are 1024 bytes apart.
+//   K-major (Q, K, P): the stride offset steps over groups of 8 rows; 16 elements of K are 32 bytes
+//     further along the row.
+//   MN-major (V): a row is one position's 64 head dims; the stride offset steps over groups of 8
+//     positions (K), the leading offset over the two 64-dim halves (N).
+__device__ __forceinline__ unsigned long long desc_k_major(unsigned smem_address) {
+  return static_cast<unsigned long long>((smem_address >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ unsigned long long desc_mn_major(unsigned smem_address) {
+  return static_cast<unsigned long long>((smem_address >> 4) & 0x3FFFu) |
+         (static_cast<unsigned long long>(TC_HALF_BYTES >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: float32 accumulator (bits 4..5 = 1), bfloat16 A and B (7..9 = 1, 10..12 = 1),
+// B MN-major if asked (bit 16), N >> 3 in 17..22, M >> 4 in 24..28.
+__host__ __device__ constexpr unsigned tc_idesc(bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One row of S (this thread's TMEM lane, 128 columns) -> probabilities exp2(s * scale + neg_shift) as
+// bfloat16 in P's row `r`, their sum, and the largest raw score.  MASKED: column i counts only if
+// after < i <= last and i >= first (positions relative to the tile's first key).
+template <bool MASKED>
+__device__ __forceinline__ void softmax_pass(unsigned tmem_row, unsigned char* p_s, int r, float scale, float neg_shift,
+                                             int last, int first, int after, float& raw_max, float& row_sum) {
+#pragma unroll 1
+  for (int c4 = 0; c4 < TC_BN / 32; ++c4) {
+    unsigned v[32];
+    tmem_ld32(tmem_row + c4 * 32, v);
+    tc_wait_ld();
+    unsigned packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float raw = __uint_as_float(v[i + e]);
+        const int column = c4 * 32 + i + e;
+        const bool ok = !MASKED || (column <= last && column >= first && column > after);
+        if (ok) raw_max = fmaxf(raw_max, raw);
+        p[e] = ok ? exp2_approx(fmaf(raw, scale, neg_shift)) : 0.0f;
+        row_sum += p[e];
+      }
+      packed[i >> 1] = pack_bf16(p[0], p[1]);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int c = c4 * 4 + q4;                  // 16-byte chunk of the row: positions 8 c .. 8 c + 7
+      *reinterpret_cast<uint4*>(p_s + (c >> 3) * TC_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+          make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+paged_prefill_tc_kernel(const PrefillTcArgs a) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;                               // [2 halves][128 rows][128 bytes]
+  unsigned char* p_s = q_s + TC_TILE_BYTES;                // the same form, K = positions of the tile
+  unsigned char* kv_s = p_s + TC_TILE_BYTES;               // [2 stages][keys, values][2 halves][128][128]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(kv_s + 4 * TC_TILE_BYTES);
+  unsigned long long* kv_full = bars;          // [2] a stage's keys and values have landed (all loader threads)
+  unsigned long long* kv_empty = bars + 2;     // [2] the products that read the stage are complete
+  unsigned long long* s_full = bars + 4;       // S of the current tile is complete
+  unsigned long long* p_full = bars + 5;       // P is written, S has been read, O has been rescaled (all softmax threads)
+  unsigned long long* o_done = bars + 6;       // O += P V of the current tile is complete
+  __shared__ unsigned tmem_base_s;
+  __shared__ volatile int abort_flag;
+
+  // The tile list runs front to back through each request's new tokens and later tiles see more
+  // keys: take it back to front, long tiles first.
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
+  if (row < 0 || row >= a.num_rows) {
+    if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
+    return;
+  }
+  const int g = a.nh / a.nkv, kvh = head / g;
+  const int q_len = a.row_q_len[row], ctx = a.row_ctx[row], tok0 = a.row_q_start[row] + q0;
+  const int n_tok = min(TC_BM, q_len - q0);
+  if (n_tok <= 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int page_size = 1 << a.page_shift;
+
+  // Keys any query of this tile may see: [lo, hi).
+  const int hi = ctx + q0 + n_tok;
+  const int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
+  const int first_tile = lo / TC_BN * TC_BN;
+  const int n_tiles = (hi - first_tile + TC_BN - 1) / TC_BN;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&kv_full[0], TC_LOADER_WARPS * 32);
+    mbar_init(&kv_full[1], TC_LOADER_WARPS * 32);
+    mbar_init(&kv_empty[0], 1);
+    mbar_init(&kv_empty[1], 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, TC_SOFTMAX_WARPS * 32);
+    mbar_init(o_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == TC_MMA_WARP) {
+    tmem_alloc(&tmem_base_s, TC_TMEM_COLUMNS);
+    tmem_relinquish();
+  }
+  // The queries, one row a thread, into the canonical layout: logical 16-byte chunk c of row r goes
+  // to half c / 8, chunk (c % 8) xor (r % 8).  Rows past the tile's tokens are zero.
+  if (warp < TC_SOFTMAX_WARPS) {
+    const int r = threadIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(a.q + (static_cast<size_t>(tok0 + (r < n_tok ? r : 0)) * a.nh + head) * TC_HD);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const uint4 v = r < n_tok ? src[c] : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(q_s + (c >> 3) * TC_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    }
+    fence_proxy_async();       // the tensor core reads these stores through the asynchronous proxy
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const unsigned tmem_base = tmem_base_s;
+
+  auto wait = [&](unsigned long long* bar, unsigned parity) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < TC_WAIT_LIMIT; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 63) == 63 && abort_flag) return false;
+    }
+    return false;
+  };
+  auto give_up = [&](int where) {
+    if (!abort_flag) report(a.status, STATUS_COPY_TIMEOUT, where, tile);
+    abort_flag = 1;
+  };
+
+  if (warp > TC_MMA_WARP) {
+    // ------------------------------------------------------------------------- the loaders
+    const int lt = threadIdx.x - (TC_MMA_WARP + 1) * 32;          // 0..127
+    const int chunk = lt & 15, row_in_8 = lt >> 4;                // this thread's chunk of rows row_in_8 + 8 i
+    const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
+    const long long v_offset = static_cast<long long>(a.nkv) * page_size * TC_HD;
+    const unsigned dst_base = (chunk >> 3) * TC_HALF_BYTES + ((chunk & 7) << 4);
+    bool failed = false;
+    for (int j = 0; j < n_tiles && !failed; ++j) {
+      const int stage = j & 1;
+      if (!wait(&kv_empty[stage], ((j >> 1) & 1) ^ 1)) {
+        give_up(-1);
+        failed = true;
+        break;
+      }
+      unsigned char* k_dst = kv_s + stage * 2 * TC_TILE_BYTES + dst_base;
+      unsigned char* v_dst = k_dst + TC_TILE_BYTES;
+      const int k0 = first_tile + j * TC_BN;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int r = row_in_8 + 8 * i, pos = k0 + r;
+        bool ok = pos >= lo && pos < hi;
+        const __nv_bfloat16* src = a.kv_cache;
+        if (ok) {
+          const int block = pos >> a.page_shift;
+          const int page = block < a.max_blocks ? table[block] : -1;
+          if (page <= 0 || page >= a.num_pages) {
+            report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
+            ok = false;
+          } else {
+            src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD + chunk * 8;
+          }
+        }
+        // Rows outside [lo, hi) are filled with zeros: their scores are masked, and a zero
+        // probability times a zero value stays zero.
+        cp_async_16(k_dst + r * 128, src, ok);
+        cp_async_16(v_dst + r * 128, ok ? src + v_offset : src, ok);
+      }
+      cp_async_commit();
+      if (j >= 1) {
+        cp_async_wait<1>();            // tile j - 1 has landed
+        fence_proxy_async();
+        tc_mbar_arrive(&kv_full[(j - 1) & 1]);
+      }
+    }
+    cp_async_wait<0>();
+    if (!failed) {
+      fence_proxy_async();
+      tc_mbar_arrive(&kv_full[(n_tiles - 1) & 1]);
+    }
+  } else if (warp == TC_MMA_WARP) {
+    // ------------------------------------------------------------- the thread that issues products
+    if (lane == 0) {
+      constexpr unsigned IDESC_QK = tc_idesc(false), IDESC_PV = tc_idesc(true);
+      const unsigned q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const unsigned tmem_s = tmem_base, tmem_o = tmem_base + TC_BN;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int stage = j & 1;
+        const unsigned k_addr = smem_u32(kv_s + stage * 2 * TC_TILE_BYTES), v_addr = k_addr + TC_TILE_BYTES;
+        if (!wait(&kv_full[stage], (j >> 1) & 1)) { give_up(-2); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < TC_HD / 16; ++k) {
+          const unsigned at = (k >> 2) * TC_HALF_BYTES + (k & 3) * 32;
+          tc_mma(tmem_s, desc_k_major(q_addr + at), desc_k_major(k_addr + at), IDESC_QK, k > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        if (!wait(p_full, j & 1)) { give_up(-3); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < TC_BN / 16; ++k) {
+          const unsigned at = (k >> 2) * TC_HALF_BYTES + (k & 3) * 32;      // 16 positions along P's rows
+          tc_mma(tmem_o, desc_k_major(p_addr + at), desc_mn_major(v_addr + k * 2048), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&kv_empty[stage]);
+        tc_commit(o_done);
+      }
+    }
+  } else {
+    // --------------------------------------------------------------------------- the softmax
+    const int r = threadIdx.x;                                   // this thread's query row = its TMEM lane
+    const unsigned lane_base = static_cast<unsigned>(warp * 32) << 16;
+    const unsigned tmem_s = tmem_base + lane_base, tmem_o = tmem_base + lane_base + TC_BN;
+    const int qp = ctx + q0 + r;
+    float m_used = -INFINITY, l_run = 0.0f;
+    bool failed = false;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int k0 = first_tile + j * TC_BN;
+      // Whether to go on is decided by the warp as one: the tensor-memory instructions below are
+      // for all of its lanes together.
+      if (!__all_sync(0xffffffffu, wait(s_full, j & 1))) { give_up(-4); failed = true; break; }
+      tc_fence_after_sync();
+      // Most tiles lie wholly in every row's past (and inside its window): no mask to evaluate.
+      const bool open_tile = k0 + TC_BN - 1 <= ctx + q0 && k0 >= lo &&
+                             (a.window == 0 || k0 > ctx + q0 + TC_BM - 1 - a.window);
+      if (j > 0) {
+        // The product before this one has to be complete: it reads P and adds into O.
+        if (!__all_sync(0xffffffffu, wait(o_done, (j - 1) & 1))) { give_up(-5); failed = true; break; }
+        tc_fence_after_sync();
+      }
+      // One pass writes the probabilities with the shift the row already has and notes the row's
+      // largest score; only if that has outgrown the shift by 2^8 (always for a row's first keys) is
+      // the shift moved, O and the sum rescaled, and the pass repeated.  Per score the pass costs a
+      // maximum, a fused multiply-add, an exp2 and an addition.
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float neg_shift = m_used == -INFINITY ? 0.0f : -m_used;
+        float raw_max = -INFINITY, row_sum = 0.0f;
+        if (open_tile)
+          softmax_pass<false>(tmem_s, p_s, r, a.scale_log2, neg_shift, 0, 0, 0, raw_max, row_sum);
+        else
+          softmax_pass<true>(tmem_s, p_s, r, a.scale_log2, neg_shift, qp - k0, lo - k0,
+                             a.window > 0 ? qp - a.window - k0 : -(1 << 30), raw_max, row_sum);
+        const float row_max = raw_max * a.scale_log2;       // the scale is positive
+        const bool grow = attempt == 0 && (row_max > m_used + TC_RESCALE_THRESHOLD || (m_used == -INFINITY && row_max > -INFINITY));
+        if (!__any_sync(0xffffffffu, grow)) {
+          l_run += row_sum;
+          break;
+        }
+        // Some row of the warp moves its shift: every lane takes part in the tensor-memory
+        // instructions, rows that stay multiply by one.
+        const float factor = grow ? exp2f(m_used - row_max) : 1.0f;       // 0 for a row's first keys
+        if (grow) m_used = row_max;
+        l_run *= factor;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c4 = 0; c4 < TC_HD / 32; ++c4) {
+            unsigned v[32];
+            tmem_ld32(tmem_o + c4 * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st32(tmem_o + c4 * 32, v);
+          }
+          tc_wait_st();
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      tc_mbar_arrive(p_full);
+    }
+    if (!failed && !__all_sync(0xffffffffu, wait(o_done, (n_tiles - 1) & 1))) { give_up(-6); failed = true; }
+    if (!failed) {
+      tc_fence_after_sync();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      __nv_bfloat16* dst = a.out + (static_cast<size_t>(tok0 + r) * a.nh + head) * TC_HD;
+#pragma unroll 1
+      for (int c4 = 0; c4 < TC_HD / 32; ++c4) {
+        unsigned v[32];
+        tmem_ld32(tmem_o + c4 * 32, v);
+        tc_wait_ld();
+        if (r < n_tok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o4;
+            o4.x = pack_bf16(__uint_as_float(v[8 * q4]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+            o4.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+            o4.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+            o4.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c4 * 32 + q4 * 8) = o4;
+          }
+        }
+      }
+    }
+  }
+
+  // Everybody meets here on every path, and the warp that took the tensor memory gives it back.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == TC_MMA_WARP) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TC_TMEM_COLUMNS);
+  }
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+// 1 if zb_paged_prefill_tc takes this shape.
+ZB_API int zb_paged_prefill_tc_supported(int nh, int nkv, int hd, int dtype, int page_size) {
+  if (dtype != DTYPE_BF16 || nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh > 65535) return 0;
+  if (hd != TC_HD || page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
+  return 1;
+}
+
+// Attention of the tiles' tokens (tiles of 128 new tokens of one request) over their requests'
+// pages; writes those tokens' rows of `out`.  Arguments as zb_paged_prefill.
+ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                               int page_size, int num_pages, int num_rows, const int* tile_row, const int* tile_q0,
+                               int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
+                               int nkv, int hd, int window, float scale, int* status, void* stream) {
+  if (n_tiles < 0 || page_size <= 0 || window < 0) return ERR_BAD_ARGUMENT;
+  if (!zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_BF16, page_size)) return ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(q) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(kv_cache) % 16 != 0)
+    return ERR_BAD_ARGUMENT;
+  if (n_tiles == 0) return OK;
+  PrefillTcArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.kv_cache = static_cast<const __nv_bfloat16*>(kv_cache);
+  a.block_table = block_table; a.tile_row = tile_row; a.tile_q0 = tile_q0;
+  a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
+  a.max_blocks = max_blocks; a.num_pages = num_pages; a.num_rows = num_rows;
+  a.page_shift = 0;
+  while ((1 << a.page_shift) < page_size) ++a.page_shift;
+  a.nh = nh; a.nkv = nkv; a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  const size_t smem = 1024 + 6 * TC_TILE_BYTES + 8 * sizeof(unsigned long long);
+  if (cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return ERR_CUDA;
+  paged_prefill_tc_kernel<<<dim3(n_tiles, nh), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
+  return launch_result();
+}

@@ -70,6 +70,9 @@ _SIGNATURES = {
     "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "zb_paged_prefill_tc_supported": [c_int, c_int, c_int, c_int, c_int],
+    "zb_paged_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_gemm_small_supported": [c_int, c_int, c_int],
     "zb_gemm_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                       c_int, c_void_p],
@@ -452,6 +455,9 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     return out
 
 
+USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel for every head size (for comparisons)
+
+
 def paged_prefill_tile_tokens() -> int:
     """New tokens of one request per tile of the tensor-core prompt attention kernel."""
     return library().zb_paged_prefill_tile_tokens()
@@ -472,7 +478,11 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
-    _check(library().zb_paged_prefill(
+    # Head size 128 runs on tcgen05 with the accumulators in tensor memory; other sizes on mma.sync.
+    tensor_memory = USE_TCGEN05_PREFILL and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype],
+                                                                                     page_size))
+    kernel = library().zb_paged_prefill_tc if tensor_memory else library().zb_paged_prefill
+    _check(kernel(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
         _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), _ptr(status), _stream()), "paged_prefill")

@@ -216,11 +216,13 @@ def main(argv=None) -> int:
     parser.add_argument("--top-logprobs", type=int, default=-1)
     parser.add_argument("--sequential-pages", action="store_true",
                         help="block tables that walk the pool in order instead of a random permutation")
+    parser.add_argument("--legacy-prefill", action="store_true", help="prompt attention on mma.sync even where tcgen05 applies")
     parser.add_argument("--resident", action="store_true",
                         help="do not rotate operands: what fits in L2 is read from L2")
     args = parser.parse_args(argv)
     global RESIDENT, SEQUENTIAL_PAGES
     RESIDENT, SEQUENTIAL_PAGES = args.resident, args.sequential_pages
+    ops.USE_TCGEN05_PREFILL = not args.legacy_prefill
     if not torch.cuda.is_available():
         print("a CUDA device is needed", file=sys.stderr)
         return 2
