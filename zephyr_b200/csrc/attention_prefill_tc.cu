@@ -9,9 +9,11 @@
 //     the tensor core's canonical shared-memory layout, so a row is copied as it lies, its first
 //     128 bytes to the tile's first half (head dims 0..63), the rest to the second half;
 //   * one thread issues the products: S = Q K^T (M 128 queries, N 128 keys, eight steps of K = 16
-//     over the head dims; both operands K-major) into TMEM columns 0..127, and O += P V (A = the
-//     probabilities, K-major over the keys; B = the values as they lie, MN-major) into columns
-//     128..255; completion is reported to mbarriers by tcgen05.commit;
+//     over the head dims; both operands K-major) into TMEM columns 0..127 or 128..255 by turns, and
+//     O += P V (A = the probabilities, K-major over the keys; B = the values as they lie, MN-major)
+//     into columns 256..383; S of the next tile is issued before the wait for this tile's
+//     probabilities, so the softmax runs beside the products; completion is reported to mbarriers
+//     by tcgen05.commit;
 //   * four softmax warps own the 128 query rows, one row a thread (TMEM lane = row): they read a
 //     row of S with tcgen05.ld, keep the running maximum and sum in float32 in base 2, write the
 //     probabilities as bfloat16 into shared memory in the canonical layout, and rescale O in TMEM
@@ -22,8 +24,13 @@
 // the cached context, optional window; probabilities rounded to bfloat16 for the second product;
 // reference: src/layer/paged_attention.cpp:118-296, deps/ttl/src/kernels/attention/attention.cu:58-170).
 // Every wait is bounded and reports instead of hanging; TMEM is given back on every path.
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "common.cuh"
 #include "mma.cuh"
+#include "tma.cuh"
 
 namespace zb {
 
@@ -36,11 +43,13 @@ constexpr int TC_LOADER_WARPS = 4;         // warps 5..8
 constexpr int TC_THREADS = (TC_SOFTMAX_WARPS + 1 + TC_LOADER_WARPS) * 32;
 constexpr int TC_HALF_BYTES = TC_BN * 128;             // a tile's 128 rows of one 64-dim half
 constexpr int TC_TILE_BYTES = 2 * TC_HALF_BYTES;       // 32 KB: both halves
-constexpr int TC_WAIT_LIMIT = 1 << 22;
-constexpr int TC_TMEM_COLUMNS = 256;
+constexpr int TC_WAIT_LIMIT = 1 << 18;
+constexpr int TC_TMEM_COLUMNS = 512;        // S of even tiles, S of odd tiles, O (a power of two is asked for)
 constexpr float TC_RESCALE_THRESHOLD = 8.0f;
 
 struct PrefillTcArgs {
+  CUtensorMap cache_map;         // the cache as [rows of all pages, keys and values, heads][hd]; box: 64 dims x one page's rows (at most 128)
+  int tiled;                     // 0: no map (every tile goes through 16-byte copies)
   const __nv_bfloat16* q;        // [T, nh*hd]
   __nv_bfloat16* out;            // [T, nh*hd]
   const __nv_bfloat16* kv_cache; // [num_pages][2][nkv][page_size][hd]
@@ -165,18 +174,20 @@ __device__ __forceinline__ void softmax_pass(unsigned tmem_row, unsigned char* p
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-paged_prefill_tc_kernel(const PrefillTcArgs a) {
+paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
   unsigned char* q_s = smem;                               // [2 halves][128 rows][128 bytes]
-  unsigned char* p_s = q_s + TC_TILE_BYTES;                // the same form, K = positions of the tile
-  unsigned char* kv_s = p_s + TC_TILE_BYTES;               // [2 stages][keys, values][2 halves][128][128]
+  unsigned char* p_s = q_s + TC_TILE_BYTES;                // [2 buffers] of the same form, K = positions of the tile
+  unsigned char* kv_s = p_s + 2 * TC_TILE_BYTES;           // [2 stages][keys, values][2 halves][128][128]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(kv_s + 4 * TC_TILE_BYTES);
+  // Tile j uses entry j % 2 of every pair; on each barrier its phase is j / 2, and nobody ever
+  // waits for a phase that is more than one behind the barrier's current one.
   unsigned long long* kv_full = bars;          // [2] a stage's keys and values have landed (all loader threads)
   unsigned long long* kv_empty = bars + 2;     // [2] the products that read the stage are complete
-  unsigned long long* s_full = bars + 4;       // S of the current tile is complete
-  unsigned long long* p_full = bars + 5;       // P is written, S has been read, O has been rescaled (all softmax threads)
-  unsigned long long* o_done = bars + 6;       // O += P V of the current tile is complete
+  unsigned long long* s_full = bars + 4;       // [2] S of the tile is complete
+  unsigned long long* p_full = bars + 6;       // [2] P is written, S has been read, O has been rescaled (all softmax threads)
+  unsigned long long* o_done = bars + 8;       // [2] O += P V of the tile is complete
   __shared__ unsigned tmem_base_s;
   __shared__ volatile int abort_flag;
 
@@ -207,9 +218,11 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
     mbar_init(&kv_full[1], TC_LOADER_WARPS * 32);
     mbar_init(&kv_empty[0], 1);
     mbar_init(&kv_empty[1], 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, TC_SOFTMAX_WARPS * 32);
-    mbar_init(o_done, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], TC_SOFTMAX_WARPS * 32);
+      mbar_init(&o_done[b], 1);
+    }
     fence_barrier_init();
   }
   if (warp == TC_MMA_WARP) {
@@ -253,67 +266,113 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
     const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
     const long long v_offset = static_cast<long long>(a.nkv) * page_size * TC_HD;
     const unsigned dst_base = (chunk >> 3) * TC_HALF_BYTES + ((chunk & 7) << 4);
-    bool failed = false;
-    for (int j = 0; j < n_tiles && !failed; ++j) {
-      const int stage = j & 1;
-      if (!wait(&kv_empty[stage], ((j >> 1) & 1) ^ 1)) {
-        give_up(-1);
-        failed = true;
-        break;
+    // A tile that lies wholly inside [lo, hi) comes by TMA: one tiled copy per page and 64-dim half
+    // (the map's box is a page's rows by 64 dims, copied as they lie: the cache's own chunk
+    // permutation is already the canonical swizzle), 8 of the 32 copies from each loader warp, the
+    // bytes counted on the stage's barrier.  A tile at an edge of [lo, hi) needs rows filled with
+    // zeros (their scores are masked, and a zero probability times a zero value stays zero) and
+    // goes through 16-byte copies that can do that.
+    const int rows_per_copy = min(page_size, TC_BN), copies_per_half = TC_BN / rows_per_copy;
+    auto issue_tiled = [&](int j) {
+      const int stage = j & 1, k0 = first_tile + j * TC_BN;
+      unsigned char* stage_s = kv_s + stage * 2 * TC_TILE_BYTES;
+      if (lt == 0) mbar_arrive_expect_tx(&kv_full[stage], 2u * TC_TILE_BYTES);
+      else tc_mbar_arrive(&kv_full[stage]);
+      // copy id: (keys or values, 64-dim half, piece of the tile)
+      for (int id = (lt >> 5) * 8 + (lt & 31); (lt & 31) < 8 && id < 4 * copies_per_half; id += 32) {
+        const int kv = id / (2 * copies_per_half), half = (id / copies_per_half) & 1, piece = id % copies_per_half;
+        const int pos = k0 + piece * rows_per_copy, block = pos >> a.page_shift;
+        int page = block < a.max_blocks ? table[block] : -1;
+        if (page <= 0 || page >= a.num_pages) {
+          report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
+          page = 0;                     // the bytes must arrive all the same
+        }
+        const int cache_row = ((page * 2 + kv) * a.nkv + kvh) * page_size + (pos & (page_size - 1));
+        tiled_copy_2d_g2s(stage_s + kv * TC_TILE_BYTES + half * TC_HALF_BYTES + piece * rows_per_copy * 128, &a.cache_map,
+                          half * 64, cache_row, &kv_full[stage]);
       }
+    };
+    auto issue_plain = [&](int j) {
+      const int stage = j & 1;
       unsigned char* k_dst = kv_s + stage * 2 * TC_TILE_BYTES + dst_base;
       unsigned char* v_dst = k_dst + TC_TILE_BYTES;
       const int k0 = first_tile + j * TC_BN;
-#pragma unroll 4
+      // The page ids of this thread's 16 rows first, all at once: a lookup per copy would put the
+      // table's latency in front of every copy.
+      int page[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int pos = k0 + row_in_8 + 8 * i, block = pos >> a.page_shift;
+        page[i] = pos >= lo && pos < hi ? (block < a.max_blocks ? table[block] : -1) : 0;
+      }
+#pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int r = row_in_8 + 8 * i, pos = k0 + r;
         bool ok = pos >= lo && pos < hi;
         const __nv_bfloat16* src = a.kv_cache;
         if (ok) {
-          const int block = pos >> a.page_shift;
-          const int page = block < a.max_blocks ? table[block] : -1;
-          if (page <= 0 || page >= a.num_pages) {
-            report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
+          if (page[i] <= 0 || page[i] >= a.num_pages) {
+            report(a.status, STATUS_PAGE_OUT_OF_RANGE, page[i], tok0);
             ok = false;
           } else {
-            src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD + chunk * 8;
+            src += ((static_cast<long long>(page[i]) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD + chunk * 8;
           }
         }
-        // Rows outside [lo, hi) are filled with zeros: their scores are masked, and a zero
-        // probability times a zero value stays zero.
         cp_async_16(k_dst + r * 128, src, ok);
         cp_async_16(v_dst + r * 128, ok ? src + v_offset : src, ok);
       }
       cp_async_commit();
-      if (j >= 1) {
-        cp_async_wait<1>();            // tile j - 1 has landed
-        fence_proxy_async();
-        tc_mbar_arrive(&kv_full[(j - 1) & 1]);
+      cp_async_wait<0>();
+      fence_proxy_async();           // the tensor core reads what the copies wrote through the asynchronous proxy
+      tc_mbar_arrive(&kv_full[stage]);
+    };
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!wait(&kv_empty[j & 1], ((j >> 1) & 1) ^ 1)) {
+        give_up(-1);
+        break;
       }
-    }
-    cp_async_wait<0>();
-    if (!failed) {
-      fence_proxy_async();
-      tc_mbar_arrive(&kv_full[(n_tiles - 1) & 1]);
+      const int k0 = first_tile + j * TC_BN;
+      if (a.tiled && k0 >= lo && k0 + TC_BN <= hi) issue_tiled(j); else issue_plain(j);
     }
   } else if (warp == TC_MMA_WARP) {
     // ------------------------------------------------------------- the thread that issues products
     if (lane == 0) {
       constexpr unsigned IDESC_QK = tc_idesc(false), IDESC_PV = tc_idesc(true);
-      const unsigned q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      const unsigned tmem_s = tmem_base, tmem_o = tmem_base + TC_BN;
-      for (int j = 0; j < n_tiles; ++j) {
+      const unsigned q_addr = smem_u32(q_s);
+      const unsigned tmem_o = tmem_base + 2 * TC_BN;
+      // S of tile j + 1 is issued before the wait for tile j's probabilities, so that the softmax of
+      // one tile runs beside the products of its neighbours.
+      auto issue_scores = [&](int j) {          // the tile's keys have landed
         const int stage = j & 1;
-        const unsigned k_addr = smem_u32(kv_s + stage * 2 * TC_TILE_BYTES), v_addr = k_addr + TC_TILE_BYTES;
-        if (!wait(&kv_full[stage], (j >> 1) & 1)) { give_up(-2); break; }
+        const unsigned k_addr = smem_u32(kv_s + stage * 2 * TC_TILE_BYTES);
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < TC_HD / 16; ++k) {
           const unsigned at = (k >> 2) * TC_HALF_BYTES + (k & 3) * 32;
-          tc_mma(tmem_s, desc_k_major(q_addr + at), desc_k_major(k_addr + at), IDESC_QK, k > 0 ? 1u : 0u);
+          tc_mma(tmem_base + stage * TC_BN, desc_k_major(q_addr + at), desc_k_major(k_addr + at), IDESC_QK, k > 0 ? 1u : 0u);
         }
-        tc_commit(s_full);
-        if (!wait(p_full, j & 1)) { give_up(-3); break; }
+        tc_commit(&s_full[stage]);
+      };
+      // S of the next tile is issued as soon as its keys are there, before this tile's second
+      // product if they come first: the softmax of one tile then runs beside the products of its
+      // neighbours.  Neither product ever waits for something only the other can bring.
+      int scores_issued = 0;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int stage = j & 1;
+        const unsigned p_addr = smem_u32(p_s + stage * TC_TILE_BYTES);
+        const unsigned v_addr = smem_u32(kv_s + stage * 2 * TC_TILE_BYTES) + TC_TILE_BYTES;
+        bool have_p = false;
+        for (int polls = 0; !have_p; ++polls) {
+          if (scores_issued <= j + 1 && scores_issued < n_tiles &&
+              mbar_try_wait(&kv_full[scores_issued & 1], (scores_issued >> 1) & 1)) {
+            issue_scores(scores_issued++);
+            continue;
+          }
+          if (scores_issued > j && mbar_try_wait(&p_full[stage], (j >> 1) & 1)) have_p = true;
+          else if (polls > TC_WAIT_LIMIT || ((polls & 63) == 63 && abort_flag)) break;
+        }
+        if (!have_p) { give_up(-3); ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < TC_BN / 16; ++k) {
@@ -321,14 +380,14 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
           tc_mma(tmem_o, desc_k_major(p_addr + at), desc_mn_major(v_addr + k * 2048), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(&kv_empty[stage]);
-        tc_commit(o_done);
+        tc_commit(&o_done[stage]);
       }
     }
   } else {
     // --------------------------------------------------------------------------- the softmax
     const int r = threadIdx.x;                                   // this thread's query row = its TMEM lane
     const unsigned lane_base = static_cast<unsigned>(warp * 32) << 16;
-    const unsigned tmem_s = tmem_base + lane_base, tmem_o = tmem_base + lane_base + TC_BN;
+    const unsigned tmem_o = tmem_base + lane_base + 2 * TC_BN;
     const int qp = ctx + q0 + r;
     float m_used = -INFINITY, l_run = 0.0f;
     bool failed = false;
@@ -336,15 +395,17 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
       const int k0 = first_tile + j * TC_BN;
       // Whether to go on is decided by the warp as one: the tensor-memory instructions below are
       // for all of its lanes together.
-      if (!__all_sync(0xffffffffu, wait(s_full, j & 1))) { give_up(-4); failed = true; break; }
+      const int buffer = j & 1;
+      const unsigned tmem_s = tmem_base + lane_base + buffer * TC_BN;
+      unsigned char* p_tile = p_s + buffer * TC_TILE_BYTES;
+      if (!__all_sync(0xffffffffu, wait(&s_full[buffer], (j >> 1) & 1))) { give_up(-4); failed = true; break; }
       tc_fence_after_sync();
       // Most tiles lie wholly in every row's past (and inside its window): no mask to evaluate.
       const bool open_tile = k0 + TC_BN - 1 <= ctx + q0 && k0 >= lo &&
                              (a.window == 0 || k0 > ctx + q0 + TC_BM - 1 - a.window);
-      if (j > 0) {
-        // The product before this one has to be complete: it reads P and adds into O.
-        if (!__all_sync(0xffffffffu, wait(o_done, (j - 1) & 1))) { give_up(-5); failed = true; break; }
-        tc_fence_after_sync();
+      if (j >= 2) {
+        // This tile's P buffer was read by the product two tiles back.
+        if (!__all_sync(0xffffffffu, wait(&o_done[buffer], ((j - 2) >> 1) & 1))) { give_up(-5); failed = true; break; }
       }
       // One pass writes the probabilities with the shift the row already has and notes the row's
       // largest score; only if that has outgrown the shift by 2^8 (always for a row's first keys) is
@@ -354,9 +415,9 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
         const float neg_shift = m_used == -INFINITY ? 0.0f : -m_used;
         float raw_max = -INFINITY, row_sum = 0.0f;
         if (open_tile)
-          softmax_pass<false>(tmem_s, p_s, r, a.scale_log2, neg_shift, 0, 0, 0, raw_max, row_sum);
+          softmax_pass<false>(tmem_s, p_tile, r, a.scale_log2, neg_shift, 0, 0, 0, raw_max, row_sum);
         else
-          softmax_pass<true>(tmem_s, p_s, r, a.scale_log2, neg_shift, qp - k0, lo - k0,
+          softmax_pass<true>(tmem_s, p_tile, r, a.scale_log2, neg_shift, qp - k0, lo - k0,
                              a.window > 0 ? qp - a.window - k0 : -(1 << 30), raw_max, row_sum);
         const float row_max = raw_max * a.scale_log2;       // the scale is positive
         const bool grow = attempt == 0 && (row_max > m_used + TC_RESCALE_THRESHOLD || (m_used == -INFINITY && row_max > -INFINITY));
@@ -370,6 +431,10 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
         if (grow) m_used = row_max;
         l_run *= factor;
         if (j > 0) {
+          // O is touched only between the product of the tile before, which has to be complete, and
+          // this tile's product, which waits for this warp's arrival below.
+          if (!__all_sync(0xffffffffu, wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1))) { give_up(-7); failed = true; break; }
+          tc_fence_after_sync();
 #pragma unroll 1
           for (int c4 = 0; c4 < TC_HD / 32; ++c4) {
             unsigned v[32];
@@ -382,11 +447,12 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
           tc_wait_st();
         }
       }
+      if (failed) break;
       fence_proxy_async();
       tc_fence_before_sync();
-      tc_mbar_arrive(p_full);
+      tc_mbar_arrive(&p_full[buffer]);
     }
-    if (!failed && !__all_sync(0xffffffffu, wait(o_done, (n_tiles - 1) & 1))) { give_up(-6); failed = true; }
+    if (!failed && !__all_sync(0xffffffffu, wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1))) { give_up(-6); failed = true; }
     if (!failed) {
       tc_fence_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -420,6 +486,33 @@ paged_prefill_tc_kernel(const PrefillTcArgs a) {
   }
 }
 
+// The cache [pages][2][nkv][page_size][hd] as rows of hd bfloat16; a box is 64 head dims by one
+// page's rows (at most a tile's 128).  Maps are kept: the same caches come back every step.
+bool cache_tensor_map(const __nv_bfloat16* cache, long long rows, int hd, int box_rows, CUtensorMap* out) {
+  static std::mutex mutex;
+  static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> kept;
+  std::lock_guard<std::mutex> lock(mutex);
+  const auto key = std::make_tuple(static_cast<const void*>(cache), rows, hd, box_rows);
+  const auto found = kept.find(key);
+  if (found != kept.end()) {
+    *out = found->second;
+    return true;
+  }
+  const EncodeTiled encode = tensor_map_encoder();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  if (encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(cache), dims, strides, box, element_strides,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (kept.size() > 4096) kept.clear();
+  kept.emplace(key, *out);
+  return true;
+}
+
 }  // namespace zb
 
 using namespace zb;
@@ -444,6 +537,10 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
     return ERR_BAD_ARGUMENT;
   if (n_tiles == 0) return OK;
   PrefillTcArgs a;
+  const long long cache_rows = static_cast<long long>(num_pages) * 2 * nkv * page_size;
+  a.tiled = cache_rows < (1LL << 31) &&
+            cache_tensor_map(static_cast<const __nv_bfloat16*>(kv_cache), cache_rows, hd, page_size < TC_BN ? page_size : TC_BN,
+                             &a.cache_map) ? 1 : 0;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.kv_cache = static_cast<const __nv_bfloat16*>(kv_cache);
@@ -455,7 +552,7 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
   a.nh = nh; a.nkv = nkv; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
-  const size_t smem = 1024 + 6 * TC_TILE_BYTES + 8 * sizeof(unsigned long long);
+  const size_t smem = 1024 + 7 * TC_TILE_BYTES + 10 * sizeof(unsigned long long);
   if (cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
   paged_prefill_tc_kernel<<<dim3(n_tiles, nh), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);

@@ -29,14 +29,13 @@
 // activation in float32, one rounding to bfloat16 where a tensor is stored
 // (reference: src/model/causal_lm/qwen3.cpp:17-88, src/layer/mlp.cpp:16-36,
 // src/layer/normalization.cpp:10-18).
-#include <cuda.h>
-
 #include <map>
 #include <mutex>
 #include <tuple>
 
 #include "common.cuh"
 #include "mma.cuh"
+#include "tma.cuh"
 
 namespace zb {
 
@@ -500,25 +499,6 @@ size_t chain_smem_bytes(int slots, int xs_rows, int xs_row_bytes) {
 }
 
 // ---- tensor maps -------------------------------------------------------------------------------
-// The driver's encoder is looked up through the runtime, so that nothing links against the driver.
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled tensor_map_encoder() {
-  static EncodeTiled encoder = [] {
-    void* entry = nullptr;
-    cudaDriverEntryPointQueryResult found;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess ||
-        found != cudaDriverEntryPointSuccess) {
-      (void)cudaGetLastError();
-      return static_cast<EncodeTiled>(nullptr);
-    }
-    return reinterpret_cast<EncodeTiled>(entry);
-  }();
-  return encoder;
-}
-
 // W [N, K] (K a multiple of 64, rows ldw apart) seen as [N][K / 64][64]: a box of 8 x 16 x 64 is
 // 8 rows by 1024 columns.  Maps are kept: the same weights come back every step.
 bool weight_tensor_map(const __nv_bfloat16* w, int N, int K, long long ldw, CUtensorMap* out) {
