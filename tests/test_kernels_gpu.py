@@ -437,6 +437,71 @@ def test_paged_prefill_tensor_core(ops, cuda_device, nh, nkv, hd, page, window):
         cursor += n
 
 
+@pytest.mark.parametrize("page,window", [(8, 0), (16, 0), (32, 300), (64, 0), (128, 129), (256, 0)])
+def test_paged_prefill_tensor_memory(ops, cuda_device, page, window):
+    """The tcgen05 kernel (head size 128) at every page size it takes: portions that start and end
+    inside tiles of 128 keys, contexts of several tiles (interior tiles arrive by TMA, edge tiles
+    by 16-byte copies with zero fill; freed and unused cache rows hold NaN), a window that ends
+    inside a tile, and the same inputs through the mma.sync kernel."""
+    nh, nkv, hd, dtype = 6, 2, 128, torch.bfloat16
+    q_lens = [130, 2, 257, 128, 1, 40]
+    ctx = [0, 700, 383, 1, 9, 1000]
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 900 + page)
+    tile_row, tile_q0 = tiles_for(q_lens, ops.paged_prefill_tile_tokens(), cuda_device, only_multi=True)
+    outs = []
+    for tensor_memory in (True, False):
+        ops.USE_TCGEN05_PREFILL = tensor_memory
+        try:
+            status = ops.new_status(cuda_device)
+            out = torch.full_like(q, float("nan"))
+            ops.paged_prefill(q, cache, meta["table"], tile_row, tile_q0, meta["row_q_start"], meta["row_q_len"],
+                              meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status, out=out)
+            ops.check_status(status)
+        finally:
+            ops.USE_TCGEN05_PREFILL = True
+        outs.append(out.double().cpu().view(-1, nh, hd))
+    cursor = 0
+    for r, n in enumerate(q_lens):
+        if n > 1:
+            expected = ref_attention_row(qs[r].double(), Ks[r].double(), Vs[r].double(), ctx[r], n, window, nh, nkv)
+            for got, name in zip(outs, ("tcgen05", "mma.sync")):
+                assert torch.isfinite(got[cursor:cursor + n]).all(), f"{name} row {r}"
+                error = (got[cursor:cursor + n] - expected).abs().max()
+                assert error <= tol(dtype, 2.0), f"{name} row {r} (context {ctx[r]}, {n} new): {error}"
+        cursor += n
+
+
+def test_paged_prefill_tensor_memory_growing_scores(ops, cuda_device):
+    """Scores that grow along the context by far more than 2^8 from tile to tile: every tile moves
+    the rows' shift and rescales the output kept in tensor memory."""
+    nh, nkv, hd, page, dtype = 2, 1, 128, 16, torch.bfloat16
+    n = 640
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, [n], [0], 77)
+    direction = torch.ones(hd) / math.sqrt(hd)
+    K = Ks[0].clone()
+    for p in range(n):
+        K[p, 0] = (direction * (0.05 * p)).to(dtype)                  # key p scores 0.05 p * |q|: about 12 per 128 keys in base 2
+    Ks[0] = K
+    qs[0][:] = (direction * 4.0 * math.sqrt(hd)).to(dtype)
+    # rebuild the cache and the queries with the edited tensors
+    from zephyr_b200.kernels.ops import kv_row_permutation
+    table = meta["table"].cpu()
+    for p in range(n):
+        inverse = torch.argsort(kv_row_permutation(p, hd, dtype))
+        cache[int(table[0, p // page]), 0, :, p % page] = K[p][:, inverse].to(cuda_device)
+    q = qs[0].reshape(-1, nh * hd).to(cuda_device)
+    tile_row, tile_q0 = tiles_for([n], ops.paged_prefill_tile_tokens(), cuda_device, only_multi=True)
+    status = ops.new_status(cuda_device)
+    out = torch.full_like(q, float("nan"))
+    ops.paged_prefill(q, cache, meta["table"], tile_row, tile_q0, meta["row_q_start"], meta["row_q_len"], meta["row_ctx"],
+                      nh, nkv, hd, 0, 1 / math.sqrt(hd), status, out=out)
+    ops.check_status(status)
+    expected = ref_attention_row(qs[0].double(), Ks[0].double(), Vs[0].double(), 0, n, 0, nh, nkv)
+    got = out.double().cpu().view(-1, nh, hd)
+    assert torch.isfinite(got).all()
+    assert (got - expected).abs().max() <= tol(dtype, 2.0)
+
+
 def test_paged_prefill_far_key_and_window_edge(ops, cuda_device):
     nh, nkv, hd, page = 4, 2, 64, 16
     for window, key, visible in ((0, 3, True), (50, 700 - 50 + 1, True), (50, 700 - 50, False)):
