@@ -25,6 +25,8 @@
 // scheme), except where that kernel is not exact: no epsilon is added to the denominator, and
 // partial results stay float32.  Probabilities are rounded to bfloat16 for the second product, as
 // the reference does (paged_decode.cu:289).  Every wait is bounded and reports instead of hanging.
+#include <algorithm>
+
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -37,6 +39,7 @@ constexpr int DEC_TILE = 32;             // positions per tile: one consumer war
 constexpr int DEC_MAX_GROUP = 16;        // query heads per key/value head that fit one MMA tile
 constexpr int DEC_WAIT_LIMIT = 1 << 24;  // polls of an mbarrier before a warp gives up and reports
 constexpr int DEC_SMEM_BUDGET = 227 * 1024 - 1024;
+constexpr int DEC_MAX_BALANCED_GRID = 256;  // CTAs of a launch with balanced items: the scratch holds two slots for each
 
 struct DecodeArgs {
   const __nv_bfloat16* q;        // [T, nh*hd]
@@ -46,8 +49,8 @@ struct DecodeArgs {
   const int* rows;               // [n_rows] request rows that decode one token
   const int* row_q_start;        // [R]
   const int* row_ctx;            // [R] tokens in the cache before this step (the new token's position)
-  float* part_o;                 // [n_rows, nh, max_splits, hd]
-  float* part_ml;                // [n_rows, nh, max_splits, 2]
+  float* part_o;                 // [slots][g][hd]: partial outputs, one slot per item that is not its pair's only one
+  float* part_ml;                // [slots][g][2]: their maxima and sums
   int* counters;                 // [n_rows, nkv] zero on entry, zero again on exit
   int max_blocks, page_shift, num_pages, num_rows, n_rows;
   int nh, nkv, window, split_size, max_splits, ring_slots, item_pages;
@@ -55,30 +58,109 @@ struct DecodeArgs {
   int* status;
 };
 
-// Which positions split `s` of a row covers: [begin, end), empty if begin >= end.
+// How a (request, key/value head) pair's context is cut into work items.
+//   Fixed splits (split_size > 0): item = (row, head, split of split_size positions); CTAs take items in
+//     turn.  A pair's partial results lie in slots pair * max_splits + split.
+//   Balanced (split_size == 0): the tiles of all pairs, laid end to end, are cut into ranges of equal
+//     length, one range per CTA; an item is the part of a pair inside a range.  A CTA's range may
+//     begin inside one pair and end inside another, so a range owns two slots: slot 0 for a pair that
+//     began before the range, slot 1 for one that began inside it and goes on.  Every CTA streams
+//     the same number of tiles whatever the batch and the context lengths are.
+struct DecodeItem {
+  int r, row, kvh, ctx_total, begin, end, first_tile, n_tiles;
+  int n_parts;          // items the pair is cut into (1: this item's result is the pair's result)
+  int my_slot;          // where this item's partial result goes
+  int merge_first;      // fixed: slot of the pair's first item; balanced: the pair's first range
+  long long pair_start; // balanced: the pair's first tile in the global order
+};
+
+struct ItemWalker {
+  int next;             // fixed: the next item number; balanced: the next range
+  int tile, range, range_end, r;
+};
+
+// Positions [begin, end) of split `s` of a row; empty if begin >= end.
 __device__ __forceinline__ void split_range(int ctx_total, int window, int split_size, int s, int& begin, int& end) {
   const int lo = window > 0 ? max(0, ctx_total - window) : 0;   // the query sits at ctx_total - 1
   begin = max(s * split_size, lo);
   end = min((s + 1) * split_size, ctx_total);
 }
 
-// One work item, as producer and consumers both derive it from the item's number.
-struct DecodeItem {
-  int r, row, kvh, split, ctx_total, begin, end, first_tile, n_tiles;
-};
+__device__ __forceinline__ int balanced_slot(long long pair_start, int range, int per_range) {
+  return range * 2 + (pair_start < static_cast<long long>(range) * per_range ? 0 : 1);
+}
 
-__device__ __forceinline__ bool decode_item(const DecodeArgs& a, int id, DecodeItem& it) {
-  it.split = id % a.max_splits;
-  it.kvh = (id / a.max_splits) % a.nkv;
-  it.r = id / (a.max_splits * a.nkv);
-  it.row = a.rows[it.r];
-  if (it.row < 0 || it.row >= a.num_rows) return false;        // reported once, by the consumers
-  it.ctx_total = a.row_ctx[it.row] + 1;
-  split_range(it.ctx_total, a.window, a.split_size, it.split, it.begin, it.end);
-  if (it.begin >= it.end) return false;
-  it.first_tile = it.begin / DEC_TILE * DEC_TILE;
-  it.n_tiles = (it.end - it.first_tile + DEC_TILE - 1) / DEC_TILE;
-  return true;
+__device__ __forceinline__ void walker_init(ItemWalker& w) {
+  w.next = blockIdx.x;
+  w.tile = w.range_end = w.range = w.r = 0;
+}
+
+// The CTA's next item, the same sequence for every warp that asks.  `prefix` (balanced only): the
+// first global tile of every row, n_rows + 1 entries; `per_range`: tiles per range.
+__device__ __forceinline__ bool next_item(const DecodeArgs& a, const int* prefix, int per_range, ItemWalker& w,
+                                          DecodeItem& it) {
+  if (a.split_size > 0) {
+    const int n_items = a.n_rows * a.nkv * a.max_splits;
+    while (w.next < n_items) {
+      const int id = w.next;
+      w.next += gridDim.x;
+      const int split = id % a.max_splits;
+      it.kvh = (id / a.max_splits) % a.nkv;
+      it.r = id / (a.max_splits * a.nkv);
+      it.row = a.rows[it.r];
+      if (it.row < 0 || it.row >= a.num_rows) continue;            // reported when the kernel starts
+      it.ctx_total = a.row_ctx[it.row] + 1;
+      split_range(it.ctx_total, a.window, a.split_size, split, it.begin, it.end);
+      if (it.begin >= it.end) continue;
+      it.first_tile = it.begin / DEC_TILE * DEC_TILE;
+      it.n_tiles = (it.end - it.first_tile + DEC_TILE - 1) / DEC_TILE;
+      const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
+      const int first_split = lo / a.split_size, last_split = (it.ctx_total - 1) / a.split_size;
+      it.n_parts = last_split - first_split + 1;
+      it.merge_first = (it.r * a.nkv + it.kvh) * a.max_splits + first_split;
+      it.my_slot = (it.r * a.nkv + it.kvh) * a.max_splits + split;
+      it.pair_start = 0;
+      return true;
+    }
+    return false;
+  }
+  const int total = prefix[a.n_rows];
+  while (true) {
+    if (w.tile >= w.range_end) {
+      const long long begin = static_cast<long long>(w.next) * per_range;
+      if (begin >= total) return false;
+      w.range = w.next;
+      w.next += gridDim.x;
+      w.tile = static_cast<int>(begin);
+      w.range_end = min(total, w.tile + per_range);
+    }
+    while (prefix[w.r + 1] <= w.tile) ++w.r;                        // ranges only move forward
+    const int row_tiles = (prefix[w.r + 1] - prefix[w.r]) / a.nkv;
+    it.r = w.r;
+    it.row = a.rows[w.r];
+    it.kvh = (w.tile - prefix[w.r]) / row_tiles;
+    it.pair_start = prefix[w.r] + it.kvh * row_tiles;
+    const int seg_end = min(w.range_end, static_cast<int>(it.pair_start) + row_tiles);
+    it.ctx_total = a.row_ctx[it.row] + 1;
+    const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
+    const int first = lo / DEC_TILE + (w.tile - static_cast<int>(it.pair_start));   // the item's first tile of the row
+    it.n_tiles = seg_end - w.tile;
+    it.first_tile = first * DEC_TILE;
+    it.begin = max(lo, it.first_tile);
+    it.end = min(it.ctx_total, (first + it.n_tiles) * DEC_TILE);
+    const int first_range = static_cast<int>(it.pair_start / per_range);
+    const int last_range = static_cast<int>((it.pair_start + row_tiles - 1) / per_range);
+    it.n_parts = last_range - first_range + 1;
+    it.merge_first = first_range;
+    it.my_slot = balanced_slot(it.pair_start, w.range, per_range);
+    w.tile = seg_end;
+    return true;
+  }
+}
+
+// Slot of the k-th of the pair's partial results.
+__device__ __forceinline__ int part_slot(const DecodeArgs& a, const DecodeItem& it, int k, int per_range) {
+  return a.split_size > 0 ? it.merge_first + k : balanced_slot(it.pair_start, it.merge_first + k, per_range);
 }
 
 __device__ __forceinline__ void consumer_barrier() {      // the 128 consumer threads only
@@ -109,6 +191,12 @@ paged_decode_kernel(const DecodeArgs a) {
   unsigned long long* qfull = empty + R;
   unsigned long long* qempty = qfull + 2;
   int* page_ids_all = reinterpret_cast<int*>(qempty + 2);     // the current item's pages, one list per producer warp
+  int* prefix = page_ids_all + DEC_PRODUCERS * a.item_pages;  // balanced items: every row's first global tile, n_rows + 1
+  // How many fillings of each slot have been read to the end.  Several producers and consumers
+  // run at their own pace, and an mbarrier's parity tells apart two successive phases only: nobody
+  // waits for a slot's n-th filling, or for its release, before the count says the fillings before
+  // it are done with.
+  volatile int* consumed = prefix + a.n_rows + 2;
   __shared__ int is_last;
   __shared__ volatile int abort_flag;      // set by the first warp whose wait ran out; every later wait gives up at once
 
@@ -125,13 +213,34 @@ paged_decode_kernel(const DecodeArgs a) {
   for (int e = threadIdx.x; e < 2 * 16 * KROW / 8; e += DEC_THREADS)
     reinterpret_cast<uint4*>(qbuf)[e] = make_uint4(0, 0, 0, 0);      // rows past the group stay zero for good
   if (threadIdx.x == 0) {
-    for (int s = 0; s < R; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < R; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); consumed[s] = 0; }
     for (int s = 0; s < 2; ++s) { mbar_init(&qfull[s], 1); mbar_init(&qempty[s], DEC_CONSUMERS); }
     fence_barrier_init();
   }
+  // Rows that do not exist are reported once and own no tiles.
+  for (int r = threadIdx.x; r < a.n_rows; r += DEC_THREADS) {
+    const int row = a.rows[r];
+    const bool ok = row >= 0 && row < a.num_rows;
+    if (!ok) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, r);
+    if (a.split_size == 0) {
+      int tiles = 0;
+      if (ok) {
+        const int ctx_total = a.row_ctx[row] + 1;
+        const int lo = a.window > 0 ? max(0, ctx_total - a.window) : 0;
+        tiles = (ctx_total + DEC_TILE - 1) / DEC_TILE - lo / DEC_TILE;
+      }
+      prefix[r + 1] = tiles * a.nkv;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && a.split_size == 0) {
+    prefix[0] = 0;
+    for (int r = 0; r < a.n_rows; ++r) prefix[r + 1] += prefix[r];
+  }
   __syncthreads();
   fence_proxy_async();
-  const int n_items = a.n_rows * a.nkv * a.max_splits;
+  // Balanced items: as many tiles per range as spread all tiles evenly over the CTAs.
+  const int per_range = a.split_size == 0 ? max(1, (prefix[a.n_rows] + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) : 0;
   const int page_size = 1 << a.page_shift;
   const long long page_stride = 2LL * a.nkv * page_size * HD;
 
@@ -142,9 +251,10 @@ paged_decode_kernel(const DecodeArgs a) {
     const int me = warp - DEC_CONSUMERS;
     int* page_ids = page_ids_all + me * a.item_pages;
     int tile_seq = 0, item_seq = 0;
-    for (int id = blockIdx.x; id < n_items; id += gridDim.x) {
-      DecodeItem it;
-      if (!decode_item(a, id, it)) continue;
+    ItemWalker walker;
+    walker_init(walker);
+    DecodeItem it;
+    while (next_item(a, prefix, per_range, walker, it)) {
       const int qb = item_seq & 1;
       if (me == 0) {
         if (!wait(&qempty[qb], ((item_seq >> 1) & 1) ^ 1)) {
@@ -175,8 +285,10 @@ paged_decode_kernel(const DecodeArgs a) {
       const int n_runs = DEC_TILE / run_rows;
       for (int t = 0; t < it.n_tiles; ++t, ++tile_seq) {
         if (tile_seq % DEC_PRODUCERS != me) continue;
-        const int slot = tile_seq % R;
-        if (!wait(&empty[slot], ((tile_seq / R) & 1) ^ 1)) {
+        const int slot = tile_seq % R, filling = tile_seq / R;
+        bool released = consumed[slot] >= filling;
+        for (int i = 0; !released && i < DEC_WAIT_LIMIT && !abort_flag; ++i) released = consumed[slot] >= filling;
+        if (!released || !wait(&empty[slot], (filling & 1) ^ 1)) {
           if (lane == 0) report(a.status, STATUS_COPY_TIMEOUT, -2, it.row);
           abort_flag = 1;
           return;
@@ -215,12 +327,10 @@ paged_decode_kernel(const DecodeArgs a) {
   const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
   const int ctid = threadIdx.x;                       // 0..127 among the consumers
   int tile_base = 0, item_seq = 0;
-  for (int id = blockIdx.x; id < n_items; id += gridDim.x) {
-    DecodeItem it;
-    if (!decode_item(a, id, it)) {
-      if (ctid == 0 && (it.row < 0 || it.row >= a.num_rows)) report(a.status, STATUS_ROW_OUT_OF_RANGE, it.row, it.r);
-      continue;
-    }
+  ItemWalker walker;
+  walker_init(walker);
+  DecodeItem it;
+  while (next_item(a, prefix, per_range, walker, it)) {
     const int qb = item_seq & 1;
     // A consumer whose wait runs out reports, raises the abort flag and keeps walking the items
     // without computing: the consumer barriers below need all four warps to the very end.
@@ -243,8 +353,10 @@ paged_decode_kernel(const DecodeArgs a) {
     for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
 
     for (int j = warp; j < it.n_tiles; j += DEC_CONSUMERS) {
-      const int seq = tile_base + j, slot = seq % R;
-      if (abort_flag || !wait(&full[slot], (seq / R) & 1)) {
+      const int seq = tile_base + j, slot = seq % R, filling = seq / R;
+      bool in_turn = consumed[slot] == filling;
+      for (int i = 0; !in_turn && i < DEC_WAIT_LIMIT && !abort_flag; ++i) in_turn = consumed[slot] == filling;
+      if (abort_flag || !in_turn || !wait(&full[slot], filling & 1)) {
         if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, j, it.row);
         abort_flag = 1;
         break;
@@ -338,7 +450,10 @@ paged_decode_kernel(const DecodeArgs a) {
         }
       }
       __syncwarp();            // every lane has read the tile
-      if (lane == 0) mbar_arrive(&empty[slot]);
+      if (lane == 0) {
+        consumed[slot] = filling + 1;
+        mbar_arrive(&empty[slot]);
+      }
     }
     tile_base += it.n_tiles;
 
@@ -362,9 +477,7 @@ paged_decode_kernel(const DecodeArgs a) {
     }
     consumer_barrier();
 
-    const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
-    const int first_split = lo / a.split_size, last_split = (it.ctx_total - 1) / a.split_size;
-    const bool alone = first_split == last_split;
+    const bool alone = it.n_parts == 1;
     const size_t out_base = (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g) * HD;
     for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
       const int h = e / HD, d = e - h * HD;
@@ -382,7 +495,7 @@ paged_decode_kernel(const DecodeArgs a) {
       if (alone) {               // the only split of its row: this is the result
         a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
       } else {
-        const size_t slot = (static_cast<size_t>(it.r) * a.nh + static_cast<size_t>(it.kvh) * g + h) * a.max_splits + it.split;
+        const size_t slot = static_cast<size_t>(it.my_slot) * g + h;
         a.part_o[slot * HD + d] = acc;
         if (d == 0) {
           a.part_ml[slot * 2] = mx;
@@ -397,21 +510,22 @@ paged_decode_kernel(const DecodeArgs a) {
     consumer_barrier();
     if (ctid == 0) {
       const int arrived = atomicAdd(&a.counters[it.r * a.nkv + it.kvh], 1);
-      is_last = arrived == last_split - first_split;
+      is_last = arrived == it.n_parts - 1;
     }
     consumer_barrier();
     if (!is_last) continue;
     __threadfence();
     for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
       const int h = e / HD, d = e - h * HD;
-      const size_t base = (static_cast<size_t>(it.r) * a.nh + static_cast<size_t>(it.kvh) * g + h) * a.max_splits;
       float mx = -INFINITY;
-      for (int sp = first_split; sp <= last_split; ++sp) mx = fmaxf(mx, __ldcg(&a.part_ml[(base + sp) * 2]));
+      for (int k = 0; k < it.n_parts; ++k)
+        mx = fmaxf(mx, __ldcg(&a.part_ml[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * 2]));
       float acc = 0.0f, l = 0.0f;
-      for (int sp = first_split; sp <= last_split; ++sp) {
-        const float f = exp2f(__ldcg(&a.part_ml[(base + sp) * 2]) - mx);
-        acc += __ldcg(&a.part_o[(base + sp) * HD + d]) * f;
-        l += __ldcg(&a.part_ml[(base + sp) * 2 + 1]) * f;
+      for (int k = 0; k < it.n_parts; ++k) {             // in the order of the context: a fixed order
+        const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
+        const float f = exp2f(__ldcg(&a.part_ml[slot * 2]) - mx);
+        acc += __ldcg(&a.part_o[slot * HD + d]) * f;
+        l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
       }
       a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
     }
@@ -426,8 +540,9 @@ paged_decode_kernel(const DecodeArgs a) {
 }
 
 // Shared memory of one CTA with `slots` ring slots, and the most slots that fit.
-template <int HD> size_t decode_smem_bytes(int slots, int g, int item_pages) {
+template <int HD> size_t decode_smem_bytes(int slots, int g, int item_pages, int n_rows) {
   return static_cast<size_t>(item_pages) * DEC_PRODUCERS * sizeof(int)                     // the item's page ids, per producer
+         + (static_cast<size_t>(n_rows) + 2 + slots) * sizeof(int)                         // rows' first tiles (balanced items), slots' counts
          + static_cast<size_t>(slots) * 2 * DEC_TILE * HD * sizeof(__nv_bfloat16)         // ring
          + 2 * 16 * (HD + 8) * sizeof(__nv_bfloat16)                                       // queries, two items
          + static_cast<size_t>(DEC_CONSUMERS) * g * (HD + 2) * sizeof(float)               // merge buffers
@@ -437,22 +552,27 @@ template <int HD> size_t decode_smem_bytes(int slots, int g, int item_pages) {
 template <int HD>
 int decode_launch(DecodeArgs& a, cudaStream_t stream) {
   const int g = a.nh / a.nkv;
-  const int item_pages = ((a.split_size + DEC_TILE) >> a.page_shift) + 2;
-  if (decode_smem_bytes<HD>(2, g, item_pages) > static_cast<size_t>(DEC_SMEM_BUDGET)) return ERR_UNSUPPORTED;
-  int slots = 2;
-  while (decode_smem_bytes<HD>(slots + 1, g, item_pages) <= static_cast<size_t>(DEC_SMEM_BUDGET)) ++slots;
-  a.ring_slots = slots;
-  a.item_pages = item_pages;
-  const size_t smem = decode_smem_bytes<HD>(slots, g, item_pages);
-  auto kernel = paged_decode_kernel<HD>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-    return ERR_CUDA;
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
     return ERR_CUDA;
-  const long long items = static_cast<long long>(a.n_rows) * a.nkv * a.max_splits;
-  const int grid = static_cast<int>(items < sms ? items : sms);     // one persistent CTA per SM
+  // One persistent CTA per SM.  Fixed splits: max_splits items per pair.  Balanced: max_splits is the
+  // most tiles a pair can have, and an item is at most a pair's tiles or a range's, whichever is less.
+  const long long units = static_cast<long long>(a.n_rows) * a.nkv * a.max_splits;
+  int grid = static_cast<int>(units < sms ? units : sms);
+  if (a.split_size == 0 && grid > DEC_MAX_BALANCED_GRID) grid = DEC_MAX_BALANCED_GRID;
+  const long long item_tiles = a.split_size > 0 ? a.split_size / DEC_TILE + 1
+                                                : std::min<long long>(a.max_splits, (units + grid - 1) / grid) + 1;
+  const int item_pages = static_cast<int>((item_tiles * DEC_TILE) >> a.page_shift) + 2;
+  if (decode_smem_bytes<HD>(2, g, item_pages, a.n_rows) > static_cast<size_t>(DEC_SMEM_BUDGET)) return ERR_UNSUPPORTED;
+  int slots = 2;
+  while (decode_smem_bytes<HD>(slots + 1, g, item_pages, a.n_rows) <= static_cast<size_t>(DEC_SMEM_BUDGET)) ++slots;
+  a.ring_slots = slots;
+  a.item_pages = item_pages;
+  const size_t smem = decode_smem_bytes<HD>(slots, g, item_pages, a.n_rows);
+  auto kernel = paged_decode_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return ERR_CUDA;
   kernel<<<grid, DEC_THREADS, smem, stream>>>(a);
   return launch_result();
 }
@@ -467,21 +587,29 @@ ZB_API int zb_paged_decode_supported(int nh, int nkv, int hd, int dtype) {
   return hd == 32 || hd == 64 || hd == 96 || hd == 128 ? 1 : 0;
 }
 
-// Floats of scratch the kernel needs for the partial results of the splits.
+// Floats of scratch the kernel needs for the partial results of fixed splits.
 ZB_API long long zb_paged_decode_scratch_floats(int n_rows, int nh, int hd, int max_splits) {
   return static_cast<long long>(n_rows) * nh * max_splits * (hd + 2);
 }
 
-// Attention of `n_rows` single new tokens over their paged context.  `scratch` holds
-// zb_paged_decode_scratch_floats(...) floats (contents irrelevant); `counters` holds n_rows * nkv
-// ints that are zero on entry and are left zero.  max_splits >= ceil((longest context + 1) /
-// split_size); split_size is a multiple of 32; page_size is a power of two.
+// The same for balanced items (split_size 0): two slots per CTA, whatever the batch.
+ZB_API long long zb_paged_decode_balanced_scratch_floats(int nh, int nkv, int hd) {
+  return 2LL * DEC_MAX_BALANCED_GRID * (nh / nkv) * (hd + 2);
+}
+
+// Attention of `n_rows` single new tokens over their paged context.  `counters` holds n_rows * nkv
+// ints that are zero on entry and are left zero; page_size is a power of two.
+//   split_size > 0 (a multiple of 32): every row's context is cut into splits of that many positions;
+//     max_splits >= ceil((longest context + 1) / split_size); `scratch` holds
+//     zb_paged_decode_scratch_floats(...) floats (contents irrelevant).
+//   split_size == 0: the tiles of all rows are spread evenly over the CTAs; max_splits >=
+//     ceil((longest context + 1) / 32); `scratch` holds zb_paged_decode_balanced_scratch_floats(...).
 ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
                            int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
                            const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
                            float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
                            void* stream) {
-  if (n_rows < 0 || max_splits <= 0 || split_size <= 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0 ||
+  if (n_rows < 0 || max_splits <= 0 || split_size < 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0 ||
       counters == nullptr)
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_decode_supported(nh, nkv, hd, DTYPE_BF16) || (page_size & (page_size - 1)) != 0) return ERR_UNSUPPORTED;
@@ -495,7 +623,8 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
   a.kv_cache = static_cast<const __nv_bfloat16*>(kv_cache);
   a.block_table = block_table; a.rows = rows; a.row_q_start = row_q_start; a.row_ctx = row_ctx;
   a.part_o = scratch;
-  a.part_ml = scratch + static_cast<size_t>(n_rows) * nh * max_splits * hd;
+  a.part_ml = scratch + (split_size > 0 ? static_cast<size_t>(n_rows) * nh * max_splits * hd
+                                        : static_cast<size_t>(2) * DEC_MAX_BALANCED_GRID * (nh / nkv) * hd);
   a.counters = counters;
   a.max_blocks = max_blocks; a.page_shift = page_shift; a.num_pages = num_pages; a.num_rows = num_rows;
   a.n_rows = n_rows;

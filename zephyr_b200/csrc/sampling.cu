@@ -321,6 +321,18 @@ __device__ __forceinline__ unsigned sort_key(const SortJob& job, int i, const fl
   return job.by_z ? __float_as_uint(fabsf(scaled(x[i], maximum, T))) : ~__float_as_uint(w[i]);
 }
 
+// Lanes of the warp whose 8-bit digit equals this lane's (lanes with `valid` false match nobody):
+// eight ballots, one per bit, where a single match instruction walks the distinct values one by one.
+__device__ __forceinline__ unsigned lanes_with_same_digit(unsigned digit, bool valid) {
+  unsigned peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+  for (int bit = 0; bit < 8; ++bit) {
+    const unsigned set = __ballot_sync(0xffffffffu, (digit >> bit) & 1u);
+    peers &= (digit >> bit) & 1u ? set : ~set;
+  }
+  return valid ? peers : 0u;
+}
+
 __global__ void __launch_bounds__(ROW_THREADS)
 sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
                    const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
@@ -360,8 +372,8 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
 #pragma unroll
       for (int u = 0; u < SORT_UNROLL; ++u) {
         const bool valid = i + u * 32 + lane < w_end;
-        const int digit = valid ? static_cast<int>((key[u] >> shift) & 255u) : 256;
-        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        const unsigned digit = (key[u] >> shift) & 255u;
+        const unsigned peers = lanes_with_same_digit(digit, valid);
         if (valid && (peers & lanes_below) == 0) hist[digit * 32 + warp] += __popc(peers);
         __syncwarp();
       }
@@ -390,8 +402,8 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
 #pragma unroll
       for (int u = 0; u < SORT_UNROLL; ++u) {
         const bool valid = i + u * 32 + lane < w_end;
-        const int digit = valid ? static_cast<int>((key[u] >> shift) & 255u) : 256;
-        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        const unsigned digit = (key[u] >> shift) & 255u;
+        const unsigned peers = lanes_with_same_digit(digit, valid);
         if (valid) {
           const int at = hist[digit * 32 + warp] + __popc(peers & lanes_below);
           dst_key[at] = key[u];

@@ -109,6 +109,8 @@ def library() -> ctypes.CDLL:
                 fn.restype = c_int
             lib.zb_paged_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
             lib.zb_paged_decode_scratch_floats.restype = c_longlong
+            lib.zb_paged_decode_balanced_scratch_floats.argtypes = [c_int, c_int, c_int]
+            lib.zb_paged_decode_balanced_scratch_floats.restype = c_longlong
             _lib = lib
     return _lib
 
@@ -401,10 +403,11 @@ def _decode_workspace(device: torch.device, floats: int, counters: int) -> tuple
 
 
 def decode_split_size(n_rows: int, nkv: int, max_context: int) -> int:
-    """Positions per work item of the decode kernel.  Long items cost less per position (one merge
-    and one partial result per item); short ones spread a small batch over all SMs.  The size
-    depends on the batch, so the split points of a row, and with them the last bits of its
-    result, depend on what else is decoded beside it."""
+    """A size for fixed splits (``paged_decode(..., split_size=...)``): long items cost less per
+    position, short ones spread a small batch over all SMs.  The engine does not use fixed splits:
+    without a split size the kernel spreads the tiles of all rows evenly over its CTAs, so where a
+    row's context is cut, and with that the last bits of its result, depends on what else is decoded
+    beside it."""
     split = 1024
     while split > 128 and n_rows * nkv * math.ceil(max_context / split) < _sm_count() - 20:
         split //= 2
@@ -430,17 +433,24 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
 
     ``max_context`` is at least the longest context of the rows, the new token included.  ``scratch``
     (float32, any contents) and ``counters`` (int32, zero) come from a process-wide workspace unless
-    given."""
+    given.  ``split_size`` None or 0: balanced work items; a multiple of 32: fixed splits of that size."""
     _cuda(q, kv_cache, block_table, rows, row_q_start, row_ctx, status, out)
     _i32(block_table, rows, row_q_start, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
     n_rows = rows.numel()
-    if split_size is None:
+    if split_size is None and n_rows * nkv * 4 <= _sm_count():
+        # A handful of long rows: fixed splits keep every item inside one row (a CTA whose share
+        # straddles two rows pays for two merges, which shows when the shares are a few tiles).
         split_size = decode_split_size(n_rows, nkv, max_context)
-    max_splits = max(1, math.ceil(max_context / split_size))
-    need = paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
+    if split_size is None or split_size == 0:
+        # Balanced items: the tiles of all rows spread evenly over the CTAs (see attention_decode.cu).
+        split_size, max_splits = 0, max(1, math.ceil(max_context / 32))
+        need = int(library().zb_paged_decode_balanced_scratch_floats(nh, nkv, hd))
+    else:
+        max_splits = max(1, math.ceil(max_context / split_size))
+        need = paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
     if scratch is None or counters is None:
         scratch, counters = _decode_workspace(q.device, need, n_rows * nkv)
     _require(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,

@@ -80,7 +80,7 @@ def decode_attention(args) -> dict:
     rows = torch.arange(B, dtype=torch.int32, device=device)
     row_ctx = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
     status, out = ops.new_status(device), torch.empty_like(q)
-    split = args.split or ops.decode_split_size(B, nkv, ctx)
+    split = args.split or None
 
     def run(i):
         ops.paged_decode(q, caches[i % len(caches)], table, rows, rows, row_ctx, ctx, nh, nkv, hd, args.window,
@@ -90,7 +90,7 @@ def decode_attention(args) -> dict:
     live = min(ctx, args.window) if args.window else ctx
     read = B * live * nkv * hd * 2 * 2
     return {"kernel": "paged_decode_kernel", "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
-            "page_size": args.page_size, "window": args.window, "split_size": split, "us": round(us, 2),
+            "page_size": args.page_size, "window": args.window, "split_size": split or "balanced", "us": round(us, 2),
             "bytes_read": read, "gbs": round(read / us / 1e3, 1)}
 
 
@@ -200,7 +200,7 @@ def main(argv=None) -> int:
     parser.add_argument("--head-dim", type=int, default=128)
     parser.add_argument("--page-size", type=int, default=16)
     parser.add_argument("--window", type=int, default=0)
-    parser.add_argument("--split", type=int, default=0, help="positions per work item of the decode kernel (0: its own choice)")
+    parser.add_argument("--split", type=int, default=0, help="fixed splits of this many positions in the decode kernel (0: balanced items)")
     parser.add_argument("--rows", type=int, default=8)
     parser.add_argument("--n", type=int, default=6144)
     parser.add_argument("--k", type=int, default=1024)
