@@ -217,7 +217,8 @@ def make_tables(ctx_lens, page_size, num_pages, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 4), (6, 3, 48, 8), (16, 8, 128, 16), (5, 5, 256, 32), (8, 1, 80, 64)])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 4), (6, 3, 48, 8), (16, 8, 128, 16), (5, 5, 256, 32), (8, 1, 80, 64),
+                                            (7, 2, 64, 16), (3, 1, 128, 8)])
 def test_qk_norm_rope_cache(ops, cuda_device, dtype, nh, nkv, hd, page):
     from zephyr_b200.parts import rope_tables
 
@@ -528,7 +529,7 @@ DECODE_CASES = [(4, 2, 32, 8, 0), (16, 8, 128, 16, 0), (8, 8, 64, 4, 0), (32, 2,
                 (16, 8, 128, 16, 300), (6, 2, 64, 64, 0)]
 
 
-@pytest.mark.parametrize("split_size", [None, 32, 64, 256])
+@pytest.mark.parametrize("split_size", [None, 0, 32, 64, 256])       # 0: balanced items whatever the batch
 @pytest.mark.parametrize("nh,nkv,hd,page,window", DECODE_CASES)
 def test_paged_decode_split(ops, cuda_device, nh, nkv, hd, page, window, split_size):
     """The split-context decode kernel at context lengths around tile and split edges, mixed with

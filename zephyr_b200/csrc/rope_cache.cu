@@ -163,6 +163,93 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
   }
 }
 
+// The same for bfloat16 and head sizes 64 and 128, eight bytes a lane: a head is HD / 8 lanes
+// (lane j owns elements 4j .. 4j + 3 of the first half and their partners in the second), so a warp
+// takes 32 / (HD / 8) heads of a token at once and every load and store is a vector.  The math,
+// the order of roundings and the cache layout are those of the kernel above.
+template <int HD>
+__global__ void __launch_bounds__(ROPE_WARPS * 32)
+qk_norm_rope_cache_wide_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv,
+                               long long qkv_stride, const void* __restrict__ q_norm_w,
+                               const void* __restrict__ k_norm_w, int w_dtype, float eps,
+                               const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                               int max_positions, const int* __restrict__ positions,
+                               const int* __restrict__ token_row, CacheView cache, int nh, int nkv, int* status) {
+  constexpr int LANES = HD / 8, HEADS_PER_WARP = 32 / LANES, HALF = HD / 2;
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, sub = lane % LANES;
+  const int head = (blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5)) * HEADS_PER_WARP + lane / LANES;
+  const int total_heads = cache.base != nullptr ? nh + 2 * nkv : nh;
+  const bool active = head < total_heads;
+  const int pos = positions[t];
+  const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+  const int i = 4 * sub;                                        // this lane's elements i .. i + 3 and i + HALF ..
+  float x[4] = {0, 0, 0, 0}, y[4] = {0, 0, 0, 0};
+  if (active) {
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * qkv_stride + static_cast<size_t>(head) * HD;
+    const uint2 xv = *reinterpret_cast<const uint2*>(src + i), yv = *reinterpret_cast<const uint2*>(src + i + HALF);
+    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+    const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.x));
+    const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.y));
+    x[0] = x01.x; x[1] = x01.y; x[2] = x23.x; x[3] = x23.y;
+    y[0] = y01.x; y[1] = y01.y; y[2] = y23.x; y[3] = y23.y;
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) ss += x[u] * x[u] + y[u] * y[u];
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // over the head's lanes
+  if (!active) return;
+
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(t) * nh + head) * HD;
+  } else {
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    const long long off = cache_row_offset(cache, token_row[t], pos, is_k ? 0 : 1, kvh, nkv, HD, status, t);
+    if (off < 0) return;
+    dst = static_cast<__nv_bfloat16*>(cache.base) + off;
+  }
+  if (is_q || is_k) {
+    const void* w = is_q ? q_norm_w : k_norm_w;
+    if (w != nullptr) {
+      const float inv = rsqrtf(ss / static_cast<float>(HD) + eps);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        x[u] *= inv * load_scale(w, w_dtype, i + u);
+        y[u] *= inv * load_scale(w, w_dtype, i + u + HALF);
+      }
+    }
+    if (cos_table != nullptr) {
+      if (pos < 0 || pos >= max_positions) {
+        if (sub == 0) report(status, STATUS_POSITION_OUT_OF_RANGE, pos, t);
+        return;
+      }
+      const float4 c = *reinterpret_cast<const float4*>(cos_table + static_cast<size_t>(pos) * HALF + i);
+      const float4 sn = *reinterpret_cast<const float4*>(sin_table + static_cast<size_t>(pos) * HALF + i);
+      const float cs[4] = {c.x, c.y, c.z, c.w}, si[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float xr = x[u] * cs[u] - y[u] * si[u];
+        const float yr = y[u] * cs[u] + x[u] * si[u];
+        x[u] = xr;
+        y[u] = yr;
+      }
+    }
+  }
+  // Four adjacent elements never straddle a 16-byte chunk of a cache row.
+  const int lo = is_q ? i : kv_element_index(i, pos, HD, sizeof(__nv_bfloat16));
+  const int hi = is_q ? i + HALF : kv_element_index(i + HALF, pos, HD, sizeof(__nv_bfloat16));
+  uint2 xo, yo;
+  *reinterpret_cast<__nv_bfloat162*>(&xo.x) = __floats2bfloat162_rn(x[0], x[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&xo.y) = __floats2bfloat162_rn(x[2], x[3]);
+  *reinterpret_cast<__nv_bfloat162*>(&yo.x) = __floats2bfloat162_rn(y[0], y[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&yo.y) = __floats2bfloat162_rn(y[2], y[3]);
+  *reinterpret_cast<uint2*>(dst + lo) = xo;
+  *reinterpret_cast<uint2*>(dst + hi) = yo;
+}
+
 // In-place rotation of x [T, heads, hd] (rows `stride` elements apart).
 template <typename T>
 __global__ void rope_kernel(T* __restrict__ x, long long stride, int heads, int hd,
@@ -232,7 +319,20 @@ ZB_API int zb_qk_norm_rope_cache(void* q_out, const void* qkv, long long qkv_str
     qk_norm_rope_cache_kernel<float><<<grid, ROPE_WARPS * 32, 0, s>>>(
         (float*)q_out, (const float*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table, sin_table,
         max_positions, positions, token_row, cache, nh, nkv, hd, status);
-  else
+  else if ((hd == 64 || hd == 128) && qkv_stride % 4 == 0 && reinterpret_cast<uintptr_t>(qkv) % 8 == 0 &&
+           reinterpret_cast<uintptr_t>(q_out) % 8 == 0 && reinterpret_cast<uintptr_t>(kv_cache) % 8 == 0 &&
+           reinterpret_cast<uintptr_t>(cos_table) % 16 == 0 && reinterpret_cast<uintptr_t>(sin_table) % 16 == 0) {
+    const int per_warp = hd == 64 ? 4 : 2;
+    const dim3 wide(T, (heads + ROPE_WARPS * per_warp - 1) / (ROPE_WARPS * per_warp));
+    if (hd == 64)
+      qk_norm_rope_cache_wide_kernel<64><<<wide, ROPE_WARPS * 32, 0, s>>>(
+          (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
+          sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
+    else
+      qk_norm_rope_cache_wide_kernel<128><<<wide, ROPE_WARPS * 32, 0, s>>>(
+          (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
+          sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
+  } else
     qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, 0, s>>>(
         (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
         sin_table, max_positions, positions, token_row, cache, nh, nkv, hd, status);
