@@ -108,6 +108,13 @@ __device__ __forceinline__ void tmem_st32(unsigned address, const unsigned (&r)[
                  "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                : "memory");
 }
+// Has the phase with this parity completed?  Never suspends the thread (try_wait may, for a while).
+__device__ __forceinline__ bool tc_mbar_test(unsigned long long* bar, unsigned parity) {
+  unsigned done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ void tc_mbar_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -183,11 +190,14 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(kv_s + 4 * TC_TILE_BYTES);
   // Tile j uses entry j % 2 of every pair; on each barrier its phase is j / 2, and nobody ever
   // waits for a phase that is more than one behind the barrier's current one.
-  unsigned long long* kv_full = bars;          // [2] a stage's keys and values have landed (all loader threads)
-  unsigned long long* kv_empty = bars + 2;     // [2] the products that read the stage are complete
-  unsigned long long* s_full = bars + 4;       // [2] S of the tile is complete
-  unsigned long long* p_full = bars + 6;       // [2] P is written, S has been read, O has been rescaled (all softmax threads)
-  unsigned long long* o_done = bars + 8;       // [2] O += P V of the tile is complete
+  // Keys and values have barriers of their own: a stage's keys are free again as soon as S of their
+  // tile is complete, long before its values, so the keys of the tile after next are on their way
+  // while this tile's softmax runs.  Index 0: keys, 1: values.
+  unsigned long long* kv_full = bars;          // [2 kinds][2 stages] the rows have landed (all loader threads)
+  unsigned long long* kv_empty = bars + 4;     // [2 kinds][2 stages] the product that reads them is complete
+  unsigned long long* s_full = bars + 8;       // [2] S of the tile is complete
+  unsigned long long* p_full = bars + 10;      // [2] P is written, S has been read, O has been rescaled (all softmax threads)
+  unsigned long long* o_done = bars + 12;      // [2] O += P V of the tile is complete
   __shared__ unsigned tmem_base_s;
   __shared__ volatile int abort_flag;
 
@@ -214,10 +224,10 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(&kv_full[0], TC_LOADER_WARPS * 32);
-    mbar_init(&kv_full[1], TC_LOADER_WARPS * 32);
-    mbar_init(&kv_empty[0], 1);
-    mbar_init(&kv_empty[1], 1);
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(&kv_full[b], TC_LOADER_WARPS * 32);
+      mbar_init(&kv_empty[b], 1);
+    }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], TC_SOFTMAX_WARPS * 32);
@@ -273,14 +283,15 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
     // zeros (their scores are masked, and a zero probability times a zero value stays zero) and
     // goes through 16-byte copies that can do that.
     const int rows_per_copy = min(page_size, TC_BN), copies_per_half = TC_BN / rows_per_copy;
-    auto issue_tiled = [&](int j) {
+    auto issue_tiled = [&](int kv, int j) {        // kv 0: the tile's keys, 1: its values
       const int stage = j & 1, k0 = first_tile + j * TC_BN;
-      unsigned char* stage_s = kv_s + stage * 2 * TC_TILE_BYTES;
-      if (lt == 0) mbar_arrive_expect_tx(&kv_full[stage], 2u * TC_TILE_BYTES);
-      else tc_mbar_arrive(&kv_full[stage]);
-      // copy id: (keys or values, 64-dim half, piece of the tile)
-      for (int id = (lt >> 5) * 8 + (lt & 31); (lt & 31) < 8 && id < 4 * copies_per_half; id += 32) {
-        const int kv = id / (2 * copies_per_half), half = (id / copies_per_half) & 1, piece = id % copies_per_half;
+      unsigned char* dst = kv_s + stage * 2 * TC_TILE_BYTES + kv * TC_TILE_BYTES;
+      unsigned long long* bar = &kv_full[kv * 2 + stage];
+      if (lt == 0) mbar_arrive_expect_tx(bar, TC_TILE_BYTES);
+      else tc_mbar_arrive(bar);
+      // copy id: (64-dim half, piece of the tile); four copies from each loader warp at a time
+      for (int id = (lt >> 5) * 4 + (lt & 31); (lt & 31) < 4 && id < 2 * copies_per_half; id += 16) {
+        const int half = id / copies_per_half, piece = id % copies_per_half;
         const int pos = k0 + piece * rows_per_copy, block = pos >> a.page_shift;
         int page = block < a.max_blocks ? table[block] : -1;
         if (page <= 0 || page >= a.num_pages) {
@@ -288,14 +299,12 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
           page = 0;                     // the bytes must arrive all the same
         }
         const int cache_row = ((page * 2 + kv) * a.nkv + kvh) * page_size + (pos & (page_size - 1));
-        tiled_copy_2d_g2s(stage_s + kv * TC_TILE_BYTES + half * TC_HALF_BYTES + piece * rows_per_copy * 128, &a.cache_map,
-                          half * 64, cache_row, &kv_full[stage]);
+        tiled_copy_2d_g2s(dst + half * TC_HALF_BYTES + piece * rows_per_copy * 128, &a.cache_map, half * 64, cache_row, bar);
       }
     };
-    auto issue_plain = [&](int j) {
+    auto issue_plain = [&](int kv, int j) {
       const int stage = j & 1;
-      unsigned char* k_dst = kv_s + stage * 2 * TC_TILE_BYTES + dst_base;
-      unsigned char* v_dst = k_dst + TC_TILE_BYTES;
+      unsigned char* dst = kv_s + stage * 2 * TC_TILE_BYTES + kv * TC_TILE_BYTES + dst_base;
       const int k0 = first_tile + j * TC_BN;
       // The page ids of this thread's 16 rows first, all at once: a lookup per copy would put the
       // table's latency in front of every copy.
@@ -315,24 +324,37 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
             report(a.status, STATUS_PAGE_OUT_OF_RANGE, page[i], tok0);
             ok = false;
           } else {
-            src += ((static_cast<long long>(page[i]) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD + chunk * 8;
+            src += ((static_cast<long long>(page[i]) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD +
+                   chunk * 8 + (kv ? v_offset : 0);
           }
         }
-        cp_async_16(k_dst + r * 128, src, ok);
-        cp_async_16(v_dst + r * 128, ok ? src + v_offset : src, ok);
+        cp_async_16(dst + r * 128, src, ok);
       }
       cp_async_commit();
       cp_async_wait<0>();
       fence_proxy_async();           // the tensor core reads what the copies wrote through the asynchronous proxy
-      tc_mbar_arrive(&kv_full[stage]);
+      tc_mbar_arrive(&kv_full[kv * 2 + stage]);
     };
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!wait(&kv_empty[j & 1], ((j >> 1) & 1) ^ 1)) {
+    // Keys and values are fetched in the order their stages come free; keys first when both are.
+    int next[2] = {0, 0};
+    while (next[0] < n_tiles || next[1] < n_tiles) {
+      int kind = -1;
+      for (int polls = 0; kind < 0; ++polls) {
+        // Two barriers are watched at once, so neither may put the thread to sleep for the other.
+        for (int kv = 0; kv < 2 && kind < 0; ++kv)
+          if (next[kv] < n_tiles && tc_mbar_test(&kv_empty[kv * 2 + (next[kv] & 1)], ((next[kv] >> 1) & 1) ^ 1)) kind = kv;
+        if (kind < 0) {
+          if (polls > TC_WAIT_LIMIT || ((polls & 63) == 63 && abort_flag)) break;
+          __nanosleep(64);
+        }
+      }
+      if (kind < 0) {
         give_up(-1);
         break;
       }
+      const int j = next[kind]++;
       const int k0 = first_tile + j * TC_BN;
-      if (a.tiled && k0 >= lo && k0 + TC_BN <= hi) issue_tiled(j); else issue_plain(j);
+      if (a.tiled && k0 >= lo && k0 + TC_BN <= hi) issue_tiled(kind, j); else issue_plain(kind, j);
     }
   } else if (warp == TC_MMA_WARP) {
     // ------------------------------------------------------------- the thread that issues products
@@ -351,6 +373,7 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
           const unsigned at = (k >> 2) * TC_HALF_BYTES + (k & 3) * 32;
           tc_mma(tmem_base + stage * TC_BN, desc_k_major(q_addr + at), desc_k_major(k_addr + at), IDESC_QK, k > 0 ? 1u : 0u);
         }
+        tc_commit(&kv_empty[stage]);            // the keys' stage is free as soon as these products are complete
         tc_commit(&s_full[stage]);
       };
       // S of the next tile is issued as soon as its keys are there, before this tile's second
@@ -365,12 +388,15 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
         bool have_p = false;
         for (int polls = 0; !have_p; ++polls) {
           if (scores_issued <= j + 1 && scores_issued < n_tiles &&
-              mbar_try_wait(&kv_full[scores_issued & 1], (scores_issued >> 1) & 1)) {
+              tc_mbar_test(&kv_full[scores_issued & 1], (scores_issued >> 1) & 1)) {        // the tile's keys
             issue_scores(scores_issued++);
             continue;
           }
-          if (scores_issued > j && mbar_try_wait(&p_full[stage], (j >> 1) & 1)) have_p = true;
+          if (scores_issued > j && tc_mbar_test(&p_full[stage], (j >> 1) & 1) &&
+              tc_mbar_test(&kv_full[2 + stage], (j >> 1) & 1))                            // P and the tile's values
+            have_p = true;
           else if (polls > TC_WAIT_LIMIT || ((polls & 63) == 63 && abort_flag)) break;
+          else __nanosleep(32);          // this warp shares its scheduler with a softmax warp: leave it the issue slots
         }
         if (!have_p) { give_up(-3); ok = false; break; }
         tc_fence_after_sync();
@@ -379,7 +405,7 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
           const unsigned at = (k >> 2) * TC_HALF_BYTES + (k & 3) * 32;      // 16 positions along P's rows
           tc_mma(tmem_o, desc_k_major(p_addr + at), desc_mn_major(v_addr + k * 2048), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(&kv_empty[stage]);
+        tc_commit(&kv_empty[2 + stage]);
         tc_commit(&o_done[stage]);
       }
     }
@@ -552,7 +578,7 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
   a.nh = nh; a.nkv = nkv; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
-  const size_t smem = 1024 + 7 * TC_TILE_BYTES + 10 * sizeof(unsigned long long);
+  const size_t smem = 1024 + 7 * TC_TILE_BYTES + 14 * sizeof(unsigned long long);
   if (cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
   paged_prefill_tc_kernel<<<dim3(n_tiles, nh), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
