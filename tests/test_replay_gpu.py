@@ -114,3 +114,45 @@ def test_first_tokens(model_folders, cuda_device):
             rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
             first, worst, where = first_mismatch(rows, requests, folder, dtype)
             assert first is None, f"{name} {dtype}: {first}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_shapes_replay_a_graph(model_folders, cuda_device, dtype):
+    """Steps of one shape (a portion of 9 tokens beside a portion of 5 and a single token) come five
+    times, with other requests, tokens, contexts and pages each time: the first runs launch by launch,
+    the second is captured, the others replay the graph.  All agree with the plain implementation, and
+    with a runner that never uses graphs bit for bit."""
+    from zephyr_b200.engine.replay import TraceReplayer
+
+    name = "B"
+    folder = model_folders(name, dtype)
+    vocab = TINY[name]["config"]["vocab_size"]
+    requests = {f"r{i}": random_tokens(vocab, 40 + 7 * i, seed=300 + i) for i in range(3)}
+    fed = {rid: 0 for rid in requests}
+    steps = []
+    # A first step that gives every request a different context, then the repeated shape.
+    for rid, count in zip(requests, (3, 11, 6)):
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": requests[rid][:count], "want": [count - 1]}],
+                      "end": []})
+        fed[rid] = count
+    order = list(requests)
+    for turn in range(5):
+        a, b, c = order[turn % 3], order[(turn + 1) % 3], order[(turn + 2) % 3]
+        entries = []
+        for rid, count, want in ((a, 9, [0, 8]), (b, 5, [4]), (c, 1, [0])):
+            entries.append({"id": rid, "tokens": requests[rid][fed[rid]:fed[rid] + count], "want": want})
+            fed[rid] += count
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    outputs = {}
+    for graphs in (True, False):
+        replayer = TraceReplayer(folder, dtype, peak_tokens(steps), page_size=TINY[name]["page_size"], max_requests=4)
+        replayer.runner.use_cuda_graphs = graphs
+        outputs[graphs] = {s["step"]: replayer.step(s) for s in steps}
+        if graphs:
+            shaped = [k for k in replayer.runner._graphs if not isinstance(k[0], int)]
+            assert len(shaped) == 1 and replayer.runner._graphs[shaped[0]]["graph"] is not None
+    for step in steps:
+        assert np.array_equal(outputs[True][step["step"]], outputs[False][step["step"]]), f"step {step['step']}"
+    rows = collect(steps, outputs[True])
+    first, worst, where = first_mismatch(rows, {r: t[:fed[r]] for r, t in requests.items()}, folder, dtype)
+    assert first is None, f"{dtype}: {first}; worst {worst:.3e} at {where}"

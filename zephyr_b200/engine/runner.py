@@ -12,6 +12,7 @@ are long and which are single tokens.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
@@ -46,7 +47,8 @@ class ModelRunner:
         self.poison_freed_pages = False      # tests: NaN into every page that is given back
         self.steps = 0
         self.use_cuda_graphs = use_cuda_graphs
-        self._graphs: dict[tuple[int, int], dict] = {}
+        self._graphs: OrderedDict = OrderedDict()      # graph key -> captured step
+        self._shapes_seen: dict = {}                   # graph key -> times seen before its capture
         self.last_step_h2d_bytes = 0     # bytes of the last step's description copied to the device
 
     # ------------------------------------------------------------------ sizing
@@ -179,31 +181,84 @@ class ModelRunner:
         self.last_step_h2d_bytes = 4 * sum(sizes)
         return self._context_from(device, sizes, info)
 
-    # ------------------------------------------------------------ decode graphs
+    # ------------------------------------------------------------------ graphs
+    MAX_SHAPE_GRAPHS = 16         # captured graphs of steps other than decode-only ones, least recently used first out
+    MAX_SHAPES_COUNTED = 4096
+    MAX_GRAPH_LOGIT_ROWS = 64     # a graph keeps its logits; steps that want more places run launch by launch
+
     def _graph_key(self, entries: Sequence[StepEntry]):
-        """Decode-only steps (one token and its logits per entry) replay a captured CUDA graph: the
-        launches of a whole step become one.  The key fixes everything a launch bakes in: the number
-        of rows, and a power-of-two bound on the context (it sizes the attention grid)."""
+        """A step whose shape comes again replays a captured CUDA graph: the launches of a whole step
+        become one.  The key fixes everything a launch bakes in: the number of new tokens of every row
+        and the wanted places (they size every grid and buffer), and a power-of-two bound on the
+        context of the rows with one new token (it sizes the decode attention's grid).  What a step
+        reads beyond that (tokens, positions, contexts, block tables) it reads from the device.
+        Decode-only steps are captured at once; any other shape when it is seen a second time."""
         if not self.use_cuda_graphs or not self.model.graph_safe:
             return None
-        if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
+        singles = [self.manager.computed(e.request_id) + 1 for e in entries if len(e.tokens) == 1]
+        bound = 0
+        if singles:
+            bound = max(ops.DECODE_SPLIT_SIZE, 1 << (max(singles) - 1).bit_length())
+            bound = min(bound, max(self.max_seq_len, ops.DECODE_SPLIT_SIZE))
+        if len(singles) == len(entries) and all(tuple(e.want) == (0,) for e in entries):
+            return (len(entries), bound)
+        if sum(len(e.want) for e in entries) > self.MAX_GRAPH_LOGIT_ROWS:
             return None
-        longest = max(self.manager.computed(e.request_id) for e in entries) + 1
-        bound = max(ops.DECODE_SPLIT_SIZE, 1 << (longest - 1).bit_length())
-        return (len(entries), min(bound, max(self.max_seq_len, ops.DECODE_SPLIT_SIZE)))
+        key = (tuple((len(e.tokens), tuple(e.want)) for e in entries), bound)
+        if key in self._graphs:
+            self._graphs.move_to_end(key)
+            return key
+        if len(self._shapes_seen) >= self.MAX_SHAPES_COUNTED:
+            self._shapes_seen.clear()
+        self._shapes_seen[key] = self._shapes_seen.get(key, 0) + 1
+        if self._shapes_seen[key] < 2:
+            return None
+        del self._shapes_seen[key]
+        shaped = [k for k in self._graphs if not isinstance(k[0], int)]
+        if len(shaped) >= self.MAX_SHAPE_GRAPHS:
+            del self._graphs[shaped[0]]
+        return key
+
+    def _rewrite_decode(self, record: dict, host: np.ndarray, entries: Sequence[StepEntry], width: int) -> dict:
+        """A decode-only step's values, written into their places of the pinned buffer (the order of
+        ``_describe``: 0 tokens, 1 positions, 5 contexts, 6 slots, 9.. one block table per group)."""
+        manager, R, offsets = self.manager, len(entries), record["offsets"]
+        ctx_before = [manager.computed(e.request_id) for e in entries]
+        for entry, ctx in zip(entries, ctx_before):
+            if not manager.ensure_capacity(entry.request_id, ctx + 1):
+                raise OutOfPagesError(
+                    f"no pages left for request {entry.request_id!r} ({ctx} cached + 1 new token); "
+                    f"free pages per group: {[g.pool.num_free for g in manager.groups]}")
+        host[offsets[0]:offsets[0] + R] = [e.tokens[0] for e in entries]
+        host[offsets[1]:offsets[1] + R] = ctx_before
+        host[offsets[5]:offsets[5] + R] = ctx_before
+        slots = [manager.state_slot(e.request_id) for e in entries]
+        host[offsets[6]:offsets[6] + R] = slots
+        for group in range(len(manager.groups)):
+            table = host[offsets[9 + group]:offsets[10 + group]].reshape(R, width)
+            table[:] = 0
+            for i, entry in enumerate(entries):
+                row = manager.block_table_array(entry.request_id, group)
+                table[i, :row.size] = row
+        return dict(record["info"], ctx_before=ctx_before, slots=slots)
 
     def _step_with_graph(self, key, entries: Sequence[StepEntry]) -> tuple[torch.Tensor, dict]:
         width = self.manager.blocks_for(self.max_seq_len)
+        decode_only = isinstance(key[0], int)
         record = self._graphs.get(key)
+        described = None
+        if record is None or not decode_only:
+            described = self._describe(entries, table_width=width)
+            described[1]["max_decode_context"] = key[1]
         if record is None:
-            arrays, info = self._describe(entries, table_width=width)
-            info["max_decode_context"] = key[1]
+            arrays, info = described
             sizes = [a.size for a in arrays]
             total = sum(sizes)
             # A small ring of pinned buffers: the host may run ahead of the device, and a buffer must not
-            # be refilled before the copy that reads it has been done.  Every buffer starts as a copy of
-            # the first step's description: what depends only on the number of rows stays as it is, and
-            # later steps rewrite the rest in place (tokens, positions, contexts, slots, block tables).
+            # be refilled before the copy that reads it has been done.  For decode-only steps every buffer
+            # starts as a copy of the first step's description: what depends only on the number of rows
+            # stays as it is, and later steps rewrite the rest in place (tokens, positions, contexts,
+            # slots, block tables).  Steps of other shapes write the whole description every time.
             template = np.concatenate(arrays)
             offsets = np.concatenate([[0], np.cumsum(sizes)]).tolist()
             record = {"host": [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(4)],
@@ -217,28 +272,13 @@ class ModelRunner:
         record["turn"] = (turn + 1) % len(record["host"])
         if record["copied"][turn] is not None:
             record["copied"][turn].synchronize()
-        # The step's values, written into their places (the order of ``_describe``: 0 tokens, 1 positions,
-        # 5 contexts, 6 slots, 9.. one block table per group).
-        manager, R = self.manager, len(entries)
-        ctx_before = [manager.computed(e.request_id) for e in entries]
-        for entry, ctx in zip(entries, ctx_before):
-            if not manager.ensure_capacity(entry.request_id, ctx + 1):
-                raise OutOfPagesError(
-                    f"no pages left for request {entry.request_id!r} ({ctx} cached + 1 new token); "
-                    f"free pages per group: {[g.pool.num_free for g in manager.groups]}")
-        host = record["host"][turn].numpy()
-        host[offsets[0]:offsets[0] + R] = [e.tokens[0] for e in entries]
-        host[offsets[1]:offsets[1] + R] = ctx_before
-        host[offsets[5]:offsets[5] + R] = ctx_before
-        slots = [manager.state_slot(e.request_id) for e in entries]
-        host[offsets[6]:offsets[6] + R] = slots
-        for group in range(len(manager.groups)):
-            table = host[offsets[9 + group]:offsets[10 + group]].reshape(R, width)
-            table[:] = 0
-            for i, entry in enumerate(entries):
-                row = manager.block_table_array(entry.request_id, group)
-                table[i, :row.size] = row
-        info = dict(record["info"], ctx_before=ctx_before, slots=slots)
+        if decode_only:
+            info = self._rewrite_decode(record, record["host"][turn].numpy(), entries, width)
+        else:
+            arrays, info = described
+            if [a.size for a in arrays] != sizes:
+                raise RuntimeError("a step's description changed size under one graph key")
+            np.concatenate(arrays, out=record["host"][turn].numpy())
         record["device"].copy_(record["host"][turn], non_blocking=True)
         event = record["copied"][turn] or torch.cuda.Event()
         event.record()
@@ -261,7 +301,9 @@ class ModelRunner:
             record["graph"] = graph
         record["graph"].replay()
         ops.LAUNCHES += record["kernels"]
-        return record["logits"], info
+        # A decode-only step hands out its graph's own tensor (the caller samples from it at once);
+        # steps of other shapes hand out a copy, which the next step of that shape leaves alone.
+        return (record["logits"] if decode_only else record["logits"].clone()), info
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
