@@ -700,7 +700,7 @@ def test_temperature_sampling_follows_the_prefix_sums(ops, cuda_device):
 
 FILTERS = [dict(top_k=1), dict(top_k=7), dict(top_k=300), dict(top_p=0.9), dict(top_p=0.3), dict(top_k=40, top_p=0.8),
            dict(min_p=0.05), dict(top_k=50, min_p=0.1), dict(top_p=0.95, min_p=0.02), dict(top_k=20, top_p=0.5, min_p=0.2),
-           dict(top_k=10 ** 9), dict(top_p=0.999)]
+           dict(top_k=10 ** 9), dict(top_p=0.999), dict(top_k=6000), dict(top_k=5000, top_p=0.7), dict(top_k=4096, top_p=0.99)]
 
 
 def test_filtered_sampling_matches_the_plain_sampler(ops, cuda_device):
@@ -709,9 +709,14 @@ def test_filtered_sampling_matches_the_plain_sampler(ops, cuda_device):
     import plain_sampler
 
     compared = 0
-    for V, spread in ((311, 2.0), (5000, 3.0), (151936, 4.0)):
+    decided_in_head, decided_by_whole_order = 0, 0
+    for V, spread, peaks in ((311, 2.0, 0), (5000, 3.0, 0), (151936, 4.0, 0), (151936, 1.0, 0), (151936, 1.5, 40)):
         g = torch.Generator().manual_seed(V + 1)
         logits = (torch.randn((len(FILTERS) * 2, V), generator=g) * spread)
+        if peaks:       # a few tokens far above a broad bulk, as a trained model's logits are
+            for r in range(logits.shape[0]):
+                at = torch.randperm(V, generator=g)[:peaks]
+                logits[r, at] += 8.0 + 6.0 * torch.rand(peaks, generator=g)
         uniform = torch.rand(logits.shape[0], generator=g).tolist()
         rows = []
         for r in range(logits.shape[0]):
@@ -722,6 +727,12 @@ def test_filtered_sampling_matches_the_plain_sampler(ops, cuda_device):
         status = ops.new_status(cuda_device)
         got = ops.sample_rows(logits.to(cuda_device), rows, status).ids.tolist()
         ops.check_status(status)
+        state = ops.last_sample_job_state()
+        assert len(state) == sum(1 for row in rows if row.ranked)
+        for sorted_ranks, head_was_enough in state:
+            assert sorted_ranks == V or (head_was_enough and 0 < sorted_ranks <= 4096)
+            decided_in_head += head_was_enough
+            decided_by_whole_order += not head_was_enough
         for r, row in enumerate(rows):
             want, margin = plain_sampler.sample(logits[r], row.temperature, row.uniform, row.top_k, row.top_p or 1.0,
                                                 row.min_p)
@@ -735,7 +746,9 @@ def test_filtered_sampling_matches_the_plain_sampler(ops, cuda_device):
                 assert order.index(got[r]) < row.top_k
             if row.min_p:
                 assert float(p[got[r]]) > row.min_p * float(p.max()) * (1 - 1e-5)
-    assert compared >= 0.75 * 3 * 2 * len(FILTERS)        # most rows were decided clearly and compared exactly
+    assert compared >= 0.75 * 5 * 2 * len(FILTERS)        # most rows were decided clearly and compared exactly
+    # Both ways of ranking were at work: the head of the order alone, and the whole vocabulary.
+    assert decided_in_head >= 20 and decided_by_whole_order >= 20, (decided_in_head, decided_by_whole_order)
 
 
 def test_ranked_draw_takes_equal_weights_in_index_order(ops, cuda_device):

@@ -24,8 +24,15 @@
 //
 // How it runs: passes over a row are spread over many CTAs (chunks of 4096 logits) and meet through
 // small per-chunk partial results, merged in chunk order so that a row's result does not depend on
-// the batch around it; the chunk that arrives last finishes the row's maximum.  Ranking is a
-// stable least-significant-digit radix sort, one CTA per row.
+// the batch around it; the chunk that arrives last finishes the row's maximum.  Ranking runs in two
+// steps, one CTA per row each.  The first ranks only the head of the order: a histogram of a sample of
+// the row over the keys' leading 12 bits says which leading bins hold about 2048 tokens, all tokens
+// of those bins are sorted in shared memory (if they are at most 4096), and the row is done if the
+// draw (or the report) can be decided within them, which it can whenever the distribution has a
+// peak.  Rows that are not done go through a
+// stable least-significant-digit radix sort of the whole vocabulary.  Both steps produce the same
+// order and feed the same draw, whose sums run in blocks of 4096 ranks, so a rank's prefix sum does
+// not depend on how many ranks were sorted.
 #include "common.cuh"
 
 namespace zb {
@@ -336,13 +343,14 @@ __device__ __forceinline__ unsigned lanes_with_same_digit(unsigned digit, bool v
 __global__ void __launch_bounds__(ROW_THREADS)
 sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
                    const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
-                   const float* __restrict__ weights, unsigned* keys, int* idx) {
+                   const float* __restrict__ weights, unsigned* keys, int* idx, int* job_state) {
   __shared__ int hist[256 * 32];
   __shared__ int scratch[33];
   const SortJob job = jobs[blockIdx.x];
   const int r = job.row;
   const float maximum = row_max[r];
   if (!isfinite(maximum)) return;
+  if (job_state[2 * blockIdx.x + 1]) return;        // decided within the head of the order
   const double T = scaling_temperature(rows[r]);
   const float* x = logits + static_cast<size_t>(r) * row_stride;
   const float* w = weights + static_cast<size_t>(r) * V;
@@ -416,16 +424,269 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
     }
     __syncthreads();            // this pass's stores are visible to the whole CTA before the next reads them
   }
+  if (threadIdx.x == 0) job_state[2 * blockIdx.x] = V;
 }
 
 // ---------------------------------------------------------------------- the draw over the ranks
-// One CTA per row.  `keys`/`idx`: the job's sorted second buffer; its first buffer is reused for
-// the prefix sums that the top-p rule looks at.
+constexpr int RANK_BLOCK = 4096;            // ranks per round of the draw's sums: four per thread
+constexpr int RANK_PER = RANK_BLOCK / ROW_THREADS;
+
+struct RankScratch {
+  float scan[33];
+  float carry, total;
+  int cut, first, last;
+};
+
+// The draw of one ranked row by the whole CTA.  `sorted`/`source`: the first `n_sorted` ranks (keys
+// are the inverted bit patterns of the weights).  Returns the chosen token, or -1 if the decision
+// needs ranks beyond `n_sorted`.  The ranks that stay form a prefix of the order: the limits on the
+// rank, on the mass before a rank and on the weight all cut a tail off.  Prefix sums run in rounds of
+// RANK_BLOCK ranks (a block scan plus the carry of the rounds before), so the sum at a rank is the
+// same whatever `n_sorted` is.
+__device__ int ranked_draw(const SampleRow& p, const unsigned* sorted, const int* source, int n_sorted, int V,
+                           float total_all, RankScratch& sh) {
+  const int k = p.top_k > 0 ? min(p.top_k, V) : V;
+  const int seen = min(k, n_sorted);
+  if (seen <= 0) return -1;
+  auto weight = [&](int i) { return __uint_as_float(~sorted[i]); };
+  const int mine = static_cast<int>(threadIdx.x) * RANK_PER;
+
+  // Inclusive prefix sums of the round starting at `begin`, over ranks below `limit`; `start` is the
+  // sum before this thread's first rank.
+  auto round_sums = [&](int begin, int limit, float (&w)[RANK_PER], float (&prefix)[RANK_PER], float& start) {
+    float local = 0.0f;
+#pragma unroll
+    for (int j = 0; j < RANK_PER; ++j) {
+      const int i = begin + mine + j;
+      w[j] = i < limit ? weight(i) : 0.0f;
+      local += w[j];
+    }
+    float total;
+    start = sh.carry + block_exclusive_scan(local, sh.scan, total);
+    float run = start;
+#pragma unroll
+    for (int j = 0; j < RANK_PER; ++j) { run += w[j]; prefix[j] = run; }
+    return total;
+  };
+  // Between rounds: the carry moves on after every thread has used it.
+  auto next_round = [&](float total) {
+    __syncthreads();
+    if (threadIdx.x == 0) sh.carry += total;
+    __syncthreads();
+  };
+
+  // The mass of the first k ranks, which the top-p threshold is a share of.
+  float mass = total_all;
+  if (p.top_p > 0.0 && k < V) {
+    if (k > n_sorted) return -1;
+    __syncthreads();
+    if (threadIdx.x == 0) sh.carry = 0.0f;
+    __syncthreads();
+    for (int begin = 0; begin < k; begin += RANK_BLOCK) {
+      float w[RANK_PER], prefix[RANK_PER], start;
+      const float total = round_sums(begin, k, w, prefix, start);
+#pragma unroll
+      for (int j = 0; j < RANK_PER; ++j)
+        if (begin + mine + j == k - 1) sh.total = prefix[j];
+      next_round(total);
+    }
+    mass = sh.total;
+  }
+  const float largest = weight(0);
+  const double threshold = p.top_p * static_cast<double>(mass);
+
+  // How many ranks stay, and their mass.
+  __syncthreads();
+  if (threadIdx.x == 0) { sh.carry = 0.0f; sh.cut = seen; sh.total = 0.0f; }
+  __syncthreads();
+  for (int begin = 0; begin < seen; begin += RANK_BLOCK) {
+    float w[RANK_PER], prefix[RANK_PER], start;
+    const float total = round_sums(begin, seen, w, prefix, start);
+    int cut = seen;
+#pragma unroll
+    for (int j = RANK_PER - 1; j >= 0; --j) {
+      const int i = begin + mine + j;
+      if (i >= seen) continue;
+      const float before = j == 0 ? start : prefix[j - 1];
+      bool stays = true;
+      if (p.top_p > 0.0 && i > 0 && !(static_cast<double>(before) < threshold)) stays = false;
+      if (p.min_p > 0.0 && !(static_cast<double>(w[j]) > p.min_p * static_cast<double>(largest))) stays = false;
+      if (!stays) cut = i;
+    }
+    if (cut < seen) atomicMin(&sh.cut, cut);
+    __syncthreads();
+    const int end = min(seen, begin + RANK_BLOCK);
+    const int keep_here = min(sh.cut, end);          // the ranks of this round that stay end here
+#pragma unroll
+    for (int j = 0; j < RANK_PER; ++j)
+      if (begin + mine + j == keep_here - 1) sh.total = prefix[j];
+    next_round(total);
+    if (sh.cut < end) break;
+  }
+  const int kept = sh.cut;
+  if (kept == seen && seen < k) return -1;           // the ranks that stay may go on beyond the sorted ones
+  if (kept == 0) return source[0];                   // cannot happen: rank 0 always stays
+  const float total_kept = sh.total;
+  const float target = fminf(p.uniform * total_kept, nextafterf(total_kept, 0.0f));
+
+  // The first rank with positive weight whose prefix sum exceeds the target, else the last positive one.
+  __syncthreads();
+  if (threadIdx.x == 0) { sh.carry = 0.0f; sh.first = kept; sh.last = -1; }
+  __syncthreads();
+  for (int begin = 0; begin < kept; begin += RANK_BLOCK) {
+    float w[RANK_PER], prefix[RANK_PER], start;
+    const float total = round_sums(begin, kept, w, prefix, start);
+    int first = kept, last = -1;
+#pragma unroll
+    for (int j = 0; j < RANK_PER; ++j) {
+      const int i = begin + mine + j;
+      if (i < kept && w[j] > 0.0f) {
+        last = i;
+        if (first == kept && prefix[j] > target) first = i;
+      }
+    }
+    if (first < kept) atomicMin(&sh.first, first);
+    if (last >= 0) atomicMax(&sh.last, last);
+    next_round(total);
+    if (sh.first < kept) break;
+  }
+  const int rank = sh.first < kept ? sh.first : sh.last;
+  return rank >= 0 ? source[rank] : -2;
+}
+
+__device__ float chunk_total(const float* part, int r, int chunks) {
+  float total = 0.0f;
+  for (int c = 0; c < chunks; ++c) total += part[r * chunks + c];
+  return total;
+}
+
+// ------------------------------------------------------------------- ranking the head of the order
+constexpr int HEAD_BINS = 4096;             // the keys' leading 12 bits
+constexpr int HEAD_MAX = 4096;              // tokens sorted in shared memory
+constexpr int HEAD_AIM = 2048;              // tokens the head is meant to have when the vocabulary is larger
+
+// One CTA per job.  job_state[2 * job] = how many ranks lie sorted in the job's second buffer;
+// job_state[2 * job + 1] = 1 if the row needs no more than those.
 __global__ void __launch_bounds__(ROW_THREADS)
-sample_select_sorted_kernel(int V, const SampleRow* __restrict__ rows, unsigned* keys, const int* __restrict__ idx,
-                            const float* __restrict__ row_max, const int* __restrict__ row_arg, int* out_ids) {
-  __shared__ float scratch[33];
-  __shared__ int s_first, s_last;
+sample_rank_head_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
+                        int chunks, const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
+                        const float* __restrict__ weights, const float* __restrict__ part_all, unsigned* keys, int* idx,
+                        const int* __restrict__ row_arg, int* job_state, int* out_ids) {
+  __shared__ unsigned long long candidates[HEAD_MAX];      // first used as the histogram
+  __shared__ RankScratch sh;
+  __shared__ int scratch[33];
+  __shared__ int s_bins, s_fill;
+  int* hist = reinterpret_cast<int*>(candidates);
+  const SortJob job = jobs[blockIdx.x];
+  const int r = job.row;
+  const SampleRow p = rows[r];
+  const float maximum = row_max[r];
+  if (threadIdx.x == 0) { job_state[2 * blockIdx.x] = 0; job_state[2 * blockIdx.x + 1] = 0; }
+  if (!isfinite(maximum)) return;
+  const double T = scaling_temperature(p);
+  const float* x = logits + static_cast<size_t>(r) * row_stride;
+  const float* w = weights + static_cast<size_t>(r) * V;
+  // Where the head ends is guessed from every `stride`-th token: the leading bins that hold
+  // HEAD_AIM / stride of them hold about HEAD_AIM tokens of the whole row.  The guess only decides how
+  // many ranks the head has (none, if more than HEAD_MAX tokens lie in those bins after all); the
+  // head is always every token of the leading bins, so it is the true start of the order.
+  const int stride = (V + HEAD_MAX - 1) / HEAD_MAX;
+  int bins = HEAD_BINS;
+  if (stride > 1) {
+    for (int e = threadIdx.x; e < HEAD_BINS; e += ROW_THREADS) hist[e] = 0;
+    if (threadIdx.x == 0) s_bins = 0;
+    __syncthreads();
+    for (int i = threadIdx.x * stride; i < V; i += ROW_THREADS * stride)
+      atomicAdd(&hist[sort_key(job, i, x, w, maximum, T) >> 20], 1);
+    __syncthreads();
+    constexpr int PER = HEAD_BINS / ROW_THREADS;
+    int counts[PER], local = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { counts[j] = hist[threadIdx.x * PER + j]; local += counts[j]; }
+    int total;
+    int run = block_exclusive_scan(local, scratch, total);
+    int leading = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      run += counts[j];
+      if (run * stride <= HEAD_AIM) leading = threadIdx.x * PER + j + 1;
+    }
+    if (leading > 0) atomicMax(&s_bins, leading);
+    __syncthreads();
+    bins = s_bins;
+    if (bins == 0) return;
+  }
+  __syncthreads();                                   // the histogram is done with
+  for (int e = threadIdx.x; e < HEAD_MAX; e += ROW_THREADS) candidates[e] = ~0ull;
+  if (threadIdx.x == 0) s_fill = 0;
+  __syncthreads();
+  // Loads run SORT_UNROLL steps ahead of their use.  A warp takes its places among the candidates with
+  // one addition for all its lanes.
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < V + lane; i += ROW_THREADS * SORT_UNROLL) {       // whole warps stay in the loop
+    unsigned key[SORT_UNROLL];
+#pragma unroll
+    for (int u = 0; u < SORT_UNROLL; ++u) {
+      const int e = i + u * ROW_THREADS;
+      key[u] = e < V ? sort_key(job, e, x, w, maximum, T) : ~0u;
+    }
+#pragma unroll
+    for (int u = 0; u < SORT_UNROLL; ++u) {
+      const int e = i + u * ROW_THREADS;
+      const bool take = e < V && static_cast<int>(key[u] >> 20) < bins;
+      const unsigned takers = __ballot_sync(0xffffffffu, take);
+      if (takers == 0) continue;
+      int base = 0;
+      if (lane == __ffs(takers) - 1) base = atomicAdd(&s_fill, __popc(takers));
+      base = __shfl_sync(0xffffffffu, base, __ffs(takers) - 1);
+      const int at = base + __popc(takers & ((1u << lane) - 1u));
+      if (take && at < HEAD_MAX)
+        candidates[at] = (static_cast<unsigned long long>(key[u]) << 32) | static_cast<unsigned>(e);
+    }
+  }
+  __syncthreads();
+  const int n = s_fill;
+  if (n == 0 || n > HEAD_MAX) return;                // more tokens in the leading bins than the guess allowed for
+  int padded = 1;
+  while (padded < n) padded <<= 1;
+  // Bitonic sort, ascending: by key, equal keys by index.
+  for (int size = 2; size <= padded; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < padded / 2; t += ROW_THREADS) {
+        const int low = 2 * t - (t & (stride - 1)), high = low + stride;
+        const bool ascending = (low & size) == 0;
+        const unsigned long long a = candidates[low], b = candidates[high];
+        if ((a > b) == ascending) { candidates[low] = b; candidates[high] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  unsigned* sorted = keys + (static_cast<size_t>(blockIdx.x) * 2 + 1) * V;
+  int* source = idx + (static_cast<size_t>(blockIdx.x) * 2 + 1) * V;
+  for (int e = threadIdx.x; e < n; e += ROW_THREADS) {
+    sorted[e] = static_cast<unsigned>(candidates[e] >> 32);
+    source[e] = static_cast<int>(candidates[e] & 0xffffffffu);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) job_state[2 * blockIdx.x] = n;
+  if (job.by_z) {
+    if (threadIdx.x == 0) job_state[2 * blockIdx.x + 1] = n >= min(p.num_logprobs, V);
+    return;
+  }
+  const int token = ranked_draw(p, sorted, source, n, V, chunk_total(part_all, r, chunks), sh);
+  if (threadIdx.x == 0 && token != -1) {
+    out_ids[p.result_offset] = token >= 0 ? token : row_arg[r];
+    job_state[2 * blockIdx.x + 1] = 1;
+  }
+}
+
+// One CTA per row: the draw of the rows whose whole vocabulary had to be ranked.
+__global__ void __launch_bounds__(ROW_THREADS)
+sample_select_sorted_kernel(int V, int chunks, const SampleRow* __restrict__ rows, const unsigned* __restrict__ keys,
+                            const int* __restrict__ idx, const float* __restrict__ row_max,
+                            const int* __restrict__ row_arg, const float* __restrict__ part_all,
+                            const int* __restrict__ job_state, int* out_ids) {
+  __shared__ RankScratch sh;
   const int r = blockIdx.x;
   const SampleRow p = rows[r];
   if (!is_ranked(p) || p.sort_slot < 0) return;
@@ -433,53 +694,11 @@ sample_select_sorted_kernel(int V, const SampleRow* __restrict__ rows, unsigned*
     if (threadIdx.x == 0) out_ids[p.result_offset] = row_arg[r];
     return;
   }
+  if (job_state[2 * p.sort_slot + 1]) return;
   const unsigned* sorted = keys + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
   const int* source = idx + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
-  float* prefix = reinterpret_cast<float*>(keys + static_cast<size_t>(p.sort_slot) * 2 * V);
-  const int k = p.top_k > 0 ? min(p.top_k, V) : V;
-  const int per = (k + ROW_THREADS - 1) / ROW_THREADS;
-  const int begin = min(k, static_cast<int>(threadIdx.x) * per), end = min(k, begin + per);
-  auto weight = [&](int i) { return __uint_as_float(~sorted[i]); };
-  if (threadIdx.x == 0) { s_first = k; s_last = -1; }
-
-  float mass = 0.0f;            // of the first k ranks, as the prefix sums give it
-  if (p.top_p > 0.0) {
-    float local = 0.0f;
-    for (int i = begin; i < end; ++i) local += weight(i);
-    float total;
-    float run = block_exclusive_scan(local, scratch, total);
-    for (int i = begin; i < end; ++i) { run += weight(i); prefix[i] = run; }
-    __syncthreads();
-    mass = prefix[k - 1];
-  }
-  const float largest = weight(0);
-  auto kept_weight = [&](int i) -> float {
-    const float wi = weight(i);
-    if (p.top_p > 0.0 && i > 0 && !(static_cast<double>(prefix[i - 1]) < p.top_p * static_cast<double>(mass))) return 0.0f;
-    if (p.min_p > 0.0 && !(static_cast<double>(wi) > p.min_p * static_cast<double>(largest))) return 0.0f;
-    return wi;
-  };
-  float local = 0.0f;
-  for (int i = begin; i < end; ++i) local += kept_weight(i);
-  float total;
-  float run = block_exclusive_scan(local, scratch, total);
-  const float target = fminf(p.uniform * total, nextafterf(total, 0.0f));
-  int first = k, last = -1;
-  for (int i = begin; i < end; ++i) {
-    const float wi = kept_weight(i);
-    run += wi;
-    if (wi > 0.0f) {
-      last = i;
-      if (first == k && run > target) first = i;
-    }
-  }
-  if (first < k) atomicMin(&s_first, first);
-  if (last >= 0) atomicMax(&s_last, last);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int rank = s_first < k ? s_first : s_last;
-    out_ids[p.result_offset] = rank >= 0 ? source[rank] : row_arg[r];
-  }
+  const int token = ranked_draw(p, sorted, source, job_state[2 * p.sort_slot], V, chunk_total(part_all, r, chunks), sh);
+  if (threadIdx.x == 0) out_ids[p.result_offset] = token >= 0 ? token : row_arg[r];
 }
 
 // ---------------------------------------------------------------------------------- reports
@@ -535,20 +754,21 @@ constexpr int PHASE_REPORT = 8;         // some row reports log-probabilities
 //                results start at its result_offset: the chosen token, then its top tokens if it reports.
 //   out_logprobs parallel to out_ids, written for reporting rows only; may be null without PHASE_REPORT.
 //   jobs         the rows to rank, by weight (draws with top-k or top-p) or by z (reports with n > 0);
-//                sort_keys and sort_idx hold 2 * n_jobs * V entries each.
+//                sort_keys and sort_idx hold 2 * n_jobs * V entries each, job_state 2 * n_jobs ints.
 //   part_f       3 * rows * chunks floats; part_i rows * chunks ints; counters: rows ints, zero on entry and
 //                on exit; row_max, row_arg: rows entries; weights: rows * V floats (unused without PHASE_WEIGHTS).
 ZB_API int zb_sample(int* out_ids, float* out_logprobs, float* logits, long long row_stride, int rows, int V,
                      const void* row_params, const void* adjustments, int n_adjustments, const void* jobs, int n_jobs,
                      int phases, float* part_f, int* part_i, int* counters, float* row_max, int* row_arg,
-                     float* weights, unsigned* sort_keys, int* sort_idx, int* status, void* stream) {
+                     float* weights, unsigned* sort_keys, int* sort_idx, int* job_state, int* status, void* stream) {
   if (rows < 0 || V <= 0 || row_stride < V || n_adjustments < 0 || n_jobs < 0) return ERR_BAD_ARGUMENT;
   if (V > SAMPLE_MAX_VOCAB || rows > 65535) return ERR_UNSUPPORTED;
   if (rows == 0) return OK;
   if (row_params == nullptr && (phases != 0 || n_adjustments > 0 || n_jobs > 0)) return ERR_BAD_ARGUMENT;
   if ((phases & PHASE_REPORT) && out_logprobs == nullptr) return ERR_BAD_ARGUMENT;
   if (phases != 0 && weights == nullptr) return ERR_BAD_ARGUMENT;
-  if (n_jobs > 0 && (sort_keys == nullptr || sort_idx == nullptr || jobs == nullptr)) return ERR_BAD_ARGUMENT;
+  if (n_jobs > 0 && (sort_keys == nullptr || sort_idx == nullptr || jobs == nullptr || job_state == nullptr))
+    return ERR_BAD_ARGUMENT;
   auto s = static_cast<cudaStream_t>(stream);
   const auto* params = static_cast<const SampleRow*>(row_params);
   const int chunks = zb_sample_chunks(V);
@@ -564,13 +784,18 @@ ZB_API int zb_sample(int* out_ids, float* out_logprobs, float* logits, long long
   if (phases & PHASE_WEIGHTS)
     sample_exp_kernel<<<chunk_grid, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, row_max, weights,
                                                           part_all, part_kept);
-  if (n_jobs > 0)
+  if (n_jobs > 0) {
+    sample_rank_head_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, chunks,
+                                                          params, row_max, weights, part_all, sort_keys, sort_idx, row_arg,
+                                                          job_state, out_ids);
     sample_sort_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, params,
-                                                     row_max, weights, sort_keys, sort_idx);
+                                                     row_max, weights, sort_keys, sort_idx, job_state);
+  }
   if (phases & PHASE_DRAW_INDEXED)
     sample_select_kernel<<<rows, ROW_THREADS, 0, s>>>(weights, V, chunks, params, part_kept, row_max, row_arg, out_ids);
   if (phases & PHASE_DRAW_RANKED)
-    sample_select_sorted_kernel<<<rows, ROW_THREADS, 0, s>>>(V, params, sort_keys, sort_idx, row_max, row_arg, out_ids);
+    sample_select_sorted_kernel<<<rows, ROW_THREADS, 0, s>>>(V, chunks, params, sort_keys, sort_idx, row_max, row_arg,
+                                                            part_all, job_state, out_ids);
   if (phases & PHASE_REPORT)
     sample_report_kernel<<<rows, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, row_max, part_all,
                                                        sort_idx, out_ids, out_logprobs);

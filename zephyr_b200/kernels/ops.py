@@ -84,7 +84,7 @@ _SIGNATURES = {
     "zb_sample_chunks": [c_int],
     "zb_sample": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_void_p],
+                  c_void_p, c_void_p],
 }
 
 
@@ -754,7 +754,7 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[SampleRow] | None, status: 
         ids = torch.empty(R, dtype=torch.int32, device=device)
         _check(library().zb_sample(_ptr(ids), None, _ptr(logits), logits.stride(0), R, V, None, None, 0, None, 0, 0,
                                    _ptr(part_f), _ptr(part_i), _ptr(counters), _ptr(row_max), _ptr(row_arg), None,
-                                   None, None, _ptr(status), _stream()), "sample")
+                                   None, None, None, _ptr(status), _stream()), "sample")
         return SampleOutput(ids, None, list(range(R)))
     _require(len(rows) == R, "one SampleRow per row of logits")
 
@@ -801,13 +801,27 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[SampleRow] | None, status: 
     weights = _sample_buffer(device, "weights", R * V, torch.float32) if phases else None
     sort_keys = _sample_buffer(device, "sort_keys", 2 * len(jobs) * V, torch.int32) if jobs else None
     sort_idx = _sample_buffer(device, "sort_idx", 2 * len(jobs) * V, torch.int32) if jobs else None
+    job_state = _sample_buffer(device, "job_state", 2 * len(jobs), torch.int32) if jobs else None
     _check(library().zb_sample(
         _ptr(ids), _ptr(logprobs), _ptr(logits), logits.stride(0), R, V, base,
         base + at_adjustments if adjustments else None, len(adjustments), base + at_jobs if jobs else None, len(jobs),
         phases, _ptr(part_f), _ptr(part_i), _ptr(counters), _ptr(row_max), _ptr(row_arg), _ptr(weights),
-        _ptr(sort_keys), _ptr(sort_idx), _ptr(status), _stream()),
-        "sample", kernels=1 + bool(adjustments) + bool(jobs) + bin(phases).count("1"))
+        _ptr(sort_keys), _ptr(sort_idx), _ptr(job_state), _ptr(status), _stream()),
+        "sample", kernels=1 + bool(adjustments) + 2 * bool(jobs) + bin(phases).count("1"))
+    _sample_buffers[(device, "jobs_of_last_call")] = len(jobs)
     return SampleOutput(ids, logprobs, offsets)
+
+
+def last_sample_job_state(device: torch.device | str | None = None) -> list[tuple[int, bool]]:
+    """For every ranking of the last ``sample_rows`` call on ``device``, in the order of the rows (a
+    row's draw before its report): how many ranks were sorted, and whether the head of the order was
+    enough.  Reads from the device; for tests and timing."""
+    device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    count = _sample_buffers.get((device, "jobs_of_last_call"), 0)
+    if not count:
+        return []
+    state = _sample_buffers[(device, "job_state")][:2 * count].cpu().view(count, 2).tolist()
+    return [(int(n), bool(done)) for n, done in state]
 
 
 def sample(logits: torch.Tensor, status: torch.Tensor) -> torch.Tensor:

@@ -139,7 +139,7 @@ def gemm_small(args) -> dict:
 def sample(args) -> dict:
     device = torch.device("cuda")
     R, V = args.rows, args.vocab
-    logits = [torch.randn((R, V), device=device, dtype=torch.float32) for _ in range(_copies(R * V * 4))]
+    logits = [torch.randn((R, V), device=device, dtype=torch.float32) * args.logit_scale for _ in range(_copies(R * V * 4))]
     rows = None
     if args.temperature >= 1e-7 or args.top_logprobs >= 0:
         rows = [ops.SampleRow(temperature=args.temperature, uniform=0.1 + 0.8 * r / R, top_k=args.top_k,
@@ -150,8 +150,10 @@ def sample(args) -> dict:
         ops.sample_rows(logits[i % len(logits)], rows, status)
     us = _time(run, args.warmup, args.iters)
     ops.check_status(status, "sample")
+    state = ops.last_sample_job_state()
     return {"kernel": "sample kernels", "rows": R, "vocab": V, "temperature": args.temperature, "top_k": args.top_k,
-            "top_p": args.top_p, "min_p": args.min_p, "top_logprobs": args.top_logprobs, "us": round(us, 2)}
+            "top_p": args.top_p, "min_p": args.min_p, "top_logprobs": args.top_logprobs, "logit_scale": args.logit_scale,
+            "rankings": len(state), "rankings_decided_in_the_head": sum(done for _, done in state), "us": round(us, 2)}
 
 
 def fused_chain(args) -> dict:
@@ -214,6 +216,7 @@ def main(argv=None) -> int:
     parser.add_argument("--top-p", type=float, default=0.0)
     parser.add_argument("--min-p", type=float, default=0.0)
     parser.add_argument("--top-logprobs", type=int, default=-1)
+    parser.add_argument("--logit-scale", type=float, default=1.0, help="the logits are normal draws times this")
     parser.add_argument("--sequential-pages", action="store_true",
                         help="block tables that walk the pool in order instead of a random permutation")
     parser.add_argument("--legacy-prefill", action="store_true", help="prompt attention on mma.sync even where tcgen05 applies")
