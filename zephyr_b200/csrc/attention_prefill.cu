@@ -47,10 +47,10 @@ paged_prefill_kernel(const PrefillArgs a) {
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [PRE_BM][KROW]
   __nv_bfloat16* ring = q_s + PRE_BM * KROW;                             // [2][keys, values][PRE_BN][KROW]
 
-  // The tile list runs through each request's new tokens front to back, and under the causal mask
-  // later tiles have more keys to visit: take the list back to front, the long tiles first, so
-  // that the short ones fill the gaps at the end instead of the other way round.
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // The host lists the tiles by the number of keys they see, fewest first: take the list back to
+  // front, and all heads of a tile before the next tile, so that the longest work of the whole
+  // launch starts first and the short tiles fill the gaps at the end.
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
@@ -222,7 +222,7 @@ int prefill_launch(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
   auto kernel = paged_prefill_kernel<HD>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<dim3(n_tiles, a.nh), PRE_WARPS * 32, smem, stream>>>(a);
+  kernel<<<dim3(a.nh, n_tiles), PRE_WARPS * 32, smem, stream>>>(a);
   return launch_result();
 }
 
@@ -246,6 +246,7 @@ ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, cons
   if (n_tiles < 0 || page_size <= 0 || window < 0) return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
+  if (n_tiles > 65535) return ERR_UNSUPPORTED;
   PrefillArgs a;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.out = static_cast<__nv_bfloat16*>(out);

@@ -201,9 +201,10 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
   __shared__ unsigned tmem_base_s;
   __shared__ volatile int abort_flag;
 
-  // The tile list runs front to back through each request's new tokens and later tiles see more
-  // keys: take it back to front, long tiles first.
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // The host lists the tiles by the number of keys they see, fewest first: take the list back to
+  // front, and all heads of a tile before the next tile, so that the longest work of the whole
+  // launch starts first and the short tiles fill the gaps at the end.
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
@@ -562,6 +563,7 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
       reinterpret_cast<uintptr_t>(kv_cache) % 16 != 0)
     return ERR_BAD_ARGUMENT;
   if (n_tiles == 0) return OK;
+  if (n_tiles > 65535) return ERR_UNSUPPORTED;
   PrefillTcArgs a;
   const long long cache_rows = static_cast<long long>(num_pages) * 2 * nkv * page_size;
   a.tiled = cache_rows < (1LL << 31) &&
@@ -581,6 +583,6 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
   const size_t smem = 1024 + 7 * TC_TILE_BYTES + 14 * sizeof(unsigned long long);
   if (cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  paged_prefill_tc_kernel<<<dim3(n_tiles, nh), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
+  paged_prefill_tc_kernel<<<dim3(nh, n_tiles), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
   return launch_result();
 }

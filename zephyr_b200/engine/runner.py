@@ -140,7 +140,11 @@ class ModelRunner:
                 for q0 in range(0, n, tile_tokens):
                     tile_row.append(i)
                     tile_q0.append(q0)
-            tiles[(tile_tokens, which)] = (np.asarray(tile_row, dtype=np.int32), np.asarray(tile_q0, dtype=np.int32))
+            # By the number of keys a tile sees, fewest first (the kernels start at the far end of the
+            # list, so the longest tiles of the whole step run first).
+            order = sorted(range(len(tile_row)), key=lambda t: ctx_before[tile_row[t]] + tile_q0[t])
+            tiles[(tile_tokens, which)] = (np.asarray([tile_row[t] for t in order], dtype=np.int32),
+                                           np.asarray([tile_q0[t] for t in order], dtype=np.int32))
         arrays = [token_ids, positions, token_row, q_start, np.asarray(q_len, dtype=np.int32),
                   np.asarray(ctx_before, dtype=np.int32), slots, logit_tokens, decode_rows]
         arrays += [t.reshape(-1) for t in tables]
