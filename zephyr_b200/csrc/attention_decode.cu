@@ -239,6 +239,10 @@ paged_decode_kernel(const DecodeArgs a) {
   }
   __syncthreads();
   fence_proxy_async();
+  // Up to here nothing of an earlier kernel's output was read (the step's description is older than
+  // any kernel of the step); the queries and the newest keys and values are.
+  wait_for_prior_grids();
+  let_dependents_launch();
   // Balanced items: as many tiles per range as spread all tiles evenly over the CTAs.
   const int per_range = a.split_size == 0 ? max(1, (prefix[a.n_rows] + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) : 0;
   const int page_size = 1 << a.page_shift;
@@ -573,8 +577,7 @@ int decode_launch(DecodeArgs& a, cudaStream_t stream) {
   auto kernel = paged_decode_kernel<HD>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<grid, DEC_THREADS, smem, stream>>>(a);
-  return launch_result();
+  return launch_dependent(kernel, dim3(grid), dim3(DEC_THREADS), smem, stream, false, a);
 }
 
 }  // namespace zb

@@ -106,6 +106,47 @@ inline int launch_result() {
   return cudaPeekAtLastError() == cudaSuccess ? OK : ERR_CUDA;
 }
 
+// Programmatic dependent launch.  A kernel launched with `launch_dependent` may start while the
+// kernel before it in the stream is still running: its CTAs take the SMs as they become free and
+// do whatever does not read the earlier kernel's results (shared memory set-up, barriers, plans from
+// the step's description, weights).  `wait_for_prior_grids` then blocks until every earlier kernel
+// has completed and its writes are visible; nothing an earlier kernel wrote is read, and nothing it
+// reads is written, before that.  `let_dependents_launch`, called after the wait, lets the next
+// kernel start in the same way (called before the wait, the order of completion would no longer be
+// a chain).  In a kernel launched the ordinary way both are no-ops.
+__device__ __forceinline__ void wait_for_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool& dependent_launch_enabled() {
+  static bool enabled = true;
+  return enabled;
+}
+
+template <typename... Params, typename... Args>
+inline int launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            bool cooperative, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int n = 0;
+  if (dependent_launch_enabled()) {
+    attributes[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cooperative) {
+    attributes[n].id = cudaLaunchAttributeCooperative;
+    attributes[n].val.cooperative = 1;
+    ++n;
+  }
+  config.attrs = attributes;
+  config.numAttrs = n;
+  return cudaLaunchKernelEx(&config, kernel, Params(args)...) == cudaSuccess ? launch_result() : ERR_CUDA;
+}
+
 }  // namespace zb
 
 #define ZB_API extern "C" __attribute__((visibility("default")))

@@ -81,8 +81,8 @@ struct ChainArgs {
   int n_stages, M, ring_shift, xs_row_bytes;      // the ring holds 1 << ring_shift slots
   int* sync;                         // [0] barrier arrivals, [1] CTAs done; zero on entry and on exit
   int* status;
-  int* trace;                        // null, or 4 ints per stage: CTA 1's clock at the stage's start, after its input
-                                     // is in place, after its products, after the barrier (cycles since the CTA began)
+  int* trace;                        // null, or [CTA][stage][4] ints: the global timer (ns, low 32 bits) at the stage's
+                                     // start, after its input is in place, after its products, after the barrier
 };
 
 struct StagePlan { int tiles_per_block, b0, b1, chunks; };
@@ -207,16 +207,25 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
   const bool lo_ok = g < M, hi_ok = HI && g + 8 < M;
   constexpr int RM = HI ? 16 : 8;     // token rows kept
   int seq = 0, barriers = 0, x_uses = 0;
-  const long long began = clock64();
-  const bool tracing = a.trace != nullptr && cta == 1 && ctid == 0;
+  const bool tracing = a.trace != nullptr && ctid == 0;
+  int* const trace = a.trace + static_cast<size_t>(cta) * 4 * a.n_stages;
+  auto now = [] {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return static_cast<int>(t);
+  };
   // A warp whose wait runs out reports, raises the abort flag and walks on without waiting or
   // computing: the barriers among the consumers need every warp to the very end.
   bool failed = false;
+  // The producer is already streaming weights, which no kernel writes; the inputs, the residual and
+  // the barrier's counters are earlier kernels' business until this returns.
+  wait_for_prior_grids();
+  let_dependents_launch();
   for (int s = 0; s < a.n_stages; ++s) {
     const ChainStage& st = a.stage[s];
     const StagePlan p = plans[s];
     const int K = st.K;
-    if (tracing) a.trace[4 * s] = static_cast<int>(clock64() - began);
+    if (tracing) trace[4 * s] = now();
 
     // ---- the stage's input, [M, K] bfloat16 in shared memory
     if (st.prologue == PROLOGUE_NONE) {
@@ -360,7 +369,7 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
       }
     }
     chain_consumer_barrier();
-    if (tracing) a.trace[4 * s + 1] = static_cast<int>(clock64() - began);
+    if (tracing) trace[4 * s + 1] = now();
 
     // ---- the products.  The CTA's blocks are taken in groups of up to 8 tiles.  Every warp works
     // on every slot: of a slot's 32 k-blocks it takes four (warp, warp + 8, ...), so the input's
@@ -447,7 +456,7 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
       }
       chain_consumer_barrier();
     }
-    if (tracing) a.trace[4 * s + 2] = static_cast<int>(clock64() - began);
+    if (tracing) trace[4 * s + 2] = now();
 
     if (s + 1 < a.n_stages) {
       // The barrier across the grid.  The CTA's barrier orders its threads' stores before thread 0,
@@ -470,7 +479,7 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
       chain_consumer_barrier();
       failed = failed || abort_flag != 0;
     }
-    if (tracing) a.trace[4 * s + 3] = static_cast<int>(clock64() - began);
+    if (tracing) trace[4 * s + 3] = now();
   }
 
   chain_consumer_barrier();           // nobody raises the flag after this point
@@ -542,7 +551,26 @@ ZB_API int zb_fused_chain_stage_supported(int M, int N, int K, int prologue, int
 
 ZB_API int zb_fused_chain_max_stages() { return CH_MAX_STAGES; }
 
-// `trace`: null, or 4 * n_stages ints on the device that receive one CTA's timeline (see ChainArgs).
+// Whether the kernels of a decode step (position encoding with cache write, decode attention, chain)
+// are launched as programmatic dependents of the kernel before them (on by default).  Returns the
+// setting that was in force.
+ZB_API int zb_set_dependent_launch(int enabled) {
+  const int before = dependent_launch_enabled() ? 1 : 0;
+  dependent_launch_enabled() = enabled != 0;
+  return before;
+}
+
+// CTAs of a launch: one per SM of the current device (0 if the device cannot be asked).
+ZB_API int zb_fused_chain_grid() {
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    return 0;
+  return sms;
+}
+
+// `trace`: null, or zb_fused_chain_grid() * n_stages * 4 ints on the device that receive every CTA's
+// timeline (see ChainArgs).
 // Runs `n_stages` stages (an array of ChainStage on the host) for M tokens.  `sync`: two ints on the
 // device, zero on entry, left zero.  The launch is cooperative: one CTA per SM.
 ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, int* status, int* trace, void* stream) {
@@ -597,9 +625,8 @@ ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, in
              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_chain_kernel<false>, CH_THREADS, smem)) != cudaSuccess)
     return ERR_CUDA;
   if (per_sm < 1) return ERR_UNSUPPORTED;
-  void* params[] = {&a};
-  if (cudaLaunchCooperativeKernel(kernel, dim3(sms), dim3(CH_THREADS), params,
-                                  smem, static_cast<cudaStream_t>(stream)) != cudaSuccess)
-    return ERR_CUDA;
-  return launch_result();
+  return M > 8 ? launch_dependent(fused_chain_kernel<true>, dim3(sms), dim3(CH_THREADS), smem,
+                                  static_cast<cudaStream_t>(stream), true, a)
+               : launch_dependent(fused_chain_kernel<false>, dim3(sms), dim3(CH_THREADS), smem,
+                                  static_cast<cudaStream_t>(stream), true, a);
 }

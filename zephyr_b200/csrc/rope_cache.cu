@@ -184,6 +184,8 @@ qk_norm_rope_cache_wide_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfl
   const int pos = positions[t];
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
   const int i = 4 * sub;                                        // this lane's elements i .. i + 3 and i + HALF ..
+  wait_for_prior_grids();           // the projections are an earlier kernel's output
+  let_dependents_launch();
   float x[4] = {0, 0, 0, 0}, y[4] = {0, 0, 0, 0};
   if (active) {
     const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * qkv_stride + static_cast<size_t>(head) * HD;
@@ -325,13 +327,13 @@ ZB_API int zb_qk_norm_rope_cache(void* q_out, const void* qkv, long long qkv_str
     const int per_warp = hd == 64 ? 4 : 2;
     const dim3 wide(T, (heads + ROPE_WARPS * per_warp - 1) / (ROPE_WARPS * per_warp));
     if (hd == 64)
-      qk_norm_rope_cache_wide_kernel<64><<<wide, ROPE_WARPS * 32, 0, s>>>(
-          (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
-          sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
+      return launch_dependent(qk_norm_rope_cache_wide_kernel<64>, wide, dim3(ROPE_WARPS * 32), 0, s, false,
+                              (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps,
+                              cos_table, sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
     else
-      qk_norm_rope_cache_wide_kernel<128><<<wide, ROPE_WARPS * 32, 0, s>>>(
-          (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
-          sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
+      return launch_dependent(qk_norm_rope_cache_wide_kernel<128>, wide, dim3(ROPE_WARPS * 32), 0, s, false,
+                              (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps,
+                              cos_table, sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
   } else
     qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, 0, s>>>(
         (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 import struct
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
@@ -80,6 +81,8 @@ _SIGNATURES = {
                         c_int, c_int, c_void_p],
     "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
     "zb_fused_chain_max_stages": [],
+    "zb_fused_chain_grid": [],
+    "zb_set_dependent_launch": [c_int],
     "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_sample_chunks": [c_int],
     "zb_sample": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -111,6 +114,8 @@ def library() -> ctypes.CDLL:
             lib.zb_paged_decode_scratch_floats.restype = c_longlong
             lib.zb_paged_decode_balanced_scratch_floats.argtypes = [c_int, c_int, c_int]
             lib.zb_paged_decode_balanced_scratch_floats.restype = c_longlong
+            if os.environ.get("ZEPHYR_B200_DEPENDENT_LAUNCH", "1") == "0":
+                lib.zb_set_dependent_launch(0)
             _lib = lib
     return _lib
 
@@ -602,12 +607,25 @@ def fused_chain_max_stages() -> int:
 _chain_sync: dict[torch.device, torch.Tensor] = {}
 
 
+def set_dependent_launch(enabled: bool) -> bool:
+    """Launch the kernels of a decode step (position encoding with cache write, decode attention,
+    chain) as programmatic dependents of the kernel before them: a kernel's CTAs then set themselves
+    up while the one before is still finishing.  On by default; returns the previous setting."""
+    return bool(library().zb_set_dependent_launch(int(bool(enabled))))
+
+
+def fused_chain_grid() -> int:
+    """CTAs of a chain launch (one per SM)."""
+    return int(library().zb_fused_chain_grid())
+
+
 def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
                 trace: torch.Tensor | None = None) -> None:
     """Run the stages one after the other in one cooperative launch (see csrc/fused_chain.cu).
     Every tensor is bfloat16 on the device (a norm weight may be float32); rows are contiguous.
-    ``trace`` (int32, 4 per stage) receives one CTA's timeline in clock cycles: the stage's start,
-    its input in place, its products done, the barrier passed."""
+    ``trace`` (int32 [fused_chain_grid(), stages, 4]) receives every CTA's timeline, nanoseconds of
+    the device's global timer (low 32 bits): the stage's start, its input in place, its products
+    done, the barrier passed."""
     _require(1 <= len(stages) <= fused_chain_max_stages(), "a chain has 1 to 8 stages")
     _require(1 <= tokens <= FUSED_CHAIN_MAX_TOKENS, "a chain takes 1 to 16 tokens")
     packed = (_ChainStage * len(stages))()
@@ -641,8 +659,8 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
         sync = _chain_sync[device] = torch.zeros(2, dtype=torch.int32, device=device)
     if trace is not None:
         _cuda(trace)
-        _require(trace.dtype == torch.int32 and trace.is_contiguous() and trace.numel() >= 4 * len(stages),
-                 "trace must hold 4 int32 values per stage")
+        _require(trace.dtype == torch.int32 and trace.is_contiguous()
+                 and trace.numel() >= 4 * len(stages) * fused_chain_grid(), "trace must be int32 [fused_chain_grid(), stages, 4]")
     _check(library().zb_fused_chain(ctypes.addressof(packed), len(stages), int(tokens), _ptr(sync), _ptr(status),
                                     _ptr(trace), _stream()), "fused_chain")
 

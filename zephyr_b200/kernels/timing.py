@@ -156,6 +156,16 @@ def sample(args) -> dict:
             "rankings": len(state), "rankings_decided_in_the_head": sum(done for _, done in state), "us": round(us, 2)}
 
 
+def _chain_timeline(trace: torch.Tensor) -> dict:
+    """The last launch's stages over all CTAs: when the first and the last CTA reached each mark
+    (start, input in place, products done, barrier passed), nanoseconds from the earliest start."""
+    t = trace.cpu().to(torch.int64)
+    t = (t - t[:, 0, 0].min()) & 0xFFFFFFFF
+    marks = ("start", "input", "products", "barrier")
+    return {f"stage{s}": {m: [int(t[:, s, i].min()), int(t[:, s, i].max())] for i, m in enumerate(marks)}
+            for s in range(t.shape[1])}
+
+
 def fused_chain(args) -> dict:
     """A layer's tail as one chain: output projection, add + norm + gate/up + silu * up, down
     projection, add + norm + the next layer's input projection."""
@@ -169,7 +179,7 @@ def fused_chain(args) -> dict:
     buf = lambda n: torch.empty((M, n), device=device, dtype=torch.bfloat16)
     o, act, down, out, r1, r2 = buf(d), buf(ffn), buf(d), buf(qkv), buf(d), buf(d)
     status = ops.new_status(device)
-    trace = torch.zeros(16, dtype=torch.int32, device=device)
+    trace = torch.zeros((ops.fused_chain_grid(), 4, 4), dtype=torch.int32, device=device)
 
     def run(i):
         w_o, w_gu, w_down, w_qkv = layers[i % len(layers)]
@@ -182,7 +192,7 @@ def fused_chain(args) -> dict:
     ops.check_status(status, "fused_chain")
     return {"kernel": "fused_chain_kernel", "rows": M, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv, "us": round(us, 2),
             "bytes_read": layer_bytes, "gbs": round(layer_bytes / us / 1e3, 1),
-            "cycles_start_input_products_barrier": trace.view(4, 4).tolist()}
+            "timeline_ns": _chain_timeline(trace)}
 
 
 CASES = {"fused_chain": fused_chain, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
