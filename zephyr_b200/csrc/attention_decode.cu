@@ -56,7 +56,17 @@ struct DecodeArgs {
   int nh, nkv, window, split_size, max_splits, ring_slots, item_pages;
   float scale_log2;              // scale * log2(e)
   int* status;
+  int* trace;                    // null, or [CTA][8] ints: the global timer (ns, low 32 bits) at the CTA's start, after
+                                 // the wait for earlier kernels, when its first tile had landed, after its last tile,
+                                 // at its end; then its items and its tiles, and when its last arrival among a
+                                 // row's splits was counted
 };
+
+__device__ __forceinline__ int timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return static_cast<int>(t);
+}
 
 // How a (request, key/value head) pair's context is cut into work items.
 //   Fixed splits (split_size > 0): item = (row, head, split of split_size positions); CTAs take items in
@@ -202,6 +212,8 @@ paged_decode_kernel(const DecodeArgs a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) abort_flag = 0;
+  int* const trace = a.trace != nullptr && threadIdx.x == 0 ? a.trace + 8 * blockIdx.x : nullptr;
+  if (trace) trace[0] = timer_ns();
   // A bounded wait that also ends when another warp has given up.
   auto wait = [&](unsigned long long* bar, unsigned parity) -> bool {
     for (int i = 0; i < DEC_WAIT_LIMIT; ++i) {
@@ -239,9 +251,11 @@ paged_decode_kernel(const DecodeArgs a) {
   }
   __syncthreads();
   fence_proxy_async();
-  // Up to here nothing of an earlier kernel's output was read (the step's description is older than
-  // any kernel of the step); the queries and the newest keys and values are.
-  wait_for_prior_grids();
+  // Up to here nothing of an earlier kernel's output was read: the step's description is older than
+  // any kernel of the step.  The queries and each row's newest key and value are an earlier kernel's
+  // output; the rest of the cache is older than the step.  So the consumers wait for the earlier
+  // kernels at once, and a producer only before the first copy that reads their output: the ring
+  // fills with old keys and values while the kernel before this one is still running.
   let_dependents_launch();
   // Balanced items: as many tiles per range as spread all tiles evenly over the CTAs.
   const int per_range = a.split_size == 0 ? max(1, (prefix[a.n_rows] + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) : 0;
@@ -258,6 +272,15 @@ paged_decode_kernel(const DecodeArgs a) {
     ItemWalker walker;
     walker_init(walker);
     DecodeItem it;
+    bool waited = false;               // for the earlier kernels
+    bool q_pending = false;            // the first producer: the item's queries are still to be fetched
+    auto fetch_queries = [&](int qb) {
+      if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
+      if (lane < g)
+        bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
+                      a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
+                      ROW_BYTES, &qfull[qb]);
+    };
     while (next_item(a, prefix, per_range, walker, it)) {
       const int qb = item_seq & 1;
       if (me == 0) {
@@ -266,11 +289,10 @@ paged_decode_kernel(const DecodeArgs a) {
           abort_flag = 1;
           return;
         }
-        if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
-        if (lane < g)
-          bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
-                        a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
-                        ROW_BYTES, &qfull[qb]);
+        // The queries are an earlier kernel's output.  Before the wait for it, the ring's first
+        // filling goes out (nothing can hold those copies up); then the wait, then the queries.
+        if (waited) fetch_queries(qb);
+        else q_pending = true;
       }
       ++item_seq;
       // The item's page ids in one go (one round trip to memory per item instead of one per tile).
@@ -290,6 +312,16 @@ paged_decode_kernel(const DecodeArgs a) {
       for (int t = 0; t < it.n_tiles; ++t, ++tile_seq) {
         if (tile_seq % DEC_PRODUCERS != me) continue;
         const int slot = tile_seq % R, filling = tile_seq / R;
+        // The tile that holds the row's newest position was written by an earlier kernel of this step.
+        const bool newest = it.first_tile + (t + 1) * DEC_TILE >= it.ctx_total;
+        if (!waited && (newest || (q_pending && filling > 0))) {
+          wait_for_prior_grids();
+          waited = true;
+        }
+        if (q_pending && waited) {
+          fetch_queries(qb);
+          q_pending = false;
+        }
         bool released = consumed[slot] >= filling;
         for (int i = 0; !released && i < DEC_WAIT_LIMIT && !abort_flag; ++i) released = consumed[slot] >= filling;
         if (!released || !wait(&empty[slot], (filling & 1) ^ 1)) {
@@ -322,6 +354,12 @@ paged_decode_kernel(const DecodeArgs a) {
         const unsigned copied_runs = __popc(__ballot_sync(0xffffffffu, copies));
         if (lane == 0) mbar_arrive_expect_tx(&full[slot], copied_runs * run_rows * 2u * ROW_BYTES);
       }
+      if (q_pending) {         // an item with few tiles, none of them the newest
+        wait_for_prior_grids();
+        waited = true;
+        fetch_queries(qb);
+        q_pending = false;
+      }
       __syncwarp();            // every lane is done with this item's page ids before the next item's overwrite them
     }
     return;
@@ -334,6 +372,8 @@ paged_decode_kernel(const DecodeArgs a) {
   ItemWalker walker;
   walker_init(walker);
   DecodeItem it;
+  wait_for_prior_grids();      // the consumers write results, and read queries: both wait for the kernels before
+  if (trace) trace[1] = trace[2] = trace[3] = timer_ns();
   while (next_item(a, prefix, per_range, walker, it)) {
     const int qb = item_seq & 1;
     // A consumer whose wait runs out reports, raises the abort flag and keeps walking the items
@@ -365,6 +405,7 @@ paged_decode_kernel(const DecodeArgs a) {
         abort_flag = 1;
         break;
       }
+      if (trace && seq == 0) trace[2] = timer_ns();
       __nv_bfloat16* ks_tile = ring + static_cast<size_t>(slot) * SLOT;
       __nv_bfloat16* vs_tile = ks_tile + DEC_TILE * HD;
       const int key0 = it.first_tile + j * DEC_TILE;
@@ -460,6 +501,7 @@ paged_decode_kernel(const DecodeArgs a) {
       }
     }
     tile_base += it.n_tiles;
+    if (trace) trace[3] = timer_ns();
 
     // Merge the four consumers (each saw its own tiles).  Only the group's rows are kept.
     consumer_barrier();        // the merge buffers of the previous item are no longer read
@@ -509,32 +551,118 @@ paged_decode_kernel(const DecodeArgs a) {
     }
     if (alone) continue;
 
-    // Whoever arrives last finds every split's partial result written and merges them.
-    __threadfence();
+    // Whoever arrives last finds every split's partial result written and merges them.  The barrier
+    // orders the consumers' writes before the arrival, whose release makes them visible to whoever
+    // reads the count with acquire; the barrier after it passes that on to the other consumers.
     consumer_barrier();
     if (ctid == 0) {
-      const int arrived = atomicAdd(&a.counters[it.r * a.nkv + it.kvh], 1);
+      int arrived;
+      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                   : "=r"(arrived) : "l"(&a.counters[it.r * a.nkv + it.kvh]) : "memory");
       is_last = arrived == it.n_parts - 1;
     }
     consumer_barrier();
+    if (trace) trace[7] = timer_ns();
     if (!is_last) continue;
-    __threadfence();
+    // All loads of a round are issued before the first is used: a merge costs a few round trips to
+    // the L2, not one per split.
+    constexpr int ROUND = 4, WIDE = 16;
+    float* ml_s = merge_o;                 // [n_parts][g][2], where the consumers' parts lay (they are merged by now)
+    const bool staged = it.n_parts > ROUND && it.n_parts * 2 + 1 <= DEC_CONSUMERS * HD;
+    // This thread's first two output elements' shares of the first WIDE splits, asked for before
+    // the maxima are staged so that both travel at the same time.
+    constexpr int AHEAD = 2;
+    float first_o[AHEAD][WIDE];
+    if (staged) {
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const int e = ctid + u * DEC_CONSUMERS * 32;
+        if (e >= g * HD) break;
+        const int h = e / HD, d = e - h * HD;
+#pragma unroll
+        for (int k = 0; k < WIDE; ++k)
+          first_o[u][k] = k < it.n_parts
+                              ? __ldcg(&a.part_o[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * HD + d]) : 0.0f;
+      }
+      for (int e = ctid; e < it.n_parts * g * 2; e += DEC_CONSUMERS * 32) {
+        const int k = e / (g * 2), rest = e - k * g * 2;
+        ml_s[e] = __ldcg(&a.part_ml[static_cast<size_t>(part_slot(a, it, k, per_range)) * g * 2 + rest]);
+      }
+      consumer_barrier();
+      // One warp per head turns the maxima into the splits' weights, exp2(m_k - max), in place, and
+      // leaves the head's weighted sum of the l_k behind the list: the elements below then cost a
+      // multiply-add per split (with one warp per scheduler every instruction's latency shows).
+      for (int h = warp; h < g; h += DEC_CONSUMERS) {
+        float mx = -INFINITY;
+        for (int k = lane; k < it.n_parts; k += 32) mx = fmaxf(mx, ml_s[(k * g + h) * 2]);
+        mx = warp_max(mx);
+        float lsum = 0.0f;
+        for (int k = lane; k < it.n_parts; k += 32) {
+          const float f = exp2f(ml_s[(k * g + h) * 2] - mx);
+          lsum += ml_s[(k * g + h) * 2 + 1] * f;
+          ml_s[(k * g + h) * 2] = f;
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) ml_s[it.n_parts * g * 2 + h] = lsum;
+      }
+      consumer_barrier();
+    }
     for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
       const int h = e / HD, d = e - h * HD;
-      float mx = -INFINITY;
-      for (int k = 0; k < it.n_parts; ++k)
-        mx = fmaxf(mx, __ldcg(&a.part_ml[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * 2]));
       float acc = 0.0f, l = 0.0f;
-      for (int k = 0; k < it.n_parts; ++k) {             // in the order of the context: a fixed order
-        const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
-        const float f = exp2f(__ldcg(&a.part_ml[slot * 2]) - mx);
-        acc += __ldcg(&a.part_o[slot * HD + d]) * f;
-        l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
+      if (it.n_parts <= ROUND) {
+        float pm[ROUND], pl[ROUND], po[ROUND];
+#pragma unroll
+        for (int k = 0; k < ROUND; ++k) {
+          pm[k] = -INFINITY; pl[k] = 0.0f; po[k] = 0.0f;
+          if (k < it.n_parts) {
+            const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
+            pm[k] = __ldcg(&a.part_ml[slot * 2]);
+            pl[k] = __ldcg(&a.part_ml[slot * 2 + 1]);
+            po[k] = __ldcg(&a.part_o[slot * HD + d]);
+          }
+        }
+        float mx = pm[0];
+#pragma unroll
+        for (int k = 1; k < ROUND; ++k) mx = fmaxf(mx, pm[k]);
+#pragma unroll
+        for (int k = 0; k < ROUND; ++k) {                  // in the order of the context: a fixed order
+          const float f = k < it.n_parts ? exp2f(pm[k] - mx) : 0.0f;
+          acc += po[k] * f;
+          l += pl[k] * f;
+        }
+      } else if (staged) {
+        for (int k0 = 0; k0 < it.n_parts; k0 += WIDE) {
+          float po[WIDE];
+#pragma unroll
+          for (int k = 0; k < WIDE; ++k) {
+            if (k0 == 0 && e == ctid) po[k] = first_o[0][k];
+            else if (k0 == 0 && e == ctid + DEC_CONSUMERS * 32) po[k] = first_o[1][k];
+            else
+              po[k] = k0 + k < it.n_parts
+                          ? __ldcg(&a.part_o[(static_cast<size_t>(part_slot(a, it, k0 + k, per_range)) * g + h) * HD + d]) : 0.0f;
+          }
+#pragma unroll
+          for (int k = 0; k < WIDE; ++k)                     // in the order of the context: a fixed order
+            if (k0 + k < it.n_parts) acc += po[k] * ml_s[((k0 + k) * g + h) * 2];
+        }
+        l = ml_s[it.n_parts * g * 2 + h];
+      } else {
+        float mx = -INFINITY;
+        for (int k = 0; k < it.n_parts; ++k)
+          mx = fmaxf(mx, __ldcg(&a.part_ml[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * 2]));
+        for (int k = 0; k < it.n_parts; ++k) {
+          const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
+          const float f = exp2f(__ldcg(&a.part_ml[slot * 2]) - mx);
+          acc += __ldcg(&a.part_o[slot * HD + d]) * f;
+          l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
+        }
       }
       a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
     }
     if (ctid == 0) a.counters[it.r * a.nkv + it.kvh] = 0;    // left as it was found, for the next call
   }
+  if (trace) { trace[4] = timer_ns(); trace[5] = item_seq; trace[6] = tile_base; }
   if (abort_flag) {
     // Something went wrong.  Give copies that are still in flight a bounded chance to land before
     // this CTA's shared memory is handed to another.
@@ -585,6 +713,20 @@ int decode_launch(DecodeArgs& a, cudaStream_t stream) {
 using namespace zb;
 
 // 1 if zb_paged_decode takes this shape, else 0 (the caller then uses the general kernel).
+namespace zb {
+inline int*& decode_trace() {
+  static int* buffer = nullptr;
+  return buffer;
+}
+}  // namespace zb
+
+// Timelines for later launches of zb_paged_decode: `buffer` is null (off) or 8 ints per CTA on the
+// device for up to 1024 CTAs (see DecodeArgs::trace).
+ZB_API int zb_paged_decode_set_trace(int* buffer) {
+  decode_trace() = buffer;
+  return OK;
+}
+
 ZB_API int zb_paged_decode_supported(int nh, int nkv, int hd, int dtype) {
   if (dtype != DTYPE_BF16 || nkv <= 0 || nh % nkv != 0 || nh / nkv > DEC_MAX_GROUP) return 0;
   return hd == 32 || hd == 64 || hd == 96 || hd == 128 ? 1 : 0;
@@ -632,6 +774,7 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
   a.max_blocks = max_blocks; a.page_shift = page_shift; a.num_pages = num_pages; a.num_rows = num_rows;
   a.n_rows = n_rows;
   a.nh = nh; a.nkv = nkv; a.window = window; a.split_size = split_size; a.max_splits = max_splits;
+  a.trace = decode_trace();
   a.ring_slots = 0;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;

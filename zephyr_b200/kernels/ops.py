@@ -67,6 +67,7 @@ _SIGNATURES = {
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p],
+    "zb_paged_decode_set_trace": [c_void_p],
     "zb_paged_prefill_tile_tokens": [],
     "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -471,6 +472,16 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
 
 
 USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel for every head size (for comparisons)
+
+
+def paged_decode_trace(buffer: torch.Tensor | None) -> None:
+    """Later ``paged_decode`` launches write every CTA's timeline into ``buffer`` (int32 [1024, 8] on the
+    device: the global timer in ns at the CTA's start, after the wait for earlier kernels, when its
+    first tile had landed, after its last tile, at its end; then its items and tiles); None turns it off."""
+    if buffer is not None:
+        _cuda(buffer)
+        _require(buffer.dtype == torch.int32 and buffer.is_contiguous() and buffer.numel() >= 8 * 1024, "int32 [1024, 8]")
+    _check(library().zb_paged_decode_set_trace(_ptr(buffer)), "paged_decode_trace", kernels=0)
 
 
 def paged_prefill_tile_tokens() -> int:

@@ -86,12 +86,36 @@ def decode_attention(args) -> dict:
         ops.paged_decode(q, caches[i % len(caches)], table, rows, rows, row_ctx, ctx, nh, nkv, hd, args.window,
                          1 / math.sqrt(hd), status, out=out, split_size=split)
     us = _time(run, args.warmup, args.iters)
+    trace = torch.zeros((1024, 8), dtype=torch.int32, device=device)
+    ops.paged_decode_trace(trace)
+    for i in range(3):          # the last launch's timeline stays
+        run(i)
+    ops.paged_decode_trace(None)
     ops.check_status(status, "decode_attention")
     live = min(ctx, args.window) if args.window else ctx
     read = B * live * nkv * hd * 2 * 2
     return {"kernel": "paged_decode_kernel", "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "page_size": args.page_size, "window": args.window, "split_size": split or "balanced", "us": round(us, 2),
-            "bytes_read": read, "gbs": round(read / us / 1e3, 1)}
+            "bytes_read": read, "gbs": round(read / us / 1e3, 1), "timeline_ns": _decode_timeline(trace)}
+
+
+def _decode_timeline(trace: torch.Tensor) -> dict:
+    """The last launch over all its CTAs: when the first and the last CTA reached each mark,
+    nanoseconds from the earliest start; and the fewest and most items and tiles of a CTA."""
+    t = trace.cpu().to(torch.int64)
+    t = t[t[:, 4] != 0]
+    if t.shape[0] == 0:
+        return {}
+    marks = ("start", "earlier_kernels_done", "first_tile_landed", "last_tile_done", "end")
+    rel = (t[:, :5] - t[:, 0].min()) & 0xFFFFFFFF
+    out = {m: [int(rel[:, i].min()), int(rel[:, i].max())] for i, m in enumerate(marks)}
+    counted = t[t[:, 7] != 0]
+    if counted.shape[0]:
+        arrival = (counted[:, 7] - t[:, 0].min()) & 0xFFFFFFFF
+        out["last_arrival_counted"] = [int(arrival.min()), int(arrival.max())]
+    out.update(ctas=int(t.shape[0]), items=[int(t[:, 5].min()), int(t[:, 5].max())],
+               tiles=[int(t[:, 6].min()), int(t[:, 6].max())])
+    return out
 
 
 def prefill_attention(args) -> dict:
