@@ -195,6 +195,66 @@ def test_small_pool_preempts_and_tokens_do_not_change(model_folders, cuda_device
     assert tight.runner.manager.num_free_pages() == 16
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_planning_a_step_ahead_changes_nothing(model_folders, cuda_device, dtype):
+    """While the device runs a step of decoders the engine plans the next one.  Sequences that end on a
+    stop token in the middle, requests that arrive while others decode, a cancelled request and a
+    pool so small that it preempts: the tokens are those of an engine that plans nothing ahead, and
+    plans made ahead were both used and dropped."""
+    folder = model_folders("B", dtype)
+    vocab = TINY["B"]["config"]["vocab_size"]
+    prompts = [random_tokens(vocab, n, seed=70 + n) for n in (9, 17, 5, 12, 7)]
+
+    def run(look_ahead: bool, num_blocks: int):
+        engine = make_engine(folder, "B", dtype, max_num_seqs=4, max_num_batched_tokens=32, max_prefill_chunk_tokens=32,
+                             num_blocks=num_blocks)
+        engine.look_ahead = look_ahead
+        used = dropped = 0
+        take = engine._take_ahead
+
+        def counting():
+            nonlocal used, dropped
+            had = engine._ahead
+            plan, prepared = take()
+            if had is not None:
+                used += plan is had[0]
+                dropped += plan is not had[0]
+            return plan, prepared
+        engine._take_ahead = counting
+        from zephyr_b200 import GenerationParams
+        free = list(engine.generate(prompts[0], max_tokens=24, temperature=0.0, ignore_eos=True).token_ids)
+        params = [GenerationParams(max_tokens=24, temperature=0.0, ignore_eos=True, stop_token_ids=(free[7],)),
+                  GenerationParams(max_tokens=30, temperature=0.9, seed=5, ignore_eos=True),
+                  GenerationParams(max_tokens=11, temperature=0.0, ignore_eos=True),
+                  GenerationParams(max_tokens=40, temperature=0.0, ignore_eos=True),
+                  GenerationParams(max_tokens=9, temperature=0.7, seed=2, top_k=5, ignore_eos=True)]
+        ids = [engine.add_request(prompts[i], params[i]) for i in range(3)]
+        steps = 0
+        while engine.has_unfinished():
+            engine.step()
+            steps += 1
+            if steps == 6:
+                ids.append(engine.add_request(prompts[3], params[3]))      # arrives while the others decode
+            if steps == 14:
+                ids.append(engine.add_request(prompts[4], params[4]))
+            if steps == 20:
+                engine.cancel(ids[3])
+            engine.runner.manager.check_invariants()
+        outputs = [engine.take_output(i) for i in ids]
+        return [list(o.token_ids) for o in outputs], used, dropped, engine.stats.preemptions
+
+    expected, used, dropped, _ = run(False, 64)
+    assert used == 0 and dropped == 0
+    got, used, dropped, _ = run(True, 64)
+    assert got[:3] == expected[:3] and got[4] == expected[4]
+    assert got[3] == expected[3]                     # cancelled at the same step in both
+    assert used >= 10 and dropped >= 2, (used, dropped)
+    tight_expected, _, _, preempted_without = run(False, 10)
+    tight, used, dropped, preempted = run(True, 10)
+    assert preempted > 0 and preempted_without > 0
+    assert tight[:3] == tight_expected[:3] == expected[:3] and tight[4] == expected[4]
+
+
 def test_finish_rules_and_choices(model_folders, cuda_device):
     folder = model_folders("A", "float32")
     engine = make_engine(folder, "A", "float32", max_num_seqs=4, max_num_batched_tokens=32, max_prefill_chunk_tokens=32)

@@ -125,6 +125,11 @@ class Engine:
         self._next_request_id = 0
         self.stats = EngineStats()
         self._closed = False
+        # While the device runs a step of decoders only, the host plans and describes the next one
+        # (all but its tokens): ``look_ahead`` turns that off.
+        self.look_ahead = True
+        self._ahead = None                      # (plan, entries, prepared) of the step after this one
+        self._placeholders: set[tuple[int, int]] = set()   # sequences whose last token is still on the device
 
     # ------------------------------------------------------------------- set-up
     @staticmethod
@@ -227,7 +232,9 @@ class Engine:
     def step(self) -> int:
         """Schedule and run one step; returns the number of tokens it computed (0: nothing to do)."""
         started = time.perf_counter()
-        plan = self.scheduler.schedule()
+        plan, prepared = self._take_ahead()
+        if plan is None:
+            plan = self.scheduler.schedule()
         for key in plan.rejected:
             request = self._requests[key[0]]
             request.error_message = self.sequences[key].error_message
@@ -236,12 +243,7 @@ class Engine:
             if self.scheduler.has_unfinished and not plan.preempted and not plan.rejected:
                 raise RuntimeError("the scheduler made no progress although sequences are unfinished")
             return 0
-        entries = []
-        for item in plan.sequences:
-            sequence = self.sequences[item.sequence_id]
-            tokens = sequence.token_ids[item.start_token:item.start_token + item.num_tokens]
-            entries.append(StepEntry(item.sequence_id, tokens, (item.num_tokens - 1,) if item.sample else ()))
-        logits = self.runner.step(entries)
+        logits = self.runner.step(self._entries(plan), prepared)
         self.scheduler.commit(plan)
         sampled = [item for item in plan.sequences if item.sample]
         self.stats.prefill_tokens += sum(i.num_tokens for i in plan.sequences if i.num_tokens > 1 or not i.sample)
@@ -249,23 +251,90 @@ class Engine:
             params = [self._requests[i.sequence_id[0]].sampling for i in sampled]
             generators = [self._generators[i.sequence_id] for i in sampled]
             sequences = [self.sequences[i.sequence_id] for i in sampled]
-            results = self.sampler.sample(logits, params, generators, [s.token_ids for s in sequences],
-                                          [s.prompt_length for s in sequences])    # also reads the step's status
+            pending = self.sampler.launch(logits, params, generators, [s.token_ids for s in sequences],
+                                          [s.prompt_length for s in sequences])
+            ahead = self._plan_ahead(plan)      # host work while the device runs the step
+            results = self.sampler.finish(pending)        # also reads the step's status
             for item, result in zip(sampled, results):
                 if result.logprobs is not None:
                     self._logprobs.setdefault(item.sequence_id, []).append(result.logprobs)
                 self._append_token(item.sequence_id, int(result.token_id))
+            self._ahead = ahead
             self.stats.generated_tokens += len(results)
         self.stats.steps += 1
         self.stats.preemptions = self.scheduler.num_preemptions
         self.stats.step_seconds += time.perf_counter() - started
         return plan.num_tokens
 
+    def _entries(self, plan) -> list[StepEntry]:
+        entries = []
+        for item in plan.sequences:
+            sequence = self.sequences[item.sequence_id]
+            tokens = sequence.token_ids[item.start_token:item.start_token + item.num_tokens]
+            entries.append(StepEntry(item.sequence_id, tokens, (item.num_tokens - 1,) if item.sample else ()))
+        return entries
+
+    # ------------------------------------------------------------ one step ahead
+    def _plan_ahead(self, plan):
+        """Called between the launch of a step's selection and the wait for its tokens.  If the step
+        after this one is known but for its tokens (every resident sequence is decoding and got its
+        token in this step, nothing waits for admission, no sequence reaches a length limit with the
+        token on its way), schedule it now and let the runner describe it: when the tokens arrive only
+        they are missing.  A sequence that then ends on its token (end of sequence, a stop token) or
+        anything else that changes the picture makes ``_take_ahead`` drop the plan; the scheduler is
+        asked again and decides on what it finds, as it always does."""
+        scheduler = self.scheduler
+        if (not self.look_ahead or scheduler.waiting or len(plan.sequences) != len(scheduler.running)
+                or len(plan.sequences) > self.scheduler_config.max_num_batched_tokens
+                or not all(item.sample for item in plan.sequences)):
+            return None
+        for item in plan.sequences:
+            sequence = self.sequences[item.sequence_id]
+            request = self._requests[item.sequence_id[0]]
+            if (sequence.state != SequenceState.DECODE or item.sequence_id not in scheduler.running
+                    or len(sequence.token_ids) - sequence.prompt_length + 1 >= request.max_new_tokens
+                    or len(sequence.token_ids) >= self.max_seq_len - 1):
+                return None
+        for item in plan.sequences:
+            self.sequences[item.sequence_id].token_ids.append(-1)      # stands for the token on its way
+            self._placeholders.add(item.sequence_id)
+        ahead = scheduler.schedule()
+        if ahead.preempted or ahead.rejected or not ahead.sequences:
+            return (ahead, None)
+        return (ahead, self.runner.prepare(self._entries(ahead)))
+
+    def _take_ahead(self):
+        """(plan, prepared) for this step from the plan made one step ahead, or (None, None).  The
+        plan is used as it is if it is still what the scheduler would choose: every sequence in it
+        decodes on, and nobody waits for admission but those the plan itself preempted.  Otherwise
+        the scheduler is asked again; what the dropped plan preempted or rejected has happened and
+        is reported with the new plan."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is None:
+            return None, None
+        plan, prepared = ahead
+        scheduler = self.scheduler
+        clean = set(scheduler.waiting) <= set(plan.preempted)
+        for item in plan.sequences:
+            sequence = self.sequences.get(item.sequence_id)
+            if (sequence is None or sequence.state != SequenceState.DECODE or item.sequence_id not in scheduler.running
+                    or item.start_token + item.num_tokens != len(sequence.token_ids)):
+                clean = False
+        if clean:
+            return plan, prepared
+        fresh = scheduler.schedule()
+        fresh.preempted[:0] = plan.preempted
+        fresh.rejected[:0] = plan.rejected
+        return fresh, None
+
     def _append_token(self, key: tuple[int, int], token: int) -> None:
         """The finish rules in the reference's order (src/engine/generation.cpp:81-99).  The sampled
         token enters the history now; its cache entry is made by the next step."""
         sequence = self.sequences[key]
         request = self._requests[key[0]]
+        if key in self._placeholders:          # the plan made ahead already counts this token
+            self._placeholders.discard(key)
+            sequence.token_ids.pop()
         reason = None
         if not request.params.ignore_eos and token in self.eos_token_ids:
             reason = FinishReason.EOS

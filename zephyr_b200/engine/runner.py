@@ -34,6 +34,16 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)
 
 
+@dataclass
+class PreparedStep:
+    """A decode-only step whose description is already written, all but its tokens (``ModelRunner.prepare``)."""
+
+    key: tuple
+    turn: int
+    info: dict
+    request_ids: tuple
+
+
 class ModelRunner:
     def __init__(self, model: Model, page_size: int, num_pages: int, max_requests: int,
                  max_seq_len: int | None = None, use_cuda_graphs: bool = True):
@@ -79,7 +89,7 @@ class ModelRunner:
         return self.manager.computed(request_id)
 
     # -------------------------------------------------------------------- step
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], tokens_known: bool = True) -> None:
         if not entries:
             raise InvalidArgumentError("a step needs at least one entry")
         seen = set()
@@ -96,7 +106,7 @@ class ModelRunner:
             if self.manager.computed(entry.request_id) + n > self.max_seq_len:
                 raise InvalidArgumentError(
                     f"request {entry.request_id!r} would exceed the maximum sequence length {self.max_seq_len}")
-            for token in entry.tokens:
+            for token in entry.tokens if tokens_known else ():
                 if not 0 <= int(token) < vocab:
                     raise InvalidArgumentError(f"token id {token} lies outside the vocabulary of {vocab}")
             for place in entry.want:
@@ -271,11 +281,8 @@ class ModelRunner:
             for buffer in record["host"]:
                 buffer.numpy()[:] = template
             self._graphs[key] = record
-        sizes, offsets, total = record["sizes"], record["offsets"], record["offsets"][-1]
-        turn = record["turn"]
-        record["turn"] = (turn + 1) % len(record["host"])
-        if record["copied"][turn] is not None:
-            record["copied"][turn].synchronize()
+        sizes = record["sizes"]
+        turn = self._claim_buffer(record)
         if decode_only:
             info = self._rewrite_decode(record, record["host"][turn].numpy(), entries, width)
         else:
@@ -283,6 +290,20 @@ class ModelRunner:
             if [a.size for a in arrays] != sizes:
                 raise RuntimeError("a step's description changed size under one graph key")
             np.concatenate(arrays, out=record["host"][turn].numpy())
+        return self._launch_graph(record, turn, info, decode_only)
+
+    @staticmethod
+    def _claim_buffer(record: dict) -> int:
+        """The next pinned buffer of the record's ring, once the copy that last read it is done."""
+        turn = record["turn"]
+        record["turn"] = (turn + 1) % len(record["host"])
+        if record["copied"][turn] is not None:
+            record["copied"][turn].synchronize()
+        return turn
+
+    def _launch_graph(self, record: dict, turn: int, info: dict, decode_only: bool) -> tuple[torch.Tensor, dict]:
+        """Copy the written description to the device and run the record's graph (captured at its first run)."""
+        sizes, total = record["sizes"], record["offsets"][-1]
         record["device"].copy_(record["host"][turn], non_blocking=True)
         event = record["copied"][turn] or torch.cuda.Event()
         event.record()
@@ -309,22 +330,67 @@ class ModelRunner:
         # steps of other shapes hand out a copy, which the next step of that shape leaves alone.
         return (record["logits"] if decode_only else record["logits"].clone()), info
 
+    def prepare(self, entries: Sequence[StepEntry]) -> PreparedStep | None:
+        """Write a decode-only step's description before its tokens are known (each entry's token is
+        a placeholder): positions, contexts, slots and block tables go into the graph's next pinned
+        buffer, pages are made sure of.  The host does this while the device still runs the step
+        before; ``step(entries, prepared)`` then only adds the tokens.  None if the step is not one
+        that replays an existing decode graph, or if pages are missing (``step`` will say so)."""
+        if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
+            return None
+        self._validate(entries, tokens_known=False)
+        key = self._graph_key(entries)
+        record = self._graphs.get(key) if key is not None else None
+        if record is None or record["graph"] is None:
+            return None
+        turn = self._claim_buffer(record)
+        try:
+            info = self._rewrite_decode(record, record["host"][turn].numpy(), entries,
+                                        self.manager.blocks_for(self.max_seq_len))
+        except OutOfPagesError:
+            return None
+        return PreparedStep(key, turn, info, tuple(e.request_id for e in entries))
+
+    def _still_holds(self, prepared: PreparedStep, entries: Sequence[StepEntry]) -> bool:
+        """True if ``prepared`` was made for these entries and nothing has moved since."""
+        if len(entries) != len(prepared.request_ids) or prepared.key not in self._graphs:
+            return False
+        manager = self.manager
+        for entry, request_id, before in zip(entries, prepared.request_ids, prepared.info["ctx_before"]):
+            if (entry.request_id != request_id or len(entry.tokens) != 1 or tuple(entry.want) != (0,)
+                    or request_id not in manager or manager.computed(request_id) != before):
+                return False
+        return True
+
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], prepared: PreparedStep | None = None) -> torch.Tensor:
         """Run the entries as one batch.  Returns float32 logits [sum of wanted places, vocab] on the
         device, in the order of the entries and of each entry's ``want``.  The call does not wait for
         the GPU; ``check()`` (or reading the logits on the host and then ``check()``) does.  The tensor
         returned by a decode-only step belongs to that step's graph and is overwritten by the next
-        step of the same shape: use it (sample from it, copy it) before stepping again."""
-        self._validate(entries)
-        key = self._graph_key(entries)
-        if key is not None:
-            logits, info = self._step_with_graph(key, entries)
+        step of the same shape: use it (sample from it, copy it) before stepping again.
+        ``prepared``: what ``prepare`` returned for these very entries, nothing else having touched the
+        runner in between; anything else is ignored and the step is described afresh."""
+        if prepared is not None and self._still_holds(prepared, entries):
+            # Everything but the tokens was checked and written by ``prepare``.
+            tokens = [int(e.tokens[0]) for e in entries]
+            if not 0 <= min(tokens) <= max(tokens) < self.model.spec.vocab_size:
+                raise InvalidArgumentError(f"a token id among {tokens} lies outside the vocabulary")
+            record = self._graphs[prepared.key]
+            at = record["offsets"][0]
+            record["host"][prepared.turn].numpy()[at:at + len(entries)] = tokens
+            logits, info = self._launch_graph(record, prepared.turn, prepared.info, True)
             before_all = info["ctx_before"]
         else:
-            ctx = self.build_context(entries)
-            logits = self.model.forward(ctx)
-            before_all = ctx.host_ctx
+            self._validate(entries)
+            key = self._graph_key(entries)
+            if key is not None:
+                logits, info = self._step_with_graph(key, entries)
+                before_all = info["ctx_before"]
+            else:
+                ctx = self.build_context(entries)
+                logits = self.model.forward(ctx)
+                before_all = ctx.host_ctx
         for entry, before in zip(entries, before_all):
             if self.poison_freed_pages:
                 old = [list(self.manager.block_table(entry.request_id, g)) for g in range(len(self.manager.groups))]

@@ -147,27 +147,60 @@ class Sampler:
             raise InvalidArgumentError("sample_async returns ids only; use sample() for rows that report")
         return self._launch(logits, params, generators, histories, prompt_lengths).ids
 
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None = None,
+               prompt_lengths: Sequence[int] | None = None) -> "PendingSample":
+        """Launch the selection and the copy of its results to the host; ``finish`` waits for them.
+        Between the two the host is free while the device works."""
+        for p in params:
+            p.validate(logits.shape[1])
+        out = self._launch(logits, params, generators, histories, prompt_lengths)
+        # One read brings the ids and the status word: every wait for the device costs the step time.
+        combined = torch.cat([out.ids, self.status])
+        host_ids = torch.empty(combined.shape, dtype=combined.dtype, pin_memory=True)
+        host_ids.copy_(combined, non_blocking=True)
+        host_values = None
+        if out.logprobs is not None:
+            host_values = torch.empty(out.logprobs.shape, dtype=out.logprobs.dtype, pin_memory=True)
+            host_values.copy_(out.logprobs, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return PendingSample(list(params), out.offsets, logits.shape[1], host_ids, host_values, done)
+
+    def finish(self, pending: "PendingSample") -> list[SamplingResult]:
+        """Wait for a launched selection; one ``SamplingResult`` per row."""
+        pending.done.synchronize()
+        ids = pending.host_ids.tolist()
+        if ids[-4] != 0:
+            ops.check_status(self.status, "step")
+        del ids[-4:]
+        values = pending.host_values.tolist() if pending.host_values is not None else None
+        results = []
+        for p, at in zip(pending.params, pending.offsets):
+            report = None
+            if p.top_logprobs is not None:
+                n = min(int(p.top_logprobs), pending.vocab)
+                report = SamplingLogprobs(values[at], tuple(TokenLogprob(ids[at + 1 + k], values[at + 1 + k])
+                                                             for k in range(n)))
+            results.append(SamplingResult(ids[at], report))
+        return results
+
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None = None,
                prompt_lengths: Sequence[int] | None = None) -> list[SamplingResult]:
         """One ``SamplingResult`` per row.  ``histories`` (prompt and generated tokens) and
         ``prompt_lengths`` are needed for rows with penalties.  Penalties and biases change
         ``logits`` in place."""
-        for p in params:
-            p.validate(logits.shape[1])
-        out = self._launch(logits, params, generators, histories, prompt_lengths)
-        # One read brings the ids and the status word: every wait for the device costs the step time.
-        ids = torch.cat([out.ids, self.status]).tolist()
-        if ids[-4] != 0:
-            ops.check_status(self.status, "step")
-        del ids[-4:]
-        values = out.logprobs.tolist() if out.logprobs is not None else None
-        results = []
-        for p, at in zip(params, out.offsets):
-            report = None
-            if p.top_logprobs is not None:
-                n = min(int(p.top_logprobs), logits.shape[1])
-                report = SamplingLogprobs(values[at], tuple(TokenLogprob(ids[at + 1 + k], values[at + 1 + k])
-                                                             for k in range(n)))
-            results.append(SamplingResult(ids[at], report))
-        return results
+        return self.finish(self.launch(logits, params, generators, histories, prompt_lengths))
+
+
+@dataclass
+class PendingSample:
+    """A selection that has been launched: its results are on their way to the host."""
+
+    params: list
+    offsets: list
+    vocab: int
+    host_ids: torch.Tensor
+    host_values: torch.Tensor | None
+    done: "torch.cuda.Event"
