@@ -113,3 +113,17 @@ def test_attention_mixer_and_block(model_folders, cuda_device, name, dtype):
     after = stream.flush()
     expected = plain_decoder_layer(x64, weights, config, layer, cos, sin)
     assert (after.double().cpu() - expected).abs().max() <= tol(dtype) * max(1.0, float(expected.abs().max())) * 2
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_weight_bytes_of_a_step(model_folders, cuda_device, name):
+    """What the roofline divides by: every matrix and scale a step reads, once (a fused q/k/v matrix
+    and the view of its query rows are one piece of memory; a tied head is the embedding table)."""
+    model, _, _, _ = load(model_folders, name, "bfloat16", cuda_device)
+    c = TINY[name]["config"]
+    h, i, v, layers = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["num_hidden_layers"]
+    hd = c.get("head_dim") or h // c["num_attention_heads"]
+    q, kv = c["num_attention_heads"] * hd, c["num_key_value_heads"] * hd
+    matrices = 2 * (layers * ((q + 2 * kv) * h + h * q + 3 * i * h) + v * h)      # the head, or the table that serves as it
+    scales = layers * (2 * h + 2 * hd) + h                                        # two or four bytes each, as stored
+    assert matrices + 2 * scales <= model.weight_bytes_read_per_step() <= matrices + 4 * scales

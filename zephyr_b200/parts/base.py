@@ -75,9 +75,9 @@ class Part:
         return {}
 
     def weights_read(self) -> list[torch.Tensor]:
-        """The weight tensors one forward pass reads (views of another listed tensor left out)."""
-        return [value for value in vars(self).values()
-                if isinstance(value, torch.Tensor) and value.is_floating_point() and not value._is_view()]
+        """The weight tensors one forward pass reads.  Some may share memory (the query rows of a fused
+        q/k/v matrix); whoever adds up bytes counts a piece of memory once."""
+        return [value for value in vars(self).values() if isinstance(value, torch.Tensor) and value.is_floating_point()]
 
 
 class Norm(Part):

@@ -111,14 +111,13 @@ class Model:
     def weight_bytes_read_per_step(self) -> int:
         """Bytes of weights one step reads when every matrix is used once (the embedding table is
         only gathered from, unless it also serves as the head)."""
-        seen: set[int] = set()
-        total = 0
+        by_storage: dict[int, dict[tuple[int, int], int]] = {}     # storage -> {(address, bytes) of a tensor}
+        sizes: dict[int, int] = {}
 
         def add(t: torch.Tensor) -> None:
-            nonlocal total
-            if t.data_ptr() not in seen:
-                seen.add(t.data_ptr())
-                total += t.numel() * t.element_size()
+            storage = t.untyped_storage()
+            sizes[storage.data_ptr()] = storage.nbytes()
+            by_storage.setdefault(storage.data_ptr(), {})[(t.data_ptr(), t.numel() * t.element_size())] = 1
 
         add(self.lm_head)
         for tensor in self.final_norm.weights_read():
@@ -128,7 +127,9 @@ class Model:
             for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
                 for tensor in part.weights_read():
                     add(tensor)
-        return total
+        # Tensors that share a storage overlap (a matrix and a view of its first rows): such a storage
+        # counts once, and never for more than it holds.
+        return sum(min(sizes[storage], sum(size for _, size in tensors)) for storage, tensors in by_storage.items())
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
