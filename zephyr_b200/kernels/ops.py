@@ -73,6 +73,7 @@ _SIGNATURES = {
     "zb_paged_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_paged_prefill_tc_supported": [c_int, c_int, c_int, c_int, c_int],
+    "zb_paged_prefill_tc_set_trace": [c_void_p],
     "zb_paged_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_gemm_small_supported": [c_int, c_int, c_int],
@@ -482,6 +483,18 @@ def paged_decode_trace(buffer: torch.Tensor | None) -> None:
         _cuda(buffer)
         _require(buffer.dtype == torch.int32 and buffer.is_contiguous() and buffer.numel() >= 8 * 1024, "int32 [1024, 8]")
     _check(library().zb_paged_decode_set_trace(_ptr(buffer)), "paged_decode_trace", kernels=0)
+
+
+def paged_prefill_trace(buffer: torch.Tensor | None) -> None:
+    """Later tcgen05 prompt-attention launches write the timeline of their first CTA (the longest
+    work of the launch) into ``buffer`` (int32 [2, 64, 4] on the device; per tile of keys, [0]: the
+    global timer in ns when S was issued, when its softmax began, when its probabilities were written,
+    when O += P V was issued; [1]: when the first loader thread began to issue its keys, its values,
+    and when it had issued them); None turns it off."""
+    if buffer is not None:
+        _cuda(buffer)
+        _require(buffer.dtype == torch.int32 and buffer.is_contiguous() and buffer.numel() >= 512, "int32 [2, 64, 4]")
+    _check(library().zb_paged_prefill_tc_set_trace(_ptr(buffer)), "paged_prefill_trace", kernels=0)
 
 
 def paged_prefill_tile_tokens() -> int:

@@ -135,13 +135,31 @@ def prefill_attention(args) -> dict:
         ops.paged_prefill(q, caches[i % len(caches)], table, tile_row, tile_q0, zero, q_len, zero, nh, nkv, hd,
                           args.window, 1 / math.sqrt(hd), status, out=out)
     us = _time(run, args.warmup, args.iters)
+    trace = torch.zeros((2, 64, 4), dtype=torch.int32, device=device)
+    ops.paged_prefill_trace(trace)
+    for i in range(2):
+        run(i)
+    ops.paged_prefill_trace(None)
     ops.check_status(status, "prefill_attention")
     # Two products of 2 * hd flops per (query, visible key) pair and head.
     pairs = sum(min(t + 1, args.window) if args.window else t + 1 for t in range(T))
     flops = 4 * hd * pairs * nh
     return {"kernel": "paged_prefill_kernel", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "page_size": args.page_size, "window": args.window, "us": round(us, 2), "flops": flops,
-            "tflops": round(flops / us / 1e6, 1)}
+            "tflops": round(flops / us / 1e6, 1), "longest_cta_ns": _prefill_timeline(trace)}
+
+
+def _prefill_timeline(trace: torch.Tensor) -> list:
+    """The launch's longest CTA, tile by tile: [S issued, softmax began, probabilities written,
+    O += P V issued, keys asked for, values asked for], ns from the first mark.  Empty if the kernel
+    that ran keeps no timeline."""
+    t = trace.cpu().to(torch.int64)
+    n = int((t[0, :, 3] != 0).sum())
+    if n == 0:
+        return []
+    base = min(int(t[0, 0, 0]), int(t[1, 0, 0]))
+    both = torch.cat([t[0, :n], t[1, :n, :2]], dim=1)
+    return ((both - base) & 0xFFFFFFFF).tolist()
 
 
 def gemm_small(args) -> dict:
