@@ -200,17 +200,30 @@ def test_planning_a_step_ahead_changes_nothing(model_folders, cuda_device, dtype
     """While the device runs a step of decoders the engine plans the next one.  Sequences that end on a
     stop token in the middle, requests that arrive while others decode, a cancelled request and a
     pool so small that it preempts: the tokens are those of an engine that plans nothing ahead, and
-    plans made ahead were both used and dropped."""
+    plans made ahead (and steps launched ahead, with their tokens still on the device) were both used
+    and dropped."""
     folder = model_folders("B", dtype)
     vocab = TINY["B"]["config"]["vocab_size"]
     prompts = [random_tokens(vocab, n, seed=70 + n) for n in (9, 17, 5, 12, 7)]
 
-    def run(look_ahead: bool, num_blocks: int):
+    def run(look_ahead: bool, num_blocks: int, launch_ahead: bool = False):
         engine = make_engine(folder, "B", dtype, max_num_seqs=4, max_num_batched_tokens=32, max_prefill_chunk_tokens=32,
                              num_blocks=num_blocks)
         engine.look_ahead = look_ahead
+        engine.launch_ahead = launch_ahead
         used = dropped = 0
-        take = engine._take_ahead
+        take, settle = engine._take_ahead, engine._settle_flight
+
+        def counting_flights():
+            nonlocal used, dropped
+            had = engine._flight
+            flight = settle()
+            if had is not None:
+                whole = flight is not None and len(flight.plan.sequences) == len(had.plan.sequences)
+                used += whole
+                dropped += not whole
+            return flight
+        engine._settle_flight = counting_flights
 
         def counting():
             nonlocal used, dropped
@@ -249,6 +262,15 @@ def test_planning_a_step_ahead_changes_nothing(model_folders, cuda_device, dtype
     assert got[:3] == expected[:3] and got[4] == expected[4]
     assert got[3] == expected[3]                     # cancelled at the same step in both
     assert used >= 10 and dropped >= 2, (used, dropped)
+    # The same with the next step launched before this step's tokens have reached the host.
+    got, used, dropped, _ = run(True, 64, launch_ahead=True)
+    # A request that arrives while a step is under way joins one step later, so the one that is
+    # cancelled at a fixed step has one token fewer by then; what it has is the same.
+    assert got[:3] == expected[:3] and got[4] == expected[4]
+    assert 0 < len(got[3]) <= len(expected[3]) and got[3] == expected[3][:len(got[3])]
+    assert used >= 10 and dropped >= 2, (used, dropped)
+    tight_launched, _, _, preempted_launched = run(True, 10, launch_ahead=True)
+    assert preempted_launched > 0 and tight_launched[:3] == expected[:3] and tight_launched[4] == expected[4]
     tight_expected, _, _, preempted_without = run(False, 10)
     tight, used, dropped, preempted = run(True, 10)
     assert preempted > 0 and preempted_without > 0

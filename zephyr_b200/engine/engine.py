@@ -29,7 +29,7 @@ from ..sampling import MT19937_64, Sampler, SamplingParams
 from ..weights import Checkpoint
 from .params import (Choice, FinishReason, GenerationOutput, GenerationParams, KvCacheOptions, RequestStatus, Usage)
 from .runner import ModelRunner, StepEntry
-from .scheduler import PagedSchedulerConfig, Scheduler, Sequence as Seq, SequenceState
+from .scheduler import PagedSchedulerConfig, ScheduledStep, Scheduler, Sequence as Seq, SequenceState
 
 _LOGGER = logging.getLogger("zephyr_b200")
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
@@ -64,6 +64,15 @@ class EngineStats:
     generated_tokens: int = 0
     preemptions: int = 0
     step_seconds: float = 0.0
+
+
+@dataclass
+class _Flight:
+    """A step that has been launched: its plan, the sequences it samples for, the selection under way."""
+
+    plan: Any
+    sampled: list
+    pending: Any
 
 
 class Engine:
@@ -128,7 +137,9 @@ class Engine:
         # While the device runs a step of decoders only, the host plans and describes the next one
         # (all but its tokens): ``look_ahead`` turns that off.
         self.look_ahead = True
-        self._ahead = None                      # (plan, entries, prepared) of the step after this one
+        self.launch_ahead = True                # ... and launches it where its tokens can stay on the device
+        self._flight = None                     # the step launched ahead: its plan and its selection under way
+        self._ahead = None                      # (plan, prepared) of the step after this one
         self._placeholders: set[tuple[int, int]] = set()   # sequences whose last token is still on the device
 
     # ------------------------------------------------------------------- set-up
@@ -230,8 +241,40 @@ class Engine:
 
     # -------------------------------------------------------------------- step
     def step(self) -> int:
-        """Schedule and run one step; returns the number of tokens it computed (0: nothing to do)."""
+        """Schedule and run one step; returns the number of tokens it computed (0: nothing to do).
+        The step may have been launched already, during the call before (see ``_launch_ahead``)."""
         started = time.perf_counter()
+        flight = self._settle_flight()
+        if flight is None:
+            flight = self._run_step()
+            if flight is None:
+                return 0
+        plan = flight.plan
+        if flight.pending is not None:
+            # Host work while the device runs the step: the next step is planned and described, and,
+            # where its tokens can go from this step's selection to its input on the device, launched.
+            ahead = self._plan_ahead(plan)
+            if ahead is not None and ahead[1] is not None:
+                self._flight = self._launch_ahead(flight, ahead)
+                if self._flight is not None:
+                    ahead = None
+            results = self.sampler.finish(flight.pending)        # also reads the step's status
+            for item, result in zip(flight.sampled, results):
+                sequence = self.sequences.get(item.sequence_id)
+                if sequence is None or sequence.is_terminal:
+                    continue        # ended or cancelled while its step was under way
+                if result.logprobs is not None:
+                    self._logprobs.setdefault(item.sequence_id, []).append(result.logprobs)
+                self._append_token(item.sequence_id, int(result.token_id))
+                self.stats.generated_tokens += 1
+            self._ahead = ahead
+        self.stats.steps += 1
+        self.stats.preemptions = self.scheduler.num_preemptions
+        self.stats.step_seconds += time.perf_counter() - started
+        return plan.num_tokens
+
+    def _run_step(self) -> "_Flight | None":
+        """Schedule a step (or take the plan made ahead), run it and launch its selection."""
         plan, prepared = self._take_ahead()
         if plan is None:
             plan = self.scheduler.schedule()
@@ -242,29 +285,19 @@ class Engine:
         if not plan.sequences:
             if self.scheduler.has_unfinished and not plan.preempted and not plan.rejected:
                 raise RuntimeError("the scheduler made no progress although sequences are unfinished")
-            return 0
+            return None
         logits = self.runner.step(self._entries(plan), prepared)
         self.scheduler.commit(plan)
-        sampled = [item for item in plan.sequences if item.sample]
         self.stats.prefill_tokens += sum(i.num_tokens for i in plan.sequences if i.num_tokens > 1 or not i.sample)
-        if sampled:
-            params = [self._requests[i.sequence_id[0]].sampling for i in sampled]
-            generators = [self._generators[i.sequence_id] for i in sampled]
-            sequences = [self.sequences[i.sequence_id] for i in sampled]
-            pending = self.sampler.launch(logits, params, generators, [s.token_ids for s in sequences],
-                                          [s.prompt_length for s in sequences])
-            ahead = self._plan_ahead(plan)      # host work while the device runs the step
-            results = self.sampler.finish(pending)        # also reads the step's status
-            for item, result in zip(sampled, results):
-                if result.logprobs is not None:
-                    self._logprobs.setdefault(item.sequence_id, []).append(result.logprobs)
-                self._append_token(item.sequence_id, int(result.token_id))
-            self._ahead = ahead
-            self.stats.generated_tokens += len(results)
-        self.stats.steps += 1
-        self.stats.preemptions = self.scheduler.num_preemptions
-        self.stats.step_seconds += time.perf_counter() - started
-        return plan.num_tokens
+        sampled = [item for item in plan.sequences if item.sample]
+        return _Flight(plan, sampled, self._launch_selection(logits, sampled) if sampled else None)
+
+    def _launch_selection(self, logits: torch.Tensor, sampled):
+        params = [self._requests[i.sequence_id[0]].sampling for i in sampled]
+        generators = [self._generators[i.sequence_id] for i in sampled]
+        sequences = [self.sequences[i.sequence_id] for i in sampled]
+        return self.sampler.launch(logits, params, generators, [s.token_ids for s in sequences],
+                                   [s.prompt_length for s in sequences])
 
     def _entries(self, plan) -> list[StepEntry]:
         entries = []
@@ -302,6 +335,45 @@ class Engine:
         if ahead.preempted or ahead.rejected or not ahead.sequences:
             return (ahead, None)
         return (ahead, self.runner.prepare(self._entries(ahead)))
+
+    def _launch_ahead(self, flight: "_Flight", ahead) -> "_Flight | None":
+        """Launch the step after ``flight`` before ``flight``'s tokens have reached the host: they go
+        from its selection's output to the next step's input on the device.  The device then never
+        waits for the host between two decode steps.  Only where nothing about the next step depends
+        on the tokens' values: the same sequences in the same order, one row of ids each, no
+        penalties (they need the history on the host).  A sequence that turns out to have ended on
+        its token has computed one token in vain; ``_settle_flight`` drops it."""
+        plan, prepared = ahead
+        sampled = flight.sampled
+        if (not self.launch_ahead or [i.sequence_id for i in plan.sequences] != [i.sequence_id for i in sampled]
+                or flight.pending.offsets != list(range(len(sampled)))
+                or any(self._requests[i.sequence_id[0]].sampling.uses_history for i in plan.sequences)):
+            return None
+        entries = self._entries(plan)
+        if not self.runner.holds(prepared, entries):
+            return None
+        logits = self.runner.step(entries, prepared, device_tokens=flight.pending.device_ids)
+        return _Flight(plan, list(plan.sequences), self._launch_selection(logits, plan.sequences))
+
+    def _settle_flight(self) -> "_Flight | None":
+        """The step launched ahead, now that the tokens of the step before it are known: sequences
+        that ended meanwhile fall out of it (their row was computed in vain); None if no step is
+        under way or none of its sequences is left."""
+        flight, self._flight = self._flight, None
+        if flight is None:
+            return None
+        alive = [item for item in flight.plan.sequences
+                 if item.sequence_id in self.sequences and self.sequences[item.sequence_id].state == SequenceState.DECODE
+                 and item.sequence_id in self.scheduler.running]
+        keep = {item.sequence_id for item in alive}
+        # The selection's rows stay as they were launched; rows of sequences that ended are skipped
+        # when the results are read (``step`` looks at the sequence's state).
+        plan = ScheduledStep(sequences=alive, preempted=flight.plan.preempted, rejected=flight.plan.rejected)
+        self.scheduler.commit(plan)
+        if not keep:
+            self.sampler.finish(flight.pending)      # nobody wants them, but the status word is looked at
+            return None
+        return _Flight(plan, flight.sampled, flight.pending)
 
     def _take_ahead(self):
         """(plan, prepared) for this step from the plan made one step ahead, or (None, None).  The

@@ -301,10 +301,14 @@ class ModelRunner:
             record["copied"][turn].synchronize()
         return turn
 
-    def _launch_graph(self, record: dict, turn: int, info: dict, decode_only: bool) -> tuple[torch.Tensor, dict]:
+    def _launch_graph(self, record: dict, turn: int, info: dict, decode_only: bool,
+                      device_tokens: torch.Tensor | None = None) -> tuple[torch.Tensor, dict]:
         """Copy the written description to the device and run the record's graph (captured at its first run)."""
         sizes, total = record["sizes"], record["offsets"][-1]
         record["device"].copy_(record["host"][turn], non_blocking=True)
+        if device_tokens is not None:       # the tokens come from the device, over what the host wrote in their place
+            at, rows = record["offsets"][0], info["R"]
+            record["device"][at:at + rows].copy_(device_tokens[:rows], non_blocking=True)
         event = record["copied"][turn] or torch.cuda.Event()
         event.record()
         record["copied"][turn] = event
@@ -351,6 +355,10 @@ class ModelRunner:
             return None
         return PreparedStep(key, turn, info, tuple(e.request_id for e in entries))
 
+    def holds(self, prepared: PreparedStep | None, entries: Sequence[StepEntry]) -> bool:
+        """True if ``step(entries, prepared)`` would use ``prepared`` as it is."""
+        return prepared is not None and self._still_holds(prepared, entries)
+
     def _still_holds(self, prepared: PreparedStep, entries: Sequence[StepEntry]) -> bool:
         """True if ``prepared`` was made for these entries and nothing has moved since."""
         if len(entries) != len(prepared.request_ids) or prepared.key not in self._graphs:
@@ -363,23 +371,32 @@ class ModelRunner:
         return True
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry], prepared: PreparedStep | None = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], prepared: PreparedStep | None = None,
+             device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Run the entries as one batch.  Returns float32 logits [sum of wanted places, vocab] on the
         device, in the order of the entries and of each entry's ``want``.  The call does not wait for
         the GPU; ``check()`` (or reading the logits on the host and then ``check()``) does.  The tensor
         returned by a decode-only step belongs to that step's graph and is overwritten by the next
         step of the same shape: use it (sample from it, copy it) before stepping again.
         ``prepared``: what ``prepare`` returned for these very entries, nothing else having touched the
-        runner in between; anything else is ignored and the step is described afresh."""
+        runner in between; anything else is ignored and the step is described afresh.
+        ``device_tokens`` (with a ``prepared`` that ``holds``): int32 on the device, the entries' tokens
+        in their order, for example a selection's output that has not reached the host yet; the
+        entries' own tokens are then not looked at."""
+        if device_tokens is not None and not self.holds(prepared, entries):
+            raise InvalidArgumentError("tokens on the device need a prepared step that still holds")
         if prepared is not None and self._still_holds(prepared, entries):
             # Everything but the tokens was checked and written by ``prepare``.
-            tokens = [int(e.tokens[0]) for e in entries]
-            if not 0 <= min(tokens) <= max(tokens) < self.model.spec.vocab_size:
-                raise InvalidArgumentError(f"a token id among {tokens} lies outside the vocabulary")
             record = self._graphs[prepared.key]
-            at = record["offsets"][0]
-            record["host"][prepared.turn].numpy()[at:at + len(entries)] = tokens
-            logits, info = self._launch_graph(record, prepared.turn, prepared.info, True)
+            if device_tokens is None:
+                tokens = [int(e.tokens[0]) for e in entries]
+                if not 0 <= min(tokens) <= max(tokens) < self.model.spec.vocab_size:
+                    raise InvalidArgumentError(f"a token id among {tokens} lies outside the vocabulary")
+                at = record["offsets"][0]
+                record["host"][prepared.turn].numpy()[at:at + len(entries)] = tokens
+            elif device_tokens.dtype != torch.int32 or device_tokens.numel() < len(entries) or not device_tokens.is_cuda:
+                raise InvalidArgumentError("device_tokens must be int32 on the device, one per entry")
+            logits, info = self._launch_graph(record, prepared.turn, prepared.info, True, device_tokens)
             before_all = info["ctx_before"]
         else:
             self._validate(entries)

@@ -165,7 +165,7 @@ class Sampler:
             host_values.copy_(out.logprobs, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return PendingSample(list(params), out.offsets, logits.shape[1], host_ids, host_values, done)
+        return PendingSample(list(params), out.offsets, logits.shape[1], host_ids, host_values, done, out.ids)
 
     def finish(self, pending: "PendingSample") -> list[SamplingResult]:
         """Wait for a launched selection; one ``SamplingResult`` per row."""
@@ -204,3 +204,4 @@ class PendingSample:
     host_ids: torch.Tensor
     host_values: torch.Tensor | None
     done: "torch.cuda.Event"
+    device_ids: torch.Tensor          # the rows' results on the device (a row's chosen id at its offset)
