@@ -59,7 +59,9 @@ def test_embedding_reports_bad_token(ops, cuda_device):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("wdtype", DTYPES)
-@pytest.mark.parametrize("rows,H", [(5, 100), (3, 1000), (2, 4096), (7, 24), (1, 5120)])
+@pytest.mark.parametrize("rows,H", [(5, 100), (3, 1000), (2, 4096), (7, 24), (1, 5120),
+                                    # many rows: bfloat16 rows of up to 2048 go a warp a row
+                                    (200, 1024), (70, 1000), (64, 2048), (100, 136), (65, 2056), (333, 8)])
 def test_rmsnorm_and_fused_add(ops, cuda_device, dtype, wdtype, rows, H):
     x = rand((rows, H), dtype, cuda_device, 3, 2.0)
     d = rand((rows, H), dtype, cuda_device, 4)
@@ -78,10 +80,11 @@ def test_rmsnorm_and_fused_add(ops, cuda_device, dtype, wdtype, rows, H):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_rmsnorm_over_heads(ops, cuda_device, dtype):
-    x = rand((9, 5, 48), dtype, cuda_device, 6)
-    w = (1 + rand((48,), torch.float32, cuda_device, 7, 0.1)).to(dtype)
-    got = ops.rmsnorm(x, w, 1e-6)
-    assert (got.double() - ref_rmsnorm(x, w, 1e-6)).abs().max() <= tol(dtype, 4.0)
+    for tokens in (9, 40):
+        x = rand((tokens, 5, 48), dtype, cuda_device, 6)
+        w = (1 + rand((48,), torch.float32, cuda_device, 7, 0.1)).to(dtype)
+        got = ops.rmsnorm(x, w, 1e-6)
+        assert (got.double() - ref_rmsnorm(x, w, 1e-6)).abs().max() <= tol(dtype, 4.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -5,6 +5,8 @@
 // (src/layer/activation.cu:31-33) and r = a + x in float32 (src/model/causal_lm/qwen3.cpp:85-87).
 #include <algorithm>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace zb {
@@ -135,6 +137,81 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* 
   }
 }
 
+// The same for bfloat16 rows of up to 32 * 8 * V elements (V up to 8: 2048), one warp a row, four rows a block: all of a
+// row's loads (the row, what is added to it, the scale) are in flight together, the values stay
+// in registers between the sum of squares and the scaling, and nothing waits at a block's barrier.
+// A prompt's 2048 rows of 1024 took 5.7 us with the kernel above (a second trip to memory for the
+// row, the scale element by element).
+constexpr int NORM_ROWS_PER_BLOCK = 4;
+
+template <int V, bool ADD>
+__global__ void __launch_bounds__(NORM_ROWS_PER_BLOCK * 32)
+rmsnorm_warp_rows_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ x,
+                         const __nv_bfloat16* __restrict__ delta, const void* __restrict__ w, int w_dtype, float eps,
+                         int rows, int H, long long x_stride, long long out_stride) {
+  const int lane = threadIdx.x & 31, row = blockIdx.x * NORM_ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int n_vec = H / 8;
+  __nv_bfloat16* xr = x + static_cast<size_t>(row) * x_stride;
+  const __nv_bfloat16* dr = ADD ? delta + static_cast<size_t>(row) * x_stride : nullptr;
+  __nv_bfloat16* orow = out + static_cast<size_t>(row) * out_stride;
+  uint4 xv[V], dv[V], sv[V][2];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int i = lane + 32 * j;
+    if (i < n_vec) {
+      xv[j] = *reinterpret_cast<const uint4*>(xr + i * 8);
+      if (ADD) dv[j] = *reinterpret_cast<const uint4*>(dr + i * 8);
+      if (w_dtype == DTYPE_F32) {
+        sv[j][0] = *reinterpret_cast<const uint4*>(static_cast<const float*>(w) + i * 8);
+        sv[j][1] = *reinterpret_cast<const uint4*>(static_cast<const float*>(w) + i * 8 + 4);
+      } else {
+        sv[j][0] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w) + i * 8);
+      }
+    }
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    if (lane + 32 * j >= n_vec) break;
+    __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(&xv[j]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 v = __bfloat1622float2(x2[e]);
+      if (ADD) {
+        const float2 d = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&dv[j])[e]);
+        x2[e] = __floats2bfloat162_rn(v.x + d.x, v.y + d.y);       // the stream keeps the rounded sum ...
+        v = __bfloat1622float2(x2[e]);                             // ... and the norm is taken of what it keeps
+      }
+      ss += v.x * v.x + v.y * v.y;
+    }
+    if (ADD) *reinterpret_cast<uint4*>(xr + (lane + 32 * j) * 8) = xv[j];
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int i = lane + 32 * j;
+    if (i >= n_vec) break;
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv[j]);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(x2[e]);
+      float2 scale;
+      if (w_dtype == DTYPE_F32) {
+        const float* s32 = reinterpret_cast<const float*>(&sv[j][0]);       // eight floats in the two vectors
+        scale = make_float2(s32[2 * e], s32[2 * e + 1]);
+      } else {
+        scale = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&sv[j][0])[e]);
+      }
+      o2[e] = __floats2bfloat162_rn(v.x * inv * scale.x, v.y * inv * scale.y);
+    }
+    *reinterpret_cast<uint4*>(orow + i * 8) = o;
+  }
+}
+
 // ----------------------------------------------------------------------------- SiLU * up
 // gu is [T, 2I]: columns [0, I) hold the gate, [I, 2I) the up projection.
 template <typename T>
@@ -226,6 +303,25 @@ int rmsnorm_launch(void* out, void* x, const void* delta, const void* w, int w_d
   if (rows == 0) return OK;
   const bool vec = aligned16<T>(out, H) && aligned16<T>(x, H) && x_stride % Vec<T>::N == 0 &&
                    out_stride % Vec<T>::N == 0 && (delta == nullptr || aligned16<T>(delta, H));
+  if (std::is_same<T, __nv_bfloat16>::value && vec && H % 8 == 0 && H <= 32 * 8 * 8 && rows >= 64 &&
+      reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    const int vectors = (H / 8 + 31) / 32;          // per lane
+    const int blocks = (rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
+    const bool add = delta != nullptr;
+#define ZB_ROWS(V_)                                                                                                  \
+  do {                                                                                                               \
+    if (add) rmsnorm_warp_rows_kernel<V_, true><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(                    \
+        (__nv_bfloat16*)out, (__nv_bfloat16*)x, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H, x_stride, out_stride); \
+    else rmsnorm_warp_rows_kernel<V_, false><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(                       \
+        (__nv_bfloat16*)out, (__nv_bfloat16*)x, nullptr, w, w_dtype, eps, rows, H, x_stride, out_stride);           \
+  } while (0)
+    if (vectors <= 1) ZB_ROWS(1);
+    else if (vectors <= 2) ZB_ROWS(2);
+    else if (vectors <= 4) ZB_ROWS(4);
+    else ZB_ROWS(8);
+#undef ZB_ROWS
+    return launch_result();
+  }
   const int per = vec ? Vec<T>::N : 1;
   int threads = ((H + per - 1) / per + 31) / 32 * 32;
   threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
