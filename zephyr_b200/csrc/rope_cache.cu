@@ -163,11 +163,14 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ q_out, const T* __rest
   }
 }
 
-// The same for bfloat16 and head sizes 64 and 128, eight bytes a lane: a head is HD / 8 lanes
-// (lane j owns elements 4j .. 4j + 3 of the first half and their partners in the second), so a warp
-// takes 32 / (HD / 8) heads of a token at once and every load and store is a vector.  The math,
-// the order of roundings and the cache layout are those of the kernel above.
-template <int HD>
+// The same for bfloat16 and head sizes 64 and 128, E = 4 or 8 elements of each half a lane: a head is
+// HD / (2 E) lanes (lane j owns elements E j .. E j + E - 1 of the first half and their partners in
+// the second), so a warp takes several heads of a token at once and every load and store is a
+// vector.  The math and the cache layout are those of the kernel above; the sum of squares runs
+// in another order.  Everything a lane needs is asked for in two rounds (the token's position and
+// row and the lane's elements and scales; then the page id and the angles), and with E = 8 a
+// prompt's tokens make half as many warps: the kernel is bound by those rounds, not by bytes.
+template <int HD, int E>
 __global__ void __launch_bounds__(ROPE_WARPS * 32)
 qk_norm_rope_cache_wide_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv,
                                long long qkv_stride, const void* __restrict__ q_norm_w,
@@ -175,64 +178,93 @@ qk_norm_rope_cache_wide_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfl
                                const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                int max_positions, const int* __restrict__ positions,
                                const int* __restrict__ token_row, CacheView cache, int nh, int nkv, int* status) {
-  constexpr int LANES = HD / 8, HEADS_PER_WARP = 32 / LANES, HALF = HD / 2;
+  constexpr int LANES = HD / (2 * E), HEADS_PER_WARP = 32 / LANES, HALF = HD / 2, WORDS = E / 2;
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, sub = lane % LANES;
   const int head = (blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5)) * HEADS_PER_WARP + lane / LANES;
   const int total_heads = cache.base != nullptr ? nh + 2 * nkv : nh;
   const bool active = head < total_heads;
-  const int pos = positions[t];
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
-  const int i = 4 * sub;                                        // this lane's elements i .. i + 3 and i + HALF ..
+  const int i = E * sub;                                        // this lane's elements i .. i + E - 1 and i + HALF ..
+  const int pos = positions[t], row = token_row[t];             // the step's description: older than any kernel of the step
+  // The scales do not depend on the step either.
+  float scale_x[E], scale_y[E];
+  const void* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+  if (active && w != nullptr) {
+#pragma unroll
+    for (int u = 0; u < E; ++u) {
+      scale_x[u] = load_scale(w, w_dtype, i + u);
+      scale_y[u] = load_scale(w, w_dtype, i + u + HALF);
+    }
+  }
   wait_for_prior_grids();           // the projections are an earlier kernel's output
   let_dependents_launch();
-  float x[4] = {0, 0, 0, 0}, y[4] = {0, 0, 0, 0};
+  unsigned xw[WORDS], yw[WORDS];
+#pragma unroll
+  for (int u = 0; u < WORDS; ++u) xw[u] = yw[u] = 0u;
   if (active) {
     const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * qkv_stride + static_cast<size_t>(head) * HD;
-    const uint2 xv = *reinterpret_cast<const uint2*>(src + i), yv = *reinterpret_cast<const uint2*>(src + i + HALF);
-    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
-    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
-    const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.x));
-    const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.y));
-    x[0] = x01.x; x[1] = x01.y; x[2] = x23.x; x[3] = x23.y;
-    y[0] = y01.x; y[1] = y01.y; y[2] = y23.x; y[3] = y23.y;
+    if (E == 8) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(src + i), yv = *reinterpret_cast<const uint4*>(src + i + HALF);
+      xw[0] = xv.x; xw[1] = xv.y; xw[WORDS - 2] = xv.z; xw[WORDS - 1] = xv.w;
+      yw[0] = yv.x; yw[1] = yv.y; yw[WORDS - 2] = yv.z; yw[WORDS - 1] = yv.w;
+    } else {
+      const uint2 xv = *reinterpret_cast<const uint2*>(src + i), yv = *reinterpret_cast<const uint2*>(src + i + HALF);
+      xw[0] = xv.x; xw[1] = xv.y;
+      yw[0] = yv.x; yw[1] = yv.y;
+    }
+  }
+  // The second round: where the row goes, and its angles.
+  long long off = 0;
+  if (active && !is_q) {
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    off = cache_row_offset(cache, row, pos, is_k ? 0 : 1, kvh, nkv, HD, status, t);
+  }
+  const bool rotates = active && (is_q || is_k) && cos_table != nullptr;
+  const bool pos_ok = pos >= 0 && pos < max_positions;
+  float cs[E], si[E];
+  if (rotates && pos_ok) {
+#pragma unroll
+    for (int u = 0; u < E; u += 4) {
+      const float4 c = *reinterpret_cast<const float4*>(cos_table + static_cast<size_t>(pos) * HALF + i + u);
+      const float4 sn = *reinterpret_cast<const float4*>(sin_table + static_cast<size_t>(pos) * HALF + i + u);
+      cs[u] = c.x; cs[u + 1] = c.y; cs[u + 2] = c.z; cs[u + 3] = c.w;
+      si[u] = sn.x; si[u + 1] = sn.y; si[u + 2] = sn.z; si[u + 3] = sn.w;
+    }
+  }
+  float x[E], y[E];
+#pragma unroll
+  for (int u = 0; u < WORDS; ++u) {
+    const float2 xf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[u]));
+    const float2 yf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yw[u]));
+    x[2 * u] = xf.x; x[2 * u + 1] = xf.y;
+    y[2 * u] = yf.x; y[2 * u + 1] = yf.y;
   }
   float ss = 0.0f;
 #pragma unroll
-  for (int u = 0; u < 4; ++u) ss += x[u] * x[u] + y[u] * y[u];
+  for (int u = 0; u < E; ++u) ss += x[u] * x[u] + y[u] * y[u];
 #pragma unroll
   for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // over the head's lanes
-  if (!active) return;
+  if (!active || off < 0) return;
 
-  __nv_bfloat16* dst;
-  if (is_q) {
-    dst = q_out + (static_cast<size_t>(t) * nh + head) * HD;
-  } else {
-    const int kvh = is_k ? head - nh : head - nh - nkv;
-    const long long off = cache_row_offset(cache, token_row[t], pos, is_k ? 0 : 1, kvh, nkv, HD, status, t);
-    if (off < 0) return;
-    dst = static_cast<__nv_bfloat16*>(cache.base) + off;
-  }
+  __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(t) * nh + head) * HD
+                            : static_cast<__nv_bfloat16*>(cache.base) + off;
   if (is_q || is_k) {
-    const void* w = is_q ? q_norm_w : k_norm_w;
     if (w != nullptr) {
       const float inv = rsqrtf(ss / static_cast<float>(HD) + eps);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        x[u] *= inv * load_scale(w, w_dtype, i + u);
-        y[u] *= inv * load_scale(w, w_dtype, i + u + HALF);
+      for (int u = 0; u < E; ++u) {
+        x[u] *= inv * scale_x[u];
+        y[u] *= inv * scale_y[u];
       }
     }
     if (cos_table != nullptr) {
-      if (pos < 0 || pos >= max_positions) {
+      if (!pos_ok) {
         if (sub == 0) report(status, STATUS_POSITION_OUT_OF_RANGE, pos, t);
         return;
       }
-      const float4 c = *reinterpret_cast<const float4*>(cos_table + static_cast<size_t>(pos) * HALF + i);
-      const float4 sn = *reinterpret_cast<const float4*>(sin_table + static_cast<size_t>(pos) * HALF + i);
-      const float cs[4] = {c.x, c.y, c.z, c.w}, si[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < E; ++u) {
         const float xr = x[u] * cs[u] - y[u] * si[u];
         const float yr = y[u] * cs[u] + x[u] * si[u];
         x[u] = xr;
@@ -240,16 +272,22 @@ qk_norm_rope_cache_wide_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfl
       }
     }
   }
-  // Four adjacent elements never straddle a 16-byte chunk of a cache row.
+  // E adjacent elements never straddle a 16-byte chunk of a cache row.
   const int lo = is_q ? i : kv_element_index(i, pos, HD, sizeof(__nv_bfloat16));
   const int hi = is_q ? i + HALF : kv_element_index(i + HALF, pos, HD, sizeof(__nv_bfloat16));
-  uint2 xo, yo;
-  *reinterpret_cast<__nv_bfloat162*>(&xo.x) = __floats2bfloat162_rn(x[0], x[1]);
-  *reinterpret_cast<__nv_bfloat162*>(&xo.y) = __floats2bfloat162_rn(x[2], x[3]);
-  *reinterpret_cast<__nv_bfloat162*>(&yo.x) = __floats2bfloat162_rn(y[0], y[1]);
-  *reinterpret_cast<__nv_bfloat162*>(&yo.y) = __floats2bfloat162_rn(y[2], y[3]);
-  *reinterpret_cast<uint2*>(dst + lo) = xo;
-  *reinterpret_cast<uint2*>(dst + hi) = yo;
+  unsigned xo[WORDS], yo[WORDS];
+#pragma unroll
+  for (int u = 0; u < WORDS; ++u) {
+    *reinterpret_cast<__nv_bfloat162*>(&xo[u]) = __floats2bfloat162_rn(x[2 * u], x[2 * u + 1]);
+    *reinterpret_cast<__nv_bfloat162*>(&yo[u]) = __floats2bfloat162_rn(y[2 * u], y[2 * u + 1]);
+  }
+  if (E == 8) {
+    *reinterpret_cast<uint4*>(dst + lo) = make_uint4(xo[0], xo[1], xo[WORDS - 2], xo[WORDS - 1]);
+    *reinterpret_cast<uint4*>(dst + hi) = make_uint4(yo[0], yo[1], yo[WORDS - 2], yo[WORDS - 1]);
+  } else {
+    *reinterpret_cast<uint2*>(dst + lo) = make_uint2(xo[0], xo[1]);
+    *reinterpret_cast<uint2*>(dst + hi) = make_uint2(yo[0], yo[1]);
+  }
 }
 
 // In-place rotation of x [T, heads, hd] (rows `stride` elements apart).
@@ -324,16 +362,21 @@ ZB_API int zb_qk_norm_rope_cache(void* q_out, const void* qkv, long long qkv_str
   else if ((hd == 64 || hd == 128) && qkv_stride % 4 == 0 && reinterpret_cast<uintptr_t>(qkv) % 8 == 0 &&
            reinterpret_cast<uintptr_t>(q_out) % 8 == 0 && reinterpret_cast<uintptr_t>(kv_cache) % 8 == 0 &&
            reinterpret_cast<uintptr_t>(cos_table) % 16 == 0 && reinterpret_cast<uintptr_t>(sin_table) % 16 == 0) {
-    const int per_warp = hd == 64 ? 4 : 2;
+    // Sixteen bytes a lane where everything is aligned for it and there are tokens enough to fill
+    // the GPU with half as many warps; eight bytes a lane otherwise.
+    const bool sixteen = T >= 64 && qkv_stride % 8 == 0 && reinterpret_cast<uintptr_t>(qkv) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(q_out) % 16 == 0 && reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
+    const int per_warp = 32 / (hd / (sixteen ? 16 : 8));
     const dim3 wide(T, (heads + ROPE_WARPS * per_warp - 1) / (ROPE_WARPS * per_warp));
-    if (hd == 64)
-      return launch_dependent(qk_norm_rope_cache_wide_kernel<64>, wide, dim3(ROPE_WARPS * 32), 0, s, false,
-                              (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps,
-                              cos_table, sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
-    else
-      return launch_dependent(qk_norm_rope_cache_wide_kernel<128>, wide, dim3(ROPE_WARPS * 32), 0, s, false,
-                              (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps,
-                              cos_table, sin_table, max_positions, positions, token_row, cache, nh, nkv, status);
+#define ZB_WIDE(HD_, E_)                                                                                            \
+  return launch_dependent(qk_norm_rope_cache_wide_kernel<HD_, E_>, wide, dim3(ROPE_WARPS * 32), 0, s, false,        \
+                          (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, \
+                          cos_table, sin_table, max_positions, positions, token_row, cache, nh, nkv, status)
+    if (hd == 64 && sixteen) ZB_WIDE(64, 8);
+    else if (hd == 64) ZB_WIDE(64, 4);
+    else if (sixteen) ZB_WIDE(128, 8);
+    else ZB_WIDE(128, 4);
+#undef ZB_WIDE
   } else
     qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, 0, s>>>(
         (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, q_norm_w, k_norm_w, w_dtype, eps, cos_table,
