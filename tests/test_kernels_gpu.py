@@ -106,7 +106,7 @@ def test_gather_rows(ops, cuda_device, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,I", [(5, 200), (3, 3072), (130, 144), (1, 8)])
+@pytest.mark.parametrize("T,I", [(5, 200), (3, 3072), (130, 144), (1, 8), (64, 3072), (100, 8), (77, 4104), (300, 264)])
 def test_silu_mul_blocked_layout(ops, cuda_device, dtype, T, I):
     g = rand((T, I), dtype, cuda_device, 8, 3.0)
     u = rand((T, I), dtype, cuda_device, 9, 3.0)

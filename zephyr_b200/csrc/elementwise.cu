@@ -282,6 +282,40 @@ __global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __rest
   }
 }
 
+// The same with one block per token row: no division to find the row, and a thread's loads (two
+// blocks of eight outputs where the row has them) are all asked for before the first is used.
+template <typename T>
+__global__ void silu_mul_blocked_rows_kernel(T* __restrict__ out, const T* __restrict__ gu, int I) {
+  constexpr int N = Vec<T>::N, PARTS = 8 / N;
+  const int per_row = I / 8;
+  const T* src = gu + static_cast<size_t>(blockIdx.x) * 2 * I;
+  T* dst = out + static_cast<size_t>(blockIdx.x) * I;
+  for (int j0 = threadIdx.x; j0 < per_row; j0 += 2 * blockDim.x) {
+    const int j1 = j0 + blockDim.x;
+    const bool second = j1 < per_row;
+    float g[2][PARTS][N], u[2][PARTS][N];
+#pragma unroll
+    for (int p = 0; p < PARTS; ++p) {
+      load_vec<T>(src + j0 * 16 + p * N, g[0][p]);
+      load_vec<T>(src + j0 * 16 + 8 + p * N, u[0][p]);
+      if (second) {
+        load_vec<T>(src + j1 * 16 + p * N, g[1][p]);
+        load_vec<T>(src + j1 * 16 + 8 + p * N, u[1][p]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      if (b == 1 && !second) break;
+#pragma unroll
+      for (int p = 0; p < PARTS; ++p) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) g[b][p][k] = g[b][p][k] / (1.0f + expf(-g[b][p][k])) * u[b][p][k];
+        store_vec<T>(dst + (b ? j1 : j0) * 8 + p * N, g[b][p]);
+      }
+    }
+  }
+}
+
 template <typename T> bool aligned16(const void* p, long long elems) {
   return reinterpret_cast<uintptr_t>(p) % 16 == 0 && elems % Vec<T>::N == 0;
 }
@@ -409,6 +443,14 @@ ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int b
   if (blocked) {
     if (T == 0 || I == 0) return OK;
     const bool vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0;
+    if (vec && T >= 64 && T <= 65535 * 1024) {
+      const int per_row = I / 8;
+      int threads = ((per_row + 1) / 2 + 31) / 32 * 32;
+      threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+      if (dtype == DTYPE_F32) silu_mul_blocked_rows_kernel<float><<<T, threads, 0, s>>>((float*)out, (const float*)gu, I);
+      else silu_mul_blocked_rows_kernel<__nv_bfloat16><<<T, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
+      return launch_result();
+    }
     const long long total = vec ? static_cast<long long>(T) * (I / 8) : static_cast<long long>(T) * I;
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
     if (dtype == DTYPE_F32) {
