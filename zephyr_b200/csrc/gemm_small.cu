@@ -76,7 +76,7 @@ gemm_small_kernel(const SmallGemmArgs a) {
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
 
-#pragma unroll 4
+#pragma unroll 8
   for (int b = b_begin; b < b_end; ++b) {
     const int k = b * 32;
     const bool k_ok = k + 8 * t + 8 <= a.K;          // K is a multiple of 8: a chunk is whole or absent
@@ -99,7 +99,10 @@ gemm_small_kernel(const SmallGemmArgs a) {
     red[warp][mt][g + 8][2 * t] = acc[mt][2];
     red[warp][mt][g + 8][2 * t + 1] = acc[mt][3];
   }
-  cluster.sync();           // every CTA of the cluster has its partial sums in its shared memory
+  // Every CTA of the cluster has its partial sums in its shared memory; a cluster of one needs only
+  // its own barrier (the cluster's costs a fence that the language-model head paid 9496 times).
+  if (ksplit == 1) __syncthreads();
+  else cluster.sync();
 
   if (krank == 0) {
     // The first CTA of the cluster adds all partial sums, warp by warp and CTA by CTA, and writes.
@@ -134,7 +137,7 @@ gemm_small_kernel(const SmallGemmArgs a) {
       }
     }
   }
-  cluster.sync();           // nobody leaves while its shared memory may still be read
+  if (ksplit > 1) cluster.sync();           // nobody leaves while its shared memory may still be read
 }
 
 template <int MT, typename TOut, bool SWIGLU>
