@@ -156,3 +156,63 @@ def test_repeated_step_shapes_replay_a_graph(model_folders, cuda_device, dtype):
     rows = collect(steps, outputs[True])
     first, worst, where = first_mismatch(rows, {r: t[:fed[r]] for r, t in requests.items()}, folder, dtype)
     assert first is None, f"{dtype}: {first}; worst {worst:.3e} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prepared_steps_and_tokens_from_the_device(model_folders, cuda_device, dtype):
+    """A decode step described ahead of its tokens (``prepare``), and one whose tokens never visit
+    the host (``device_tokens``: the argmax of the step before, still on the device), give the
+    logits of steps described the ordinary way, bit for bit; a prepared step that no longer holds is
+    refused when it is given tokens on the device and ignored otherwise."""
+    import torch
+
+    from zephyr_b200.config import InvalidArgumentError
+    from zephyr_b200.engine import StepEntry
+    from zephyr_b200.engine.replay import TraceReplayer
+    from zephyr_b200.kernels import ops
+
+    name = "C"
+    folder = model_folders(name, dtype)
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = {f"p{i}": random_tokens(vocab, 11 + 6 * i, seed=500 + i) for i in range(3)}
+
+    def decode(mode: str):
+        runner = TraceReplayer(folder, dtype, 256, page_size=TINY[name]["page_size"], max_requests=4).runner
+        tokens = {}
+        for rid, prompt in prompts.items():
+            assert runner.add_request(rid)
+            logits = runner.step([StepEntry(rid, prompt, (len(prompt) - 1,))])
+            tokens[rid] = int(logits[0].argmax())
+        rows, device_ids = [], None
+        for step in range(8):
+            entries = [StepEntry(rid, [tokens[rid]], (0,)) for rid in prompts]
+            if mode == "plain" or step < 2:          # the graph is captured by the first decode step
+                logits = runner.step(entries)
+            elif mode == "prepared":
+                placeholders = [StepEntry(rid, [-1], (0,)) for rid in prompts]
+                prepared = runner.prepare(placeholders)
+                assert prepared is not None and runner.holds(prepared, entries)
+                logits = runner.step(entries, prepared)
+            else:
+                prepared = runner.prepare([StepEntry(rid, [-1], (0,)) for rid in prompts])
+                assert prepared is not None
+                logits = runner.step([StepEntry(rid, [-1], (0,)) for rid in prompts], prepared, device_tokens=device_ids)
+            device_ids = ops.sample(logits, runner.status)          # int32 on the device, one per row
+            rows.append(logits.clone())
+            for rid, token in zip(prompts, device_ids.tolist()):
+                tokens[rid] = token
+        runner.check()
+        return runner, torch.stack(rows)
+
+    _, plain = decode("plain")
+    for mode in ("prepared", "device"):
+        runner, got = decode(mode)
+        assert torch.equal(got, plain), mode
+    # A prepared step goes stale when the runner moves on without it.
+    stale = runner.prepare([StepEntry(rid, [-1], (0,)) for rid in prompts])
+    fresh = [StepEntry(rid, [1], (0,)) for rid in prompts]
+    runner.step(fresh)
+    assert not runner.holds(stale, fresh)
+    runner.step(fresh, stale)                                       # ignored: described afresh
+    with pytest.raises(InvalidArgumentError, match="still holds"):
+        runner.step(fresh, stale, device_tokens=torch.zeros(3, dtype=torch.int32, device=cuda_device))
