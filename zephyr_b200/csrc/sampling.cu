@@ -25,10 +25,11 @@
 // How it runs: passes over a row are spread over many CTAs (chunks of 4096 logits) and meet through
 // small per-chunk partial results, merged in chunk order so that a row's result does not depend on
 // the batch around it; the chunk that arrives last finishes the row's maximum.  Ranking runs in two
-// steps, one CTA per row each.  The first ranks only the head of the order: a histogram of a sample of
-// the row over the keys' leading 12 bits says which leading bins hold about 2048 tokens, all tokens
-// of those bins are sorted in shared memory (if they are at most 4096), and the row is done if the
-// draw (or the report) can be decided within them, which it can whenever the distribution has a
+// steps.  The first ranks only the head of the order: a histogram of a sample of the row over the
+// keys' leading 12 bits says which leading bins hold about 2048 tokens (one CTA per row), the pass
+// that forms the weights (many CTAs per row) lists all tokens of those bins, and one CTA per row
+// sorts the list in shared memory (if it has at most 4096 entries) and decides the row if the
+// draw (or the report) can be decided within it, which it can whenever the distribution has a
 // peak.  Rows that are not done go through a
 // stable least-significant-digit radix sort of the whole vocabulary.  Both steps produce the same
 // order and feed the same draw, whose sums run in blocks of 4096 ranks, so a rank's prefix sum does
@@ -43,6 +44,9 @@ constexpr int ROW_THREADS = 1024;           // CTAs that own a whole row
 constexpr double GREEDY_TEMPERATURE = 1e-7;
 constexpr int SAMPLE_MAX_VOCAB = 1 << 22;
 constexpr int SORT_UNROLL = 8;              // loads in flight per lane of the ranking kernel
+constexpr int HEAD_BINS = 4096;             // the keys' leading 12 bits
+constexpr int HEAD_MAX = 4096;              // tokens of the order's head, sorted in shared memory
+constexpr int HEAD_AIM = 2048;              // tokens the head is meant to have when the vocabulary is larger
 
 // One row's parameters, as the host packs them (64 bytes).
 struct SampleRow {
@@ -213,10 +217,27 @@ sample_max_kernel(const float* __restrict__ logits, long long row_stride, int V,
 // ------------------------------------------------------------------------ weights and their sums
 // Grid (chunks, rows).  weights[r][i] = exp(z_i), zero where min-p removes the token from a row
 // that draws in index order.  part_all: the chunk's sum of exp(z); part_kept: of the weights.
+// A warp's lanes that `take` get consecutive places in a job's list of candidates (one addition to
+// the job's count for all of them) and leave their key and token there if the list has room.
+__device__ __forceinline__ void add_candidates(bool take, unsigned key, int token, int* count, unsigned* keys, int* tokens,
+                                               int room) {
+  const unsigned takers = __ballot_sync(0xffffffffu, take);
+  if (takers == 0) return;
+  const int lane = threadIdx.x & 31, leader = __ffs(takers) - 1;
+  int base = 0;
+  if (lane == leader) base = atomicAdd(count, __popc(takers));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  const int at = base + __popc(takers & ((1u << lane) - 1u));
+  if (take && at < room) {
+    keys[at] = key;
+    tokens[at] = token;
+  }
+}
+
 __global__ void __launch_bounds__(CHUNK_THREADS)
 sample_exp_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunks,
                   const SampleRow* __restrict__ rows, const float* __restrict__ row_max, float* __restrict__ weights,
-                  float* part_all, float* part_kept) {
+                  float* part_all, float* part_kept, unsigned* sort_keys, int* sort_idx, int* job_state) {
   __shared__ float scratch_a[33], scratch_b[33];
   const int c = blockIdx.x, r = blockIdx.y;
   const SampleRow p = rows[r];
@@ -228,15 +249,33 @@ sample_exp_kernel(const float* __restrict__ logits, long long row_stride, int V,
   const bool filter = !greedy && !is_ranked(p) && p.min_p > 0.0;
   const float* x = logits + static_cast<size_t>(r) * row_stride;
   float* w = weights + static_cast<size_t>(r) * V;
+  // Rows that are ranked (by weight for a draw, by z for a report) leave the tokens of the order's
+  // head in their job's first buffers on the way: those whose key lies in the leading bins that
+  // sample_head_bins_kernel chose.  The list is the head kernel's input.
+  const int draw_job = !greedy && is_ranked(p) ? p.sort_slot : -1;
+  const int report_job = p.num_logprobs > 0 ? p.report_slot : -1;
+  const int room = min(HEAD_MAX, V);
+  const unsigned draw_bins = draw_job >= 0 ? job_state[4 * draw_job + 2] : 0u;
+  const unsigned report_bins = report_job >= 0 ? job_state[4 * report_job + 2] : 0u;
   const int begin = c * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
   float all = 0.0f, kept = 0.0f;
-  for (int i = begin + threadIdx.x; i < end; i += CHUNK_THREADS) {
-    const float e = expf(scaled(x[i], maximum, T));
+  for (int i0 = begin; i0 < end; i0 += CHUNK_THREADS) {          // whole warps stay in the loop
+    const int i = i0 + threadIdx.x;
+    const bool valid = i < end;
+    const float z = valid ? scaled(x[i], maximum, T) : 0.0f;
+    const float e = valid ? expf(z) : 0.0f;
     // The largest probability is exp(0) = 1 before normalisation.
     const float k = filter && !(static_cast<double>(e) > p.min_p) ? 0.0f : e;
     all += e;
     kept += k;
-    if (!greedy) w[i] = k;
+    if (valid && !greedy) w[i] = k;
+    if (draw_bins)
+      add_candidates(valid && (~__float_as_uint(k) >> 20) < draw_bins, ~__float_as_uint(k), i, &job_state[4 * draw_job + 3],
+                     sort_keys + static_cast<size_t>(draw_job) * 2 * V, sort_idx + static_cast<size_t>(draw_job) * 2 * V, room);
+    if (report_bins)
+      add_candidates(valid && (__float_as_uint(fabsf(z)) >> 20) < report_bins, __float_as_uint(fabsf(z)), i,
+                     &job_state[4 * report_job + 3], sort_keys + static_cast<size_t>(report_job) * 2 * V,
+                     sort_idx + static_cast<size_t>(report_job) * 2 * V, room);
   }
   all = block_sum(all, scratch_a);
   kept = block_sum(kept, scratch_b);
@@ -350,7 +389,7 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
   const int r = job.row;
   const float maximum = row_max[r];
   if (!isfinite(maximum)) return;
-  if (job_state[2 * blockIdx.x + 1]) return;        // decided within the head of the order
+  if (job_state[4 * blockIdx.x + 1]) return;        // decided within the head of the order
   const double T = scaling_temperature(rows[r]);
   const float* x = logits + static_cast<size_t>(r) * row_stride;
   const float* w = weights + static_cast<size_t>(r) * V;
@@ -424,7 +463,7 @@ sample_sort_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ l
     }
     __syncthreads();            // this pass's stores are visible to the whole CTA before the next reads them
   }
-  if (threadIdx.x == 0) job_state[2 * blockIdx.x] = V;
+  if (threadIdx.x == 0) job_state[4 * blockIdx.x] = V;
 }
 
 // ---------------------------------------------------------------------- the draw over the ranks
@@ -561,94 +600,83 @@ __device__ float chunk_total(const float* part, int r, int chunks) {
 }
 
 // ------------------------------------------------------------------- ranking the head of the order
-constexpr int HEAD_BINS = 4096;             // the keys' leading 12 bits
-constexpr int HEAD_MAX = 4096;              // tokens sorted in shared memory
-constexpr int HEAD_AIM = 2048;              // tokens the head is meant to have when the vocabulary is larger
 
-// One CTA per job.  job_state[2 * job] = how many ranks lie sorted in the job's second buffer;
-// job_state[2 * job + 1] = 1 if the row needs no more than those.
+// A job's four words of state: [0] how many ranks lie sorted in the job's second buffer, [1] 1 if the
+// row needs no more than those, [2] the leading bins of the keys' first 12 bits that make the head of
+// the order (0: no head), [3] how many tokens lie in those bins.
+//
+// One CTA per job, before the weights are formed.  Where the head ends is guessed from every
+// `stride`-th token: the leading bins that hold HEAD_AIM / stride of them hold about HEAD_AIM tokens
+// of the whole row.  The guess only decides how many ranks the head has (none, if more than
+// HEAD_MAX tokens lie in those bins after all); the head is always every token of the leading
+// bins, so it is the true start of the order.  The pass over the whole row that finds those tokens
+// is the one that forms the weights (sample_exp_kernel, many CTAs a row): a single CTA walking the
+// row twice took 100 us.
 __global__ void __launch_bounds__(ROW_THREADS)
-sample_rank_head_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
-                        int chunks, const SampleRow* __restrict__ rows, const float* __restrict__ row_max,
-                        const float* __restrict__ weights, const float* __restrict__ part_all, unsigned* keys, int* idx,
-                        const int* __restrict__ row_arg, int* job_state, int* out_ids) {
-  __shared__ unsigned long long candidates[HEAD_MAX];      // first used as the histogram
-  __shared__ RankScratch sh;
+sample_head_bins_kernel(const SortJob* __restrict__ jobs, const float* __restrict__ logits, long long row_stride, int V,
+                        const SampleRow* __restrict__ rows, const float* __restrict__ row_max, int* job_state) {
+  __shared__ int hist[HEAD_BINS];
   __shared__ int scratch[33];
-  __shared__ int s_bins, s_fill;
-  int* hist = reinterpret_cast<int*>(candidates);
+  __shared__ int s_bins;
+  const SortJob job = jobs[blockIdx.x];
+  const int r = job.row;
+  const float maximum = row_max[r];
+  int* state = job_state + 4 * blockIdx.x;
+  if (threadIdx.x == 0) state[0] = state[1] = state[2] = state[3] = 0;
+  if (!isfinite(maximum)) return;
+  const int stride = (V + HEAD_MAX - 1) / HEAD_MAX;
+  if (stride == 1) {                 // the whole row fits into the head
+    if (threadIdx.x == 0) state[2] = HEAD_BINS;
+    return;
+  }
+  const double T = scaling_temperature(rows[r]);
+  const float* x = logits + static_cast<size_t>(r) * row_stride;
+  for (int e = threadIdx.x; e < HEAD_BINS; e += ROW_THREADS) hist[e] = 0;
+  if (threadIdx.x == 0) s_bins = 0;
+  __syncthreads();
+  for (int i = threadIdx.x * stride; i < V; i += ROW_THREADS * stride) {
+    const float z = scaled(x[i], maximum, T);
+    const unsigned key = job.by_z ? __float_as_uint(fabsf(z)) : ~__float_as_uint(expf(z));
+    atomicAdd(&hist[key >> 20], 1);
+  }
+  __syncthreads();
+  constexpr int PER = HEAD_BINS / ROW_THREADS;
+  int counts[PER], local = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) { counts[j] = hist[threadIdx.x * PER + j]; local += counts[j]; }
+  int total;
+  int run = block_exclusive_scan(local, scratch, total);
+  int leading = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    run += counts[j];
+    if (run * stride <= HEAD_AIM) leading = threadIdx.x * PER + j + 1;
+  }
+  if (leading > 0) atomicMax(&s_bins, leading);
+  __syncthreads();
+  if (threadIdx.x == 0) state[2] = s_bins;
+}
+
+// One CTA per job, after the weights: sorts the head's tokens and decides the row if they are enough.
+__global__ void __launch_bounds__(ROW_THREADS)
+sample_rank_head_kernel(const SortJob* __restrict__ jobs, int V, int chunks, const SampleRow* __restrict__ rows,
+                        const float* __restrict__ row_max, const float* __restrict__ part_all, unsigned* keys, int* idx,
+                        const int* __restrict__ row_arg, int* job_state, int* out_ids) {
+  __shared__ unsigned long long candidates[HEAD_MAX];
+  __shared__ RankScratch sh;
   const SortJob job = jobs[blockIdx.x];
   const int r = job.row;
   const SampleRow p = rows[r];
-  const float maximum = row_max[r];
-  if (threadIdx.x == 0) { job_state[2 * blockIdx.x] = 0; job_state[2 * blockIdx.x + 1] = 0; }
-  if (!isfinite(maximum)) return;
-  const double T = scaling_temperature(p);
-  const float* x = logits + static_cast<size_t>(r) * row_stride;
-  const float* w = weights + static_cast<size_t>(r) * V;
-  // Where the head ends is guessed from every `stride`-th token: the leading bins that hold
-  // HEAD_AIM / stride of them hold about HEAD_AIM tokens of the whole row.  The guess only decides how
-  // many ranks the head has (none, if more than HEAD_MAX tokens lie in those bins after all); the
-  // head is always every token of the leading bins, so it is the true start of the order.
-  const int stride = (V + HEAD_MAX - 1) / HEAD_MAX;
-  int bins = HEAD_BINS;
-  if (stride > 1) {
-    for (int e = threadIdx.x; e < HEAD_BINS; e += ROW_THREADS) hist[e] = 0;
-    if (threadIdx.x == 0) s_bins = 0;
-    __syncthreads();
-    for (int i = threadIdx.x * stride; i < V; i += ROW_THREADS * stride)
-      atomicAdd(&hist[sort_key(job, i, x, w, maximum, T) >> 20], 1);
-    __syncthreads();
-    constexpr int PER = HEAD_BINS / ROW_THREADS;
-    int counts[PER], local = 0;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) { counts[j] = hist[threadIdx.x * PER + j]; local += counts[j]; }
-    int total;
-    int run = block_exclusive_scan(local, scratch, total);
-    int leading = 0;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      run += counts[j];
-      if (run * stride <= HEAD_AIM) leading = threadIdx.x * PER + j + 1;
-    }
-    if (leading > 0) atomicMax(&s_bins, leading);
-    __syncthreads();
-    bins = s_bins;
-    if (bins == 0) return;
-  }
-  __syncthreads();                                   // the histogram is done with
-  for (int e = threadIdx.x; e < HEAD_MAX; e += ROW_THREADS) candidates[e] = ~0ull;
-  if (threadIdx.x == 0) s_fill = 0;
-  __syncthreads();
-  // Loads run SORT_UNROLL steps ahead of their use.  A warp takes its places among the candidates with
-  // one addition for all its lanes.
-  const int lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < V + lane; i += ROW_THREADS * SORT_UNROLL) {       // whole warps stay in the loop
-    unsigned key[SORT_UNROLL];
-#pragma unroll
-    for (int u = 0; u < SORT_UNROLL; ++u) {
-      const int e = i + u * ROW_THREADS;
-      key[u] = e < V ? sort_key(job, e, x, w, maximum, T) : ~0u;
-    }
-#pragma unroll
-    for (int u = 0; u < SORT_UNROLL; ++u) {
-      const int e = i + u * ROW_THREADS;
-      const bool take = e < V && static_cast<int>(key[u] >> 20) < bins;
-      const unsigned takers = __ballot_sync(0xffffffffu, take);
-      if (takers == 0) continue;
-      int base = 0;
-      if (lane == __ffs(takers) - 1) base = atomicAdd(&s_fill, __popc(takers));
-      base = __shfl_sync(0xffffffffu, base, __ffs(takers) - 1);
-      const int at = base + __popc(takers & ((1u << lane) - 1u));
-      if (take && at < HEAD_MAX)
-        candidates[at] = (static_cast<unsigned long long>(key[u]) << 32) | static_cast<unsigned>(e);
-    }
-  }
-  __syncthreads();
-  const int n = s_fill;
-  if (n == 0 || n > HEAD_MAX) return;                // more tokens in the leading bins than the guess allowed for
+  int* state = job_state + 4 * blockIdx.x;
+  const int n = state[3];
+  if (!isfinite(row_max[r]) || state[2] == 0 || n == 0 || n > min(HEAD_MAX, V)) return;      // no head, or more than fits
   int padded = 1;
   while (padded < n) padded <<= 1;
+  const unsigned* found_keys = keys + static_cast<size_t>(blockIdx.x) * 2 * V;
+  const int* found_tokens = idx + static_cast<size_t>(blockIdx.x) * 2 * V;
+  for (int e = threadIdx.x; e < padded; e += ROW_THREADS)
+    candidates[e] = e < n ? (static_cast<unsigned long long>(found_keys[e]) << 32) | static_cast<unsigned>(found_tokens[e]) : ~0ull;
+  __syncthreads();
   // Bitonic sort, ascending: by key, equal keys by index.
   for (int size = 2; size <= padded; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -668,15 +696,15 @@ sample_rank_head_kernel(const SortJob* __restrict__ jobs, const float* __restric
     source[e] = static_cast<int>(candidates[e] & 0xffffffffu);
   }
   __syncthreads();
-  if (threadIdx.x == 0) job_state[2 * blockIdx.x] = n;
+  if (threadIdx.x == 0) state[0] = n;
   if (job.by_z) {
-    if (threadIdx.x == 0) job_state[2 * blockIdx.x + 1] = n >= min(p.num_logprobs, V);
+    if (threadIdx.x == 0) state[1] = n >= min(p.num_logprobs, V);
     return;
   }
   const int token = ranked_draw(p, sorted, source, n, V, chunk_total(part_all, r, chunks), sh);
   if (threadIdx.x == 0 && token != -1) {
     out_ids[p.result_offset] = token >= 0 ? token : row_arg[r];
-    job_state[2 * blockIdx.x + 1] = 1;
+    state[1] = 1;
   }
 }
 
@@ -694,10 +722,10 @@ sample_select_sorted_kernel(int V, int chunks, const SampleRow* __restrict__ row
     if (threadIdx.x == 0) out_ids[p.result_offset] = row_arg[r];
     return;
   }
-  if (job_state[2 * p.sort_slot + 1]) return;
+  if (job_state[4 * p.sort_slot + 1]) return;
   const unsigned* sorted = keys + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
   const int* source = idx + (static_cast<size_t>(p.sort_slot) * 2 + 1) * V;
-  const int token = ranked_draw(p, sorted, source, job_state[2 * p.sort_slot], V, chunk_total(part_all, r, chunks), sh);
+  const int token = ranked_draw(p, sorted, source, job_state[4 * p.sort_slot], V, chunk_total(part_all, r, chunks), sh);
   if (threadIdx.x == 0) out_ids[p.result_offset] = token >= 0 ? token : row_arg[r];
 }
 
@@ -754,7 +782,7 @@ constexpr int PHASE_REPORT = 8;         // some row reports log-probabilities
 //                results start at its result_offset: the chosen token, then its top tokens if it reports.
 //   out_logprobs parallel to out_ids, written for reporting rows only; may be null without PHASE_REPORT.
 //   jobs         the rows to rank, by weight (draws with top-k or top-p) or by z (reports with n > 0);
-//                sort_keys and sort_idx hold 2 * n_jobs * V entries each, job_state 2 * n_jobs ints.
+//                sort_keys and sort_idx hold 2 * n_jobs * V entries each, job_state 4 * n_jobs ints.
 //   part_f       3 * rows * chunks floats; part_i rows * chunks ints; counters: rows ints, zero on entry and
 //                on exit; row_max, row_arg: rows entries; weights: rows * V floats (unused without PHASE_WEIGHTS).
 ZB_API int zb_sample(int* out_ids, float* out_logprobs, float* logits, long long row_stride, int rows, int V,
@@ -781,13 +809,15 @@ ZB_API int zb_sample(int* out_ids, float* out_logprobs, float* logits, long long
         logits, row_stride, rows, V, params, static_cast<const TokenAdjustment*>(adjustments), n_adjustments, status);
   sample_max_kernel<<<chunk_grid, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, part_max, part_i,
                                                         counters, row_max, row_arg, out_ids, status);
+  if (n_jobs > 0)
+    sample_head_bins_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, params,
+                                                          row_max, job_state);
   if (phases & PHASE_WEIGHTS)
     sample_exp_kernel<<<chunk_grid, CHUNK_THREADS, 0, s>>>(logits, row_stride, V, chunks, params, row_max, weights,
-                                                          part_all, part_kept);
+                                                          part_all, part_kept, sort_keys, sort_idx, job_state);
   if (n_jobs > 0) {
-    sample_rank_head_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, chunks,
-                                                          params, row_max, weights, part_all, sort_keys, sort_idx, row_arg,
-                                                          job_state, out_ids);
+    sample_rank_head_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), V, chunks, params, row_max,
+                                                          part_all, sort_keys, sort_idx, row_arg, job_state, out_ids);
     sample_sort_kernel<<<n_jobs, ROW_THREADS, 0, s>>>(static_cast<const SortJob*>(jobs), logits, row_stride, V, params,
                                                      row_max, weights, sort_keys, sort_idx, job_state);
   }

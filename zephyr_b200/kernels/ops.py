@@ -843,13 +843,13 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[SampleRow] | None, status: 
     weights = _sample_buffer(device, "weights", R * V, torch.float32) if phases else None
     sort_keys = _sample_buffer(device, "sort_keys", 2 * len(jobs) * V, torch.int32) if jobs else None
     sort_idx = _sample_buffer(device, "sort_idx", 2 * len(jobs) * V, torch.int32) if jobs else None
-    job_state = _sample_buffer(device, "job_state", 2 * len(jobs), torch.int32) if jobs else None
+    job_state = _sample_buffer(device, "job_state", 4 * len(jobs), torch.int32) if jobs else None
     _check(library().zb_sample(
         _ptr(ids), _ptr(logprobs), _ptr(logits), logits.stride(0), R, V, base,
         base + at_adjustments if adjustments else None, len(adjustments), base + at_jobs if jobs else None, len(jobs),
         phases, _ptr(part_f), _ptr(part_i), _ptr(counters), _ptr(row_max), _ptr(row_arg), _ptr(weights),
         _ptr(sort_keys), _ptr(sort_idx), _ptr(job_state), _ptr(status), _stream()),
-        "sample", kernels=1 + bool(adjustments) + 2 * bool(jobs) + bin(phases).count("1"))
+        "sample", kernels=1 + bool(adjustments) + 3 * bool(jobs) + bin(phases).count("1"))
     _sample_buffers[(device, "jobs_of_last_call")] = len(jobs)
     return SampleOutput(ids, logprobs, offsets)
 
@@ -862,8 +862,8 @@ def last_sample_job_state(device: torch.device | str | None = None) -> list[tupl
     count = _sample_buffers.get((device, "jobs_of_last_call"), 0)
     if not count:
         return []
-    state = _sample_buffers[(device, "job_state")][:2 * count].cpu().view(count, 2).tolist()
-    return [(int(n), bool(done)) for n, done in state]
+    state = _sample_buffers[(device, "job_state")][:4 * count].cpu().view(count, 4).tolist()
+    return [(int(n), bool(done)) for n, done, _, _ in state]
 
 
 def sample(logits: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
