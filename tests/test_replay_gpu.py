@@ -216,3 +216,39 @@ def test_prepared_steps_and_tokens_from_the_device(model_folders, cuda_device, d
     runner.step(fresh, stale)                                       # ignored: described afresh
     with pytest.raises(InvalidArgumentError, match="still holds"):
         runner.step(fresh, stale, device_tokens=torch.zeros(3, dtype=torch.int32, device=cuda_device))
+
+
+def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeypatch):
+    """Decode steps of a few tokens run as fused chains of a layer's products.  A product the chain
+    kernel refuses (its input too long for shared memory, on a large model) runs as kernels of its
+    own between two chains: here the down projections are refused by hand.  Whole chains, partial
+    chains and no chains all agree with the plain implementation."""
+    from zephyr_b200.engine.replay import TraceReplayer
+    from zephyr_b200.kernels import ops
+
+    for name in ("B", "C"):
+        folder = model_folders(name, "bfloat16")
+        config = TINY[name]["config"]
+        requests = {f"r{i}": random_tokens(config["vocab_size"], 30 + 5 * i, seed=900 + i) for i in range(3)}
+        steps = trace_mixed(requests, seed=11, tail=20)
+        for mode in ("whole", "partial", "off"):
+            with monkeypatch.context() as patch:
+                refused = []
+                if mode == "partial":
+                    real = ops.fused_chain_stage_supported
+
+                    def picky(tokens, w, normed_input, swiglu):
+                        if tuple(w.shape) == (config["hidden_size"], config["intermediate_size"]):      # a down projection
+                            refused.append(tokens)
+                            return False
+                        return real(tokens, w, normed_input, swiglu)
+                    patch.setattr(ops, "fused_chain_stage_supported", picky)
+                replayer = TraceReplayer(folder, "bfloat16", peak_tokens(steps), page_size=TINY[name]["page_size"], max_requests=4)
+                chains = replayer.runner.model.chains
+                assert chains is not None and chains.supports(3)
+                replayer.runner.model.use_chains = mode != "off"
+                outputs = {s["step"]: replayer.step(s) for s in steps}
+                assert (mode == "partial") == bool(refused)
+            rows = collect(steps, {k: v for k, v in outputs.items() if v is not None})
+            first, worst, where = first_mismatch(rows, requests, folder, "bfloat16")
+            assert first is None, f"{name} {mode}: {first}; worst {worst:.3e} at {where}"

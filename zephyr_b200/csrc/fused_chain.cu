@@ -79,6 +79,8 @@ struct ChainArgs {
   int tiled[CH_MAX_STAGES];
   ChainStage stage[CH_MAX_STAGES];
   int n_stages, M, ring_shift, xs_row_bytes;      // the ring holds 1 << ring_shift slots
+  __nv_bfloat16* xn;                 // null, or room for 16 rows of the longest normalised input: where long rows are
+                                     // normalised once for all CTAs
   int* sync;                         // [0] barrier arrivals, [1] CTAs done; zero on entry and on exit
   int* status;
   int* trace;                        // null, or [CTA][stage][4] ints: the global timer (ns, low 32 bits) at the stage's
@@ -221,6 +223,42 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
   // the barrier's counters are earlier kernels' business until this returns.
   wait_for_prior_grids();
   let_dependents_launch();
+  // The barrier across the grid.  The CTA's barrier orders its threads' stores before thread 0,
+  // whose arrival is a release at device scope; its polls are acquires, and the CTA's second
+  // barrier hands what they saw on to the other threads.
+  auto grid_barrier = [&](int where) {
+    ++barriers;
+    chain_consumer_barrier();
+    if (ctid == 0) {
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;\n" ::"l"(&a.sync[0]) : "memory");
+      const int target = barriers * ctas;
+      bool ok = !abort_flag;
+      for (int polls = 0; ok && load_acquire(&a.sync[0]) < target; ++polls)
+        if (polls > CH_WAIT_LIMIT || ((polls & 63) == 63 && (abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0)))
+          ok = false;
+      if (!ok) {
+        report(a.status, STATUS_BARRIER_TIMEOUT, where, cta);
+        abort_flag = 1;
+      }
+    }
+    chain_consumer_barrier();
+    failed = failed || abort_flag != 0;
+  };
+  // The stage's input as it lies in global memory: one bulk copy per token row.
+  auto fetch_rows = [&](const __nv_bfloat16* src, long long ld, int K, int s) {
+    if (ctid < M) {
+      fence_proxy_async();
+      bulk_copy_g2s(xs + static_cast<size_t>(ctid) * a.xs_row_bytes, src + static_cast<size_t>(ctid) * ld,
+                    static_cast<unsigned>(K) * 2u, xfull);
+    }
+    if (ctid == 0) mbar_arrive_expect_tx(xfull, static_cast<unsigned>(M) * static_cast<unsigned>(K) * 2u);
+    if (!failed && !wait(xfull, x_uses & 1)) {
+      if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, -20 - s, cta);
+      abort_flag = 1;
+      failed = true;
+    }
+    ++x_uses;
+  };
   for (int s = 0; s < a.n_stages; ++s) {
     const ChainStage& st = a.stage[s];
     const StagePlan p = plans[s];
@@ -229,19 +267,59 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
 
     // ---- the stage's input, [M, K] bfloat16 in shared memory
     if (st.prologue == PROLOGUE_NONE) {
-      // As given: one bulk copy per token row.
-      if (ctid < M) {
-        fence_proxy_async();
-        bulk_copy_g2s(xs + static_cast<size_t>(ctid) * a.xs_row_bytes, st.x + static_cast<size_t>(ctid) * st.ldx,
-                      static_cast<unsigned>(K) * 2u, xfull);
+      fetch_rows(st.x, st.ldx, K, s);
+    } else if (K > 4 * 256 && a.xn != nullptr) {
+      // A long row is normalised once, by the CTA of its number with all its warps, and fetched
+      // by everybody after one more barrier across the grid: 148 CTAs each normalising all rows of
+      // 4096 took 10 us a stage (the same 128 KB asked of the L2 by every SM, four rounds of it).
+      if (cta < M) {
+        const int m = cta;
+        const __nv_bfloat16* res = st.residual_in + static_cast<size_t>(m) * K;
+        const __nv_bfloat16* del = st.prologue == PROLOGUE_ADD_NORM ? st.delta + static_cast<size_t>(m) * st.ldd : nullptr;
+        __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(xs + static_cast<size_t>(m) * a.xs_row_bytes);
+        float ss = 0.0f;
+        for (int i = ctid * 8; i < K; i += CH_CONSUMERS * 32 * 8) {
+          uint4 rv = __ldcg(reinterpret_cast<const uint4*>(res + i));
+          __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&rv);
+          if (del != nullptr) {
+            const uint4 dv = __ldcg(reinterpret_cast<const uint4*>(del + i));
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 rf = __bfloat1622float2(r2[e]), df = __bfloat1622float2(d2[e]);
+              r2[e] = __floats2bfloat162_rn(rf.x + df.x, rf.y + df.y);
+            }
+            *reinterpret_cast<uint4*>(st.residual_out + static_cast<size_t>(m) * K + i) = rv;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 rf = __bfloat1622float2(r2[e]);
+            ss += rf.x * rf.x + rf.y * rf.y;
+          }
+          *reinterpret_cast<uint4*>(staged + i) = rv;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        chain_consumer_barrier();
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < CH_CONSUMERS; ++w) total += red[w];
+        const float inv = rsqrtf(total / static_cast<float>(K) + st.eps);
+        for (int i = ctid * 8; i < K; i += CH_CONSUMERS * 32 * 8) {       // each thread meets its own elements again
+          uint4 rv = *reinterpret_cast<const uint4*>(staged + i);
+          __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 rf = __bfloat1622float2(r2[e]);
+            r2[e] = __floats2bfloat162_rn(rf.x * inv * load_scale(st.norm_w, st.norm_w_dtype, i + 2 * e),
+                                          rf.y * inv * load_scale(st.norm_w, st.norm_w_dtype, i + 2 * e + 1));
+          }
+          *reinterpret_cast<uint4*>(a.xn + static_cast<size_t>(m) * K + i) = rv;
+        }
+        fence_proxy_async();        // the row's place in shared memory is about to be filled by a bulk copy
       }
-      if (ctid == 0) mbar_arrive_expect_tx(xfull, static_cast<unsigned>(M) * static_cast<unsigned>(K) * 2u);
-      if (!failed && !wait(xfull, x_uses & 1)) {
-        if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, -20 - s, cta);
-        abort_flag = 1;
-        failed = true;
-      }
-      ++x_uses;
+      grid_barrier(-30 - s);
+      fetch_rows(a.xn, K, K, s);
     } else {
       // Normalised rows, each warp its own: the (new) residual goes to shared memory as it is and is
       // scaled in place once the row's sum of squares is known.  All of a row's loads are in flight
@@ -458,27 +536,7 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
     }
     if (tracing) trace[4 * s + 2] = now();
 
-    if (s + 1 < a.n_stages) {
-      // The barrier across the grid.  The CTA's barrier orders its threads' stores before thread 0,
-      // whose arrival is a release at device scope; its polls are acquires, and the CTA's second
-      // barrier hands what they saw on to the other threads.
-      ++barriers;
-      chain_consumer_barrier();
-      if (ctid == 0) {
-        asm volatile("red.release.gpu.global.add.s32 [%0], 1;\n" ::"l"(&a.sync[0]) : "memory");
-        const int target = barriers * ctas;
-        bool ok = !abort_flag;
-        for (int polls = 0; ok && load_acquire(&a.sync[0]) < target; ++polls)
-          if (polls > CH_WAIT_LIMIT || ((polls & 63) == 63 && (abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0)))
-            ok = false;
-        if (!ok) {
-          report(a.status, STATUS_BARRIER_TIMEOUT, s, cta);
-          abort_flag = 1;
-        }
-      }
-      chain_consumer_barrier();
-      failed = failed || abort_flag != 0;
-    }
+    if (s + 1 < a.n_stages) grid_barrier(s);
     if (tracing) trace[4 * s + 3] = now();
   }
 
@@ -571,9 +629,12 @@ ZB_API int zb_fused_chain_grid() {
 
 // `trace`: null, or zb_fused_chain_grid() * n_stages * 4 ints on the device that receive every CTA's
 // timeline (see ChainArgs).
+// `xn`: null, or 16-byte aligned room on the device for 16 rows of the longest K among the stages with
+// a norm (long rows are normalised there once for all CTAs; without it every CTA normalises them).
 // Runs `n_stages` stages (an array of ChainStage on the host) for M tokens.  `sync`: two ints on the
 // device, zero on entry, left zero.  The launch is cooperative: one CTA per SM.
-ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, int* status, int* trace, void* stream) {
+ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, int* status, int* trace, void* xn,
+                          void* stream) {
   if (stages == nullptr || n_stages < 1 || n_stages > CH_MAX_STAGES || sync == nullptr) return ERR_BAD_ARGUMENT;
   static ChainArgs a;         // large; every field that a launch reads is set below
   static std::mutex launch_mutex;
@@ -606,6 +667,7 @@ ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, in
   a.sync = sync;
   a.status = status;
   a.trace = trace;
+  a.xn = reinterpret_cast<uintptr_t>(xn) % 16 == 0 ? static_cast<__nv_bfloat16*>(xn) : nullptr;
   const int xs_rows = M <= 8 ? 8 : 16;
   a.xs_row_bytes = xs_k * 2 + CH_PAD;
   int slots = CH_MIN_SLOTS;

@@ -85,7 +85,7 @@ _SIGNATURES = {
     "zb_fused_chain_max_stages": [],
     "zb_fused_chain_grid": [],
     "zb_set_dependent_launch": [c_int],
-    "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_sample_chunks": [c_int],
     "zb_sample": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -629,6 +629,7 @@ def fused_chain_max_stages() -> int:
 
 # The arrival counters of the chain kernel's barrier, per device: zero between launches.
 _chain_sync: dict[torch.device, torch.Tensor] = {}
+_chain_rows: dict[torch.device, torch.Tensor] = {}
 
 
 def set_dependent_launch(enabled: bool) -> bool:
@@ -685,8 +686,13 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
         _cuda(trace)
         _require(trace.dtype == torch.int32 and trace.is_contiguous()
                  and trace.numel() >= 4 * len(stages) * fused_chain_grid(), "trace must be int32 [fused_chain_grid(), stages, 4]")
+    # Room for the rows of a long normalised input, which the kernel normalises once for all CTAs.
+    longest = max((st.w.shape[1] for st in stages if st.norm_w is not None), default=0)
+    scratch = _chain_rows.get(device)
+    if longest and (scratch is None or scratch.numel() < FUSED_CHAIN_MAX_TOKENS * longest):
+        scratch = _chain_rows[device] = torch.empty(FUSED_CHAIN_MAX_TOKENS * longest, dtype=torch.bfloat16, device=device)
     _check(library().zb_fused_chain(ctypes.addressof(packed), len(stages), int(tokens), _ptr(sync), _ptr(status),
-                                    _ptr(trace), _stream()), "fused_chain")
+                                    _ptr(trace), _ptr(scratch) if longest else None, _stream()), "fused_chain")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:

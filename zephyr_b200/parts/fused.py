@@ -48,6 +48,7 @@ class DecodeChains:
         self.plans = list(plans)
         self.run_order = list(run_order)
         self.hidden = hidden
+        self._supported: dict[int, bool] = {}       # tokens -> whether steps of that size take this path
 
     @classmethod
     def build(cls, layers: Sequence[object], run_order: Sequence[LayerCall], hidden: int,
@@ -66,18 +67,50 @@ class DecodeChains:
         return cls(plans, run_order, hidden)
 
     def supports(self, tokens: int) -> bool:
-        """True if every product of every layer can be a stage for this many tokens."""
+        """True if a step of this many tokens takes this path: every product of every layer can be a
+        stage of a chain, or at least run as a product of its own beside the chains (a stage whose
+        input does not fit beside the weight ring in shared memory: K = 12288 at 8 tokens)."""
         if not 1 <= tokens <= ops.FUSED_CHAIN_MAX_TOKENS:
             return False
-        for call in self.run_order:
-            plan = self.plans[call.layer]
-            w_in, w_out = plan.mixer.projections(call)
-            if not (ops.fused_chain_stage_supported(tokens, w_in, True, False)
-                    and ops.fused_chain_stage_supported(tokens, w_out, False, False)
-                    and ops.fused_chain_stage_supported(tokens, plan.w_gate_up, True, True)
-                    and ops.fused_chain_stage_supported(tokens, plan.w_down, False, False)):
-                return False
-        return True
+        known = self._supported.get(tokens)
+        if known is None:
+            known = True
+            some_chain = False
+            probe = torch.empty((tokens, 8), dtype=torch.bfloat16, device=self.plans[0].w_down.device)
+            for call in self.run_order:
+                plan = self.plans[call.layer]
+                w_in, w_out = plan.mixer.projections(call)
+                for w, normed, swiglu in ((w_in, True, False), (w_out, False, False), (plan.w_gate_up, True, True),
+                                          (plan.w_down, False, False)):
+                    if ops.fused_chain_stage_supported(tokens, w, normed, swiglu):
+                        some_chain = True
+                    elif not ops.gemm_small_supported(probe.new_empty((tokens, w.shape[1])), w):
+                        known = False
+            known = known and some_chain
+            self._supported[tokens] = known
+        return known
+
+    def _run(self, stages: list, tokens: int, status: torch.Tensor) -> None:
+        """The stages in order: runs of stages the chain kernel takes as one launch each, the others
+        as kernels of their own (norm, product, activation) that leave the same tensors behind."""
+        run: list = []
+        for stage in stages:
+            if ops.fused_chain_stage_supported(tokens, stage.w, stage.norm_w is not None, stage.swiglu):
+                run.append(stage)
+                continue
+            if run:
+                ops.fused_chain(run, tokens, status)
+                run = []
+            if stage.norm_w is None:
+                x = stage.x
+            elif stage.delta is None:
+                x = ops.rmsnorm(stage.residual_in, stage.norm_w, stage.eps)
+            else:
+                stage.residual_out.copy_(stage.residual_in)
+                x = ops.add_rmsnorm(stage.residual_out, stage.delta, stage.norm_w, stage.eps)
+            stage.y.copy_(ops.gemm_small(x, stage.w, swiglu=stage.swiglu))
+        if run:
+            ops.fused_chain(run, tokens, status)
 
     def forward(self, hidden: torch.Tensor, ctx) -> tuple[torch.Tensor, torch.Tensor]:
         """Runs all layers on ``hidden`` [T, H] (the embeddings).  Returns (residual, pending): the
@@ -91,8 +124,8 @@ class DecodeChains:
         plan = self.plans[first.layer]
         w_in, _ = plan.mixer.projections(first)
         projected = new(w_in.shape[0])
-        ops.fused_chain([ops.ChainStage(w=w_in, y=projected, residual_in=hidden, norm_w=plan.mixer_norm[0],
-                                        eps=plan.mixer_norm[1])], T, ctx.status)
+        self._run([ops.ChainStage(w=w_in, y=projected, residual_in=hidden, norm_w=plan.mixer_norm[0],
+                                  eps=plan.mixer_norm[1])], T, ctx.status)
         for index, call in enumerate(self.run_order):
             plan = self.plans[call.layer]
             _, w_out = plan.mixer.projections(call)
@@ -106,7 +139,7 @@ class DecodeChains:
                 ops.ChainStage(w=plan.w_down, y=down, x=act),
             ]
             if index + 1 == len(self.run_order):
-                ops.fused_chain(stages, T, ctx.status)
+                self._run(stages, T, ctx.status)
                 return residuals[after_mixer], down
             following = self.run_order[index + 1]
             next_plan = self.plans[following.layer]
@@ -115,6 +148,6 @@ class DecodeChains:
             stages.append(ops.ChainStage(w=w_next, y=projected, residual_in=residuals[after_mixer],
                                          residual_out=residuals[after_ffn], delta=down, norm_w=next_plan.mixer_norm[0],
                                          eps=next_plan.mixer_norm[1]))
-            ops.fused_chain(stages, T, ctx.status)
+            self._run(stages, T, ctx.status)
             current = after_ffn
         raise AssertionError("unreachable: the run order is not empty")
