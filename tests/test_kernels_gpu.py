@@ -600,7 +600,9 @@ def _plain_rmsnorm(x, w, eps):
 
 
 @pytest.mark.parametrize("M,d,q,ffn,qkv", [(1, 1024, 2048, 3072, 4096), (8, 1024, 2048, 3072, 4096), (16, 320, 256, 880, 384),
-                                           (5, 2056, 1032, 4112, 136), (13, 64, 2304, 48, 8)])
+                                           (5, 2056, 1032, 4112, 136), (13, 64, 2304, 48, 8),
+                                           # long rows: normalised once, by the CTA of the row's number
+                                           (8, 4096, 512, 264, 136), (3, 4608, 128, 136, 72)])
 def test_fused_chain_matches_plain(ops, cuda_device, M, d, q, ffn, qkv):
     """A layer's tail as one chain: output projection; residual add, norm, gate/up with silu * up;
     down projection; residual add, norm, the next projection.  Against float64 products of the same
