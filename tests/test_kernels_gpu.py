@@ -562,6 +562,47 @@ def test_paged_decode_split(ops, cuda_device, nh, nkv, hd, page, window, split_s
         cursor += n
 
 
+@pytest.mark.parametrize("split_size", [None, 0, 64])
+@pytest.mark.parametrize("nh,nkv,hd,page,window,norms,rotate", [
+    (16, 8, 128, 16, 0, True, True), (4, 2, 32, 8, 0, True, True), (12, 3, 96, 32, 0, False, True),
+    (8, 8, 64, 4, 0, True, False), (16, 8, 128, 16, 300, True, True), (6, 2, 64, 64, 0, False, False)])
+def test_paged_decode_with_the_position_encoding_inside(ops, cuda_device, nh, nkv, hd, page, window, norms, rotate, split_size):
+    """Norms, rotation, the cache write of the new key and value and the attention in one kernel give
+    what the two kernels give one after the other, bit for bit: the attention's result and the
+    cache.  Contexts around tile, page and split edges; the new position is a page's first, a
+    page's last, a tile's first and so on."""
+    dtype = torch.bfloat16
+    ctx = [0, 15, 16, 31, 32, 63, 255, 256, 600, 1029]
+    R = len(ctx)
+    _, cache, meta, _, _, _ = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, [1] * R, ctx, 700)
+    cache = torch.nan_to_num(cache, nan=0.0)          # rows nobody wrote compare equal
+    width = (nh + 2 * nkv) * hd
+    qkv = rand((R, width + 16), dtype, cuda_device, 701, 2.0)[:, :width]        # rows further apart than they are long
+    q_norm = (1 + rand((hd,), torch.float32, cuda_device, 702, 0.1)).to(dtype) if norms else None
+    k_norm = (1 + rand((hd,), torch.float32, cuda_device, 703, 0.1)).to(dtype) if norms else None
+    positions = torch.arange(1100, dtype=torch.float32, device=cuda_device)[:, None]
+    freq = 1.0 / (10000.0 ** (torch.arange(hd // 2, dtype=torch.float32, device=cuda_device) / (hd // 2)))
+    cos, sin = (torch.cos(positions * freq).contiguous(), torch.sin(positions * freq).contiguous()) if rotate else (None, None)
+    rows = torch.arange(R, dtype=torch.int32, device=cuda_device)
+    scale, eps = 1 / math.sqrt(hd), 1e-6
+    status = ops.new_status(cuda_device)
+
+    two_cache = cache.clone()
+    q = ops.qk_norm_rope_cache(qkv, nh, nkv, hd, q_norm, k_norm, eps, cos, sin, meta["row_ctx"], rows, two_cache,
+                               meta["table"], status)
+    two = torch.empty_like(q)
+    ops.paged_decode(q, two_cache, meta["table"], rows, meta["row_q_start"], meta["row_ctx"], max(ctx) + 1, nh, nkv, hd,
+                     window, scale, status, out=two, split_size=split_size)
+    one_cache = cache.clone()
+    one = torch.full_like(q, float("nan"))
+    for _ in range(2):          # the second call finds the counters as the first left them, and the cache written
+        ops.paged_decode_fused(qkv, one_cache, meta["table"], rows, meta["row_q_start"], meta["row_ctx"], max(ctx) + 1,
+                               nh, nkv, hd, window, scale, q_norm, k_norm, eps, cos, sin, status, one, split_size=split_size)
+    ops.check_status(status)
+    assert torch.equal(one_cache, two_cache)
+    assert torch.equal(one, two)
+
+
 def test_paged_decode_far_key(ops, cuda_device):
     nh, nkv, hd, page = 16, 8, 128, 16
     for key in (2, 255, 256, 511, 900):

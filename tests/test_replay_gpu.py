@@ -222,7 +222,8 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
     """Decode steps of a few tokens run as fused chains of a layer's products.  A product the chain
     kernel refuses (its input too long for shared memory, on a large model) runs as kernels of its
     own between two chains: here the down projections are refused by hand.  Whole chains, partial
-    chains and no chains all agree with the plain implementation."""
+    chains and no chains all agree with the plain implementation, and so does the decode attention
+    that does the position encoding and the cache write itself (the engine uses it for large batches)."""
     from zephyr_b200.engine.replay import TraceReplayer
     from zephyr_b200.kernels import ops
 
@@ -231,7 +232,7 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
         config = TINY[name]["config"]
         requests = {f"r{i}": random_tokens(config["vocab_size"], 30 + 5 * i, seed=900 + i) for i in range(3)}
         steps = trace_mixed(requests, seed=11, tail=20)
-        for mode in ("whole", "partial", "off"):
+        for mode in ("whole", "partial", "off", "one kernel"):
             with monkeypatch.context() as patch:
                 refused = []
                 if mode == "partial":
@@ -247,6 +248,9 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
                 chains = replayer.runner.model.chains
                 assert chains is not None and chains.supports(3)
                 replayer.runner.model.use_chains = mode != "off"
+                if mode == "one kernel":        # position encoding inside the decode attention, whatever the batch
+                    for block in replayer.runner.model.layers:
+                        block.mixer.fuse_decode_rows = 1
                 outputs = {s["step"]: replayer.step(s) for s in steps}
                 assert (mode == "partial") == bool(refused)
             rows = collect(steps, {k: v for k, v in outputs.items() if v is not None})

@@ -56,6 +56,20 @@ struct DecodeArgs {
   int nh, nkv, window, split_size, max_splits, ring_slots, item_pages;
   float scale_log2;              // scale * log2(e)
   int* status;
+  // Position encoding inside this kernel (`qkv` null: off; q then holds finished queries and the
+  // cache the newest keys and values).  With it, q is not read: a request's new token lies raw in
+  // qkv (query heads, key heads, value heads); every CTA norms and rotates the queries of its own
+  // items, and the consumer warp that meets the tile of a row's newest position norms and rotates
+  // that key, puts it and the value into the tile in shared memory and into the cache.
+  const __nv_bfloat16* qkv;      // [T, qkv_stride]
+  long long qkv_stride;
+  const void* q_norm_w;          // [hd] or null
+  const void* k_norm_w;
+  int norm_w_dtype;
+  float norm_eps;
+  const float* cos_table;        // [max_positions, hd / 2] or null (no rotation)
+  const float* sin_table;
+  int max_positions;
   int* trace;                    // null, or [CTA][8] ints: the global timer (ns, low 32 bits) at the CTA's start, after
                                  // the wait for earlier kernels, when its first tile had landed, after its last tile,
                                  // at its end; then its items and its tiles, and when its last arrival among a
@@ -180,6 +194,48 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One head of a new token by one warp, as zb_qk_norm_rope_cache does it (rope_cache.cu: the same
+// sums, factors and roundings): lane l owns the adjacent elements 2l, 2l + 1 of the head's first half
+// and their partners in the second.  `norm_w` null: no norm; `rotate` false: no rotation (a value).
+// Returns false for lanes that own nothing (head sizes below 128).
+template <int HD>
+__device__ __forceinline__ bool new_token_head(const __nv_bfloat16* src, const void* norm_w, int w_dtype, float eps,
+                                               const float* cos_row, const float* sin_row, float (&x)[2], float (&y)[2]) {
+  constexpr int HALF = HD / 2;
+  const int lane = threadIdx.x & 31, i = 2 * lane;
+  const bool mine = i < HALF;
+  x[0] = x[1] = y[0] = y[1] = 0.0f;
+  float ss = 0.0f;
+  if (mine) {
+    const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i));
+    const float2 yv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i + HALF));
+    x[0] = xv.x; x[1] = xv.y; y[0] = yv.x; y[1] = yv.y;
+    ss = x[0] * x[0] + x[1] * x[1] + y[0] * y[0] + y[1] * y[1];
+  }
+  if (norm_w != nullptr) {
+    const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(HD) + eps);
+    if (mine) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        x[u] *= inv * load_scale(norm_w, w_dtype, i + u);
+        y[u] *= inv * load_scale(norm_w, w_dtype, i + u + HALF);
+      }
+    }
+  }
+  if (cos_row != nullptr && mine) {
+    const float2 cv = *reinterpret_cast<const float2*>(cos_row + i), sv = *reinterpret_cast<const float2*>(sin_row + i);
+    const float cs[2] = {cv.x, cv.y}, sn[2] = {sv.x, sv.y};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float xr = x[u] * cs[u] - y[u] * sn[u];
+      const float yr = y[u] * cs[u] + x[u] * sn[u];
+      x[u] = xr;
+      y[u] = yr;
+    }
+  }
+  return mine;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 paged_decode_kernel(const DecodeArgs a) {
@@ -261,6 +317,7 @@ paged_decode_kernel(const DecodeArgs a) {
   const int per_range = a.split_size == 0 ? max(1, (prefix[a.n_rows] + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) : 0;
   const int page_size = 1 << a.page_shift;
   const long long page_stride = 2LL * a.nkv * page_size * HD;
+  const bool fused = a.qkv != nullptr;       // the new tokens' position encoding happens in this kernel
 
   if (warp >= DEC_CONSUMERS) {
     // ------------------------------------------------------------------------ the producers
@@ -274,12 +331,71 @@ paged_decode_kernel(const DecodeArgs a) {
     DecodeItem it;
     bool waited = false;               // for the earlier kernels
     bool q_pending = false;            // the first producer: the item's queries are still to be fetched
+    // With the position encoding inside the kernel the producers do its work, off the consumers'
+    // path: the first producer forms an item's queries from the raw projection (the consumers find
+    // them in the query buffer as if they had been copied there), and the producer whose turn it
+    // is to copy the tile of a row's newest position first forms that key, writes it and the value
+    // into the cache, and then copies the tile like any other.
+    auto rotation_rows = [&](const float*& cos_row, const float*& sin_row) {
+      const int pos = it.ctx_total - 1;
+      const bool ok = a.cos_table != nullptr && pos >= 0 && pos < a.max_positions;
+      if (a.cos_table != nullptr && !ok && lane == 0) report(a.status, STATUS_POSITION_OUT_OF_RANGE, pos, it.row);
+      cos_row = ok ? a.cos_table + static_cast<size_t>(pos) * (HD / 2) : nullptr;
+      sin_row = ok ? a.sin_table + static_cast<size_t>(pos) * (HD / 2) : nullptr;
+    };
     auto fetch_queries = [&](int qb) {
+      if (fused) {
+        const __nv_bfloat16* token = a.qkv + static_cast<size_t>(a.row_q_start[it.row]) * a.qkv_stride;
+        const float *cos_row, *sin_row;
+        rotation_rows(cos_row, sin_row);
+        for (int h = 0; h < g; ++h) {
+          float x[2], y[2];
+          if (new_token_head<HD>(token + static_cast<size_t>(it.kvh * g + h) * HD, a.q_norm_w, a.norm_w_dtype, a.norm_eps,
+                                 cos_row, sin_row, x, y)) {
+            __nv_bfloat16* dst = qbuf + (qb * 16 + h) * KROW + 2 * lane;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(x[0], x[1]);
+            *reinterpret_cast<__nv_bfloat162*>(dst + HD / 2) = __floats2bfloat162_rn(y[0], y[1]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&qfull[qb]);        // a release: the consumers' wait sees the stores
+        return;
+      }
       if (lane == 0) mbar_arrive_expect_tx(&qfull[qb], static_cast<unsigned>(g) * ROW_BYTES);
       if (lane < g)
         bulk_copy_g2s(qbuf + (qb * 16 + lane) * KROW,
                       a.q + (static_cast<size_t>(a.row_q_start[it.row]) * a.nh + static_cast<size_t>(it.kvh) * g + lane) * HD,
                       ROW_BYTES, &qfull[qb]);
+    };
+    // The new token's key and value into the cache (their row of the page, chunks permuted as
+    // every cache row's are).
+    auto write_newest = [&]() {
+      const int pos = it.ctx_total - 1;
+      const int block = pos >> a.page_shift;
+      const int page = block < a.max_blocks ? a.block_table[static_cast<size_t>(it.row) * a.max_blocks + block] : -1;
+      if (page <= 0 || page >= a.num_pages) {
+        if (lane == 0) report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, it.row);
+        return;
+      }
+      const __nv_bfloat16* token = a.qkv + static_cast<size_t>(a.row_q_start[it.row]) * a.qkv_stride;
+      const float *cos_row, *sin_row;
+      rotation_rows(cos_row, sin_row);
+      __nv_bfloat16* key_row = const_cast<__nv_bfloat16*>(a.kv_cache) + page * page_stride +
+                               (static_cast<long long>(it.kvh) * page_size + (pos & (page_size - 1))) * HD;
+      const int lo = kv_element_index(2 * lane, pos, HD, sizeof(__nv_bfloat16));
+      const int hi = kv_element_index(2 * lane + HD / 2, pos, HD, sizeof(__nv_bfloat16));
+#pragma unroll
+      for (int kind = 0; kind < 2; ++kind) {              // the key, then the value
+        float x[2], y[2];
+        if (new_token_head<HD>(token + static_cast<size_t>(a.nh + kind * a.nkv + it.kvh) * HD, kind == 0 ? a.k_norm_w : nullptr,
+                               a.norm_w_dtype, a.norm_eps, kind == 0 ? cos_row : nullptr, kind == 0 ? sin_row : nullptr, x, y)) {
+          __nv_bfloat16* row = key_row + (kind == 0 ? 0 : static_cast<long long>(a.nkv) * page_size * HD);
+          *reinterpret_cast<__nv_bfloat162*>(row + lo) = __floats2bfloat162_rn(x[0], x[1]);
+          *reinterpret_cast<__nv_bfloat162*>(row + hi) = __floats2bfloat162_rn(y[0], y[1]);
+        }
+      }
+      __syncwarp();
+      fence_proxy_async();       // the tile's bulk copies, issued next by this warp, read these rows
     };
     while (next_item(a, prefix, per_range, walker, it)) {
       const int qb = item_seq & 1;
@@ -312,7 +428,8 @@ paged_decode_kernel(const DecodeArgs a) {
       for (int t = 0; t < it.n_tiles; ++t, ++tile_seq) {
         if (tile_seq % DEC_PRODUCERS != me) continue;
         const int slot = tile_seq % R, filling = tile_seq / R;
-        // The tile that holds the row's newest position was written by an earlier kernel of this step.
+        // The tile that holds the row's newest position was written by an earlier kernel of this step,
+        // or is written here from that kernel's projection.
         const bool newest = it.first_tile + (t + 1) * DEC_TILE >= it.ctx_total;
         if (!waited && (newest || (q_pending && filling > 0))) {
           wait_for_prior_grids();
@@ -322,6 +439,7 @@ paged_decode_kernel(const DecodeArgs a) {
           fetch_queries(qb);
           q_pending = false;
         }
+        if (fused && newest) write_newest();
         bool released = consumed[slot] >= filling;
         for (int i = 0; !released && i < DEC_WAIT_LIMIT && !abort_flag; ++i) released = consumed[slot] >= filling;
         if (!released || !wait(&empty[slot], (filling & 1) ^ 1)) {
@@ -749,11 +867,25 @@ ZB_API long long zb_paged_decode_balanced_scratch_floats(int nh, int nkv, int hd
 //     zb_paged_decode_scratch_floats(...) floats (contents irrelevant).
 //   split_size == 0: the tiles of all rows are spread evenly over the CTAs; max_splits >=
 //     ceil((longest context + 1) / 32); `scratch` holds zb_paged_decode_balanced_scratch_floats(...).
-ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
-                           int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
-                           const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
-                           float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
-                           void* stream) {
+namespace zb {
+struct DecodeFusion {            // position encoding inside the kernel (see DecodeArgs)
+  const void* qkv;
+  long long qkv_stride;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  int norm_w_dtype;
+  float norm_eps;
+  const float* cos_table;
+  const float* sin_table;
+  int max_positions;
+};
+}  // namespace zb
+
+static int paged_decode_entry(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                              int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
+                              const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
+                              float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
+                              const DecodeFusion* fusion, void* stream) {
   if (n_rows < 0 || max_splits <= 0 || split_size < 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0 ||
       counters == nullptr)
     return ERR_BAD_ARGUMENT;
@@ -775,6 +907,28 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
   a.n_rows = n_rows;
   a.nh = nh; a.nkv = nkv; a.window = window; a.split_size = split_size; a.max_splits = max_splits;
   a.trace = decode_trace();
+  a.qkv = nullptr;
+  a.qkv_stride = 0;
+  a.q_norm_w = a.k_norm_w = nullptr;
+  a.norm_w_dtype = DTYPE_BF16;
+  a.norm_eps = 0.0f;
+  a.cos_table = a.sin_table = nullptr;
+  a.max_positions = 0;
+  if (fusion != nullptr) {
+    if (fusion->qkv == nullptr || reinterpret_cast<uintptr_t>(fusion->qkv) % 4 != 0 || fusion->qkv_stride % 2 != 0 ||
+        fusion->qkv_stride < static_cast<long long>(nh + 2 * nkv) * hd || (fusion->cos_table == nullptr) != (fusion->sin_table == nullptr) ||
+        reinterpret_cast<uintptr_t>(fusion->cos_table) % 8 != 0 || reinterpret_cast<uintptr_t>(fusion->sin_table) % 8 != 0)
+      return ERR_BAD_ARGUMENT;
+    a.qkv = static_cast<const __nv_bfloat16*>(fusion->qkv);
+    a.qkv_stride = fusion->qkv_stride;
+    a.q_norm_w = fusion->q_norm_w;
+    a.k_norm_w = fusion->k_norm_w;
+    a.norm_w_dtype = fusion->norm_w_dtype;
+    a.norm_eps = fusion->norm_eps;
+    a.cos_table = fusion->cos_table;
+    a.sin_table = fusion->sin_table;
+    a.max_positions = fusion->max_positions;
+  }
   a.ring_slots = 0;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
@@ -785,6 +939,34 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
     case 96: return decode_launch<96>(a, s);
     default: return decode_launch<128>(a, s);
   }
+}
+
+ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                           int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
+                           const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
+                           float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
+                           void* stream) {
+  return paged_decode_entry(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
+                            row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, counters,
+                            status, nullptr, stream);
+}
+
+// The same with the new tokens' position encoding inside the kernel: `qkv` [T, qkv_stride] holds each
+// request's new token raw (query heads, key heads, value heads); per-head RMS norms of q and k
+// (scales may be null), the rotation by the tables (may be null) and the write of the new key and
+// value into the cache (`kv_cache` is written) happen here, and no kernel has to run between the
+// projection and this one.  For steps in which every request has exactly one new token.
+ZB_API int zb_paged_decode_fused(void* out, void* kv_cache, const int* block_table, int max_blocks, int page_size,
+                                 int num_pages, int num_rows, const int* rows, int n_rows, const int* row_q_start,
+                                 const int* row_ctx, int nh, int nkv, int hd, int window, float scale, int split_size,
+                                 int max_splits, float* scratch, int* counters, int* status, const void* qkv,
+                                 long long qkv_stride, const void* q_norm_w, const void* k_norm_w, int norm_w_dtype,
+                                 float norm_eps, const float* cos_table, const float* sin_table, int max_positions,
+                                 void* stream) {
+  const DecodeFusion fusion{qkv, qkv_stride, q_norm_w, k_norm_w, norm_w_dtype, norm_eps, cos_table, sin_table, max_positions};
+  return paged_decode_entry(out, out, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
+                            row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, counters,
+                            status, &fusion, stream);
 }
 
 // ------------------------------------------------------------------------------------------

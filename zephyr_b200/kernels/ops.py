@@ -67,6 +67,9 @@ _SIGNATURES = {
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p],
+    "zb_paged_decode_fused": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
     "zb_paged_decode_set_trace": [c_void_p],
     "zb_paged_prefill_tile_tokens": [],
     "zb_paged_prefill_supported": [c_int, c_int, c_int, c_int],
@@ -469,6 +472,53 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
         block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
         float(scale), int(split_size), max_splits, _ptr(scratch), _ptr(counters), _ptr(status), _stream()),
         "paged_decode")
+    return out
+
+
+def paged_decode_fused(qkv: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
+                       row_q_start: torch.Tensor, row_ctx: torch.Tensor, max_context: int, nh: int, nkv: int, hd: int,
+                       window: int, scale: float, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, eps: float,
+                       cos: torch.Tensor | None, sin: torch.Tensor | None, status: torch.Tensor, out: torch.Tensor,
+                       split_size: int | None = None) -> torch.Tensor:
+    """``qk_norm_rope_cache`` and ``paged_decode`` in one kernel, for steps in which every request
+    has exactly one new token: ``qkv`` [T, >= (nh + 2 nkv) hd] holds the new tokens raw; the per-head
+    norms, the rotation and the cache write of the new keys and values happen inside the attention
+    kernel (a row's new position is its ``row_ctx``), and ``out`` [T, nh hd] gets the attention's
+    result.  No kernel stands between the projection and the attention then."""
+    _cuda(qkv, kv_cache, block_table, rows, row_q_start, row_ctx, status, out, q_norm_w, k_norm_w, cos, sin)
+    _i32(block_table, rows, row_q_start, row_ctx)
+    T = qkv.shape[0]
+    _require(qkv.dim() == 2 and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] >= (nh + 2 * nkv) * hd
+             and qkv.stride(0) % 2 == 0, "qkv must be bfloat16 [T, (heads + 2*kv_heads)*head_dim] with unit inner stride")
+    _require(out.shape == (T, nh * hd) and out.dtype == torch.bfloat16 and out.is_contiguous(), "out must be [T, heads*head_dim]")
+    pages, page_size = _check_cache(kv_cache, nkv, hd, qkv.dtype)
+    w_code = 0
+    if q_norm_w is not None or k_norm_w is not None:
+        _require(q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype == k_norm_w.dtype,
+                 "q and k norm scales come together and share a type")
+        w_code = _scale_code(q_norm_w, hd)
+        _scale_code(k_norm_w, hd)
+    max_positions = 0
+    if cos is not None:
+        _require(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32
+                 and cos.shape == sin.shape and cos.dim() == 2 and cos.shape[1] == hd // 2
+                 and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be float32 [positions, head_dim/2]")
+        max_positions = cos.shape[0]
+    n_rows = rows.numel()
+    if split_size is None and n_rows * nkv * 4 <= _sm_count():
+        split_size = decode_split_size(n_rows, nkv, max_context)
+    if split_size is None or split_size == 0:
+        split_size, max_splits = 0, max(1, math.ceil(max_context / 32))
+        need = int(library().zb_paged_decode_balanced_scratch_floats(nh, nkv, hd))
+    else:
+        max_splits = max(1, math.ceil(max_context / split_size))
+        need = paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
+    scratch, counters = _decode_workspace(qkv.device, need, n_rows * nkv)
+    _check(library().zb_paged_decode_fused(
+        _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages, block_table.shape[0],
+        _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), int(split_size),
+        max_splits, _ptr(scratch), _ptr(counters), _ptr(status), _ptr(qkv), qkv.stride(0), _ptr(q_norm_w), _ptr(k_norm_w),
+        w_code, float(eps), _ptr(cos), _ptr(sin), max_positions, _stream()), "paged_decode_fused")
     return out
 
 
