@@ -21,6 +21,13 @@
 // key/value head) to finish, found with an atomic counter, merges the splits' partial results, so
 // no CTA ever waits for another and there is no second launch.
 //
+// The kernel is launched as a programmatic dependent of the kernel before it: its CTAs fill their
+// rings with keys and values of old positions while that kernel is still running, and wait for it
+// only before they touch what it wrote (the queries, a row's newest key and value).  Asked to, it
+// also does that kernel's work (zb_paged_decode_fused): the first producer warp forms an item's
+// queries from the raw projection (per-head RMS norm, rotation), and the producer whose turn it is
+// to copy the tile of a row's newest position first writes that key and value into the cache.
+//
 // Math as in attention_simt.cu (reference: src/attention/paged_decode.cu:169-352 for the split
 // scheme), except where that kernel is not exact: no epsilon is added to the denominator, and
 // partial results stay float32.  Probabilities are rounded to bfloat16 for the second product, as

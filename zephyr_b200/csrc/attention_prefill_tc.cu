@@ -1,30 +1,30 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores: tcgen05.mma
-// with both operands in shared memory and the accumulators in tensor memory (TMEM).
+// with the A operands (queries, probabilities) and the accumulators in tensor memory (TMEM) and the
+// B operands (keys, values) in shared memory.
 //
 // One CTA = up to 128 consecutive new tokens of one request x one query head, head size 128,
-// bfloat16.  Keys and values stream through a two-stage ring of 128-position tiles.  Roles:
-//   * four loader warps copy a tile's key and value rows from the cache pages (TMA tiled copies
-//     per page for tiles inside the context, 16-byte asynchronous copies at its edges).  A cache row's 16-byte chunks are stored permuted with the position
-//     (common.cuh: kv_swizzle); for rows of 256 bytes that permutation IS the 128-byte swizzle of
-//     the tensor core's canonical shared-memory layout, so a row is copied as it lies, its first
-//     128 bytes to the tile's first half (head dims 0..63), the rest to the second half;
+// bfloat16.  Keys and values stream through three stages each of 128-position tiles.  Roles:
+//   * four loader warps, two for the keys and two for the values, copy a tile's rows from the cache
+//     pages (TMA tiled copies per page for tiles inside the context, 16-byte asynchronous copies at
+//     its edges, where rows have to be zero).  A cache row's 16-byte chunks are stored permuted
+//     with the position (common.cuh: kv_swizzle); for rows of 256 bytes that permutation IS the
+//     128-byte swizzle of the tensor core's canonical shared-memory layout, so a row is copied as
+//     it lies, its first 128 bytes to the tile's first half (head dims 0..63), the rest to the
+//     second half;
 //   * one thread issues the products: S = Q K^T (M 128 queries, N 128 keys, eight steps of K = 16
-//     over the head dims; both operands K-major) into TMEM columns 0..127 or 128..255 by turns, and
-//     O += P V (A = the probabilities, K-major over the keys; B = the values as they lie, MN-major)
-//     into columns 256..383; S of the next tile is issued before the wait for this tile's
-//     probabilities, so the softmax runs beside the products; completion is reported to mbarriers
-//     by tcgen05.commit;
+//     over the head dims; Q from TMEM columns 384..447, two bfloat16 a column; the keys K-major)
+//     into TMEM columns 0..127 or 128..255 by turns, and O += P V (A = the probabilities, which
+//     the softmax leaves where their S lay; B = the values as they lie, MN-major) into columns
+//     256..383; S of the next tile is issued before the wait for this tile's probabilities, so the
+//     softmax runs beside the products; completion is reported to mbarriers by tcgen05.commit;
 //   * eight softmax warps own the 128 query rows, two threads a row (TMEM lane = row; one thread
 //     takes the first 64 columns of S and of O, the other the rest): they read their half of a row
-//     of S with tcgen05.ld, keep the running sum in float32 in base 2, write the probabilities as
-//     bfloat16 into shared memory in the canonical layout, and rescale O in TMEM when the row's
-//     maximum has grown by more than 2^8 since the value the row last rescaled to (the softmax does
-//     not care which shift it is given as long as it is given everywhere; the bound keeps exp2 far
-//     from overflow).  A row's two threads tell each other their largest score every tile, so both
-//     take the same decisions.  Two warps per scheduler because a row's work is a chain of
-//     latencies (tensor-memory reads, 128 exp2 on the special-function unit, conversions) that
-//     one warp cannot hide: the kernel's own timeline showed 1.28 us of softmax per tile against
-//     0.56 us of tensor work.
+//     of S with tcgen05.ld, keep the running sum in float32 in base 2, store the probabilities as
+//     bfloat16 pairs with tcgen05.st, and rescale O in TMEM when the row's maximum has grown by
+//     more than 2^8 since the value the row last rescaled to (the softmax does not care which
+//     shift it is given as long as it is given everywhere; the bound keeps exp2 far from
+//     overflow).  A row's two threads tell each other their largest score every tile, so both
+//     take the same decisions.
 // Math and masking as in attention_prefill.cu and attention_simt.cu (causal, lower-right aligned on
 // the cached context, optional window; probabilities rounded to bfloat16 for the second product;
 // reference: src/layer/paged_attention.cpp:118-296, deps/ttl/src/kernels/attention/attention.cu:58-170).
