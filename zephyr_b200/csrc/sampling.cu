@@ -631,6 +631,10 @@ sample_head_bins_kernel(const SortJob* __restrict__ jobs, const float* __restric
   }
   const double T = scaling_temperature(rows[r]);
   const float* x = logits + static_cast<size_t>(r) * row_stride;
+  // A row that needs few ranks (a small top-k, a report of a few tokens) aims at a shorter head:
+  // half as many keys to sort, and still four times what it needs with room for the guess's error.
+  const int needs = job.by_z ? rows[r].num_logprobs : rows[r].top_k;
+  const int aim = needs > 0 && needs <= HEAD_AIM / 8 ? HEAD_AIM / 2 : HEAD_AIM;
   for (int e = threadIdx.x; e < HEAD_BINS; e += ROW_THREADS) hist[e] = 0;
   if (threadIdx.x == 0) s_bins = 0;
   __syncthreads();
@@ -650,7 +654,7 @@ sample_head_bins_kernel(const SortJob* __restrict__ jobs, const float* __restric
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     run += counts[j];
-    if (run * stride <= HEAD_AIM) leading = threadIdx.x * PER + j + 1;
+    if (run * stride <= aim) leading = threadIdx.x * PER + j + 1;
   }
   if (leading > 0) atomicMax(&s_bins, leading);
   __syncthreads();
