@@ -36,6 +36,38 @@ SHAPES = {      # the layer sizes of the Qwen3 family members the benchmark name
                 intermediate_size=25600, vocab_size=151936, tie_word_embeddings=False),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def metric_name(args) -> str:
+    """One string for both arms: the driver divides their values only if the strings are equal."""
+    return f"decode tok/s @ batch {args.batch}, context {args.context} (Qwen3-{args.shape.upper()} shape)"
+
+
+def kernel_fractions(config, batch: int, context: int, peak: dict) -> tuple[dict, dict]:
+    """The step's dominant kernels alone, timed with CUDA events over rotating operands larger than L2
+    (``zephyr_b200.kernels.timing``): achieved bytes/s over the copy rate for the decode kernels,
+    FLOP/s over the library's burst rate for the prompt kernels.  A layer's share of the decode step
+    is its products (one fused chain) and its attention; the head comes once."""
+    from types import SimpleNamespace
+
+    from zephyr_b200.kernels import timing
+
+    base = dict(warmup=3, iters=20, heads=config.num_attention_heads, kv_heads=config.num_key_value_heads,
+                head_dim=config.head_dim, page_size=PAGE_SIZE, window=0, split=0, hidden=config.hidden_size,
+                ffn=config.intermediate_size)
+    chain = timing.fused_chain(SimpleNamespace(rows=batch, **base))
+    attention = timing.decode_attention(SimpleNamespace(batch=batch, context=context, **base))
+    head = timing.gemm_small(SimpleNamespace(rows=batch, n=config.vocab_size, k=config.hidden_size, swiglu=False,
+                                             float_out=True, **base))
+    hbm, tflops = peak["hbm_gbs"], peak["bf16_tflops"]
+    decode = {"layer_products": {"us": chain["us"], "frac": round(chain["gbs"] / hbm, 3)},
+              "decode_attention": {"us": attention["us"], "frac": round(attention["gbs"] / hbm, 3)},
+              "lm_head": {"us": head["us"], "frac": round(head["gbs"] / hbm, 3)}}
+    prompt_attention = timing.prefill_attention(SimpleNamespace(tokens=PREFILL_TOKENS, **base))
+    prompt_products = timing.products(SimpleNamespace(tokens=PREFILL_TOKENS, **base))
+    prefill = {"attention": {"us": prompt_attention["us"], "frac": round(prompt_attention["tflops"] / tflops, 3)},
+               "layer_products": {"us": prompt_products["us"], "frac": round(prompt_products["tflops"] / tflops, 3)}}
+    return decode, prefill
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 16
 
@@ -110,19 +142,23 @@ def build_engine(shape: str, layers: int | None, batch: int, context: int, dtype
     full_layers = sizes["num_hidden_layers"]
     if layers:
         sizes["num_hidden_layers"] = layers
-    config = Qwen3Config(max_position_embeddings=max(context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0,
-                         layer_windows=tuple(0 for _ in range(sizes["num_hidden_layers"])), **sizes)
+    config = Qwen3Config(max_position_embeddings=max(context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0, **sizes)
     spec = config.to_model_spec()
     store = RandomWeights(expected_weights(spec), seed=0, dtype=getattr(torch, dtype), device="cuda")
-    pages = batch * (-(-context // PAGE_SIZE) + 1) + 1
-    engine = Engine(None, dtype=dtype, model_config=config, weights=store,
-                    kv_cache=KvCacheOptions(block_size=PAGE_SIZE, num_blocks=pages),
+    # The pool is sized by the engine from the memory that is left after the weights and a profiled
+    # step; it never holds more than ``batch`` sequences of the model's length need.
+    engine = Engine(None, dtype=dtype, model_config=config, weights=store, max_seq_len=context,
+                    kv_cache=KvCacheOptions(block_size=PAGE_SIZE),
                     # The token budget lets `prefill_together` whole prompts share one step, so that the
                     # sequences of the end-to-end run start decoding together and the batch stays whole.
                     scheduler=PagedSchedulerConfig(max_num_seqs=batch,
                                                    max_num_batched_tokens=max(PREFILL_TOKENS, batch,
                                                                               prefill_together * context),
                                                    max_prefill_chunk_tokens=max(PREFILL_TOKENS, context)))
+    needed = batch * -(-context // PAGE_SIZE)
+    if engine.runner.manager.groups[0].pool.num_usable < needed:
+        raise SystemExit(f"bench.py: the cache pool got {engine.runner.manager.groups[0].pool.num_usable} pages, "
+                         f"{needed} are needed for batch {batch} at context {context}")
     return engine, config, full_layers
 
 
@@ -267,9 +303,9 @@ def run_ours(args) -> dict:
         for batch in (1, 64):
             p_ms, _, _ = device_decode(engine, batch, args.context, 3, max(8, args.steps // 2), None)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / p_ms, 1)
+    decode_kernels, prefill_kernels = kernel_fractions(config, args.batch, args.context, peak)
     result = {
-        "metric": "decode tok/s @ batch 8, context 4096 (Qwen3-0.6B shape)" if (args.shape, args.batch, args.context) ==
-                  ("0.6b", 8, 4096) else f"decode tok/s @ batch {args.batch}, context {args.context} ({args.shape})",
+        "metric": metric_name(args),
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
@@ -280,16 +316,19 @@ def run_ours(args) -> dict:
             "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
             "intermediate_size": config.intermediate_size, "vocab_size": config.vocab_size,
             "tied_head": config.tie_word_embeddings, "kv_page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-            "l2": "inputs (weights + cache, GBs per step) larger than L2; no flush", "peaks": peak_source,
+            "l2": "inputs (weights + cache, GBs per step) larger than L2; no flush",
+            "peaks": f"{peak_source}: copy rate for decode, burst bf16 product rate for prefill",
+            "cache_pages": runner.manager.groups[0].pool.num_usable,
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clocks,
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4),
+                    "kernels": prefill_kernels},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "kernels": decode_kernels},
         "points": points,
     }
     return result
@@ -322,8 +361,7 @@ def run_reference(args) -> dict:
     full_layers = sizes["num_hidden_layers"]
     if args.layers:
         sizes["num_hidden_layers"] = args.layers
-    config = Qwen3Config(max_position_embeddings=max(args.context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0,
-                         layer_windows=tuple(0 for _ in range(sizes["num_hidden_layers"])), **sizes)
+    config = Qwen3Config(max_position_embeddings=max(args.context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0, **sizes)
     rng = random.Random(77)
     steps, batch = args.steps, args.batch
     start = args.context - steps - 1
@@ -380,7 +418,7 @@ def run_reference(args) -> dict:
     steps_timed = max(decode_tokens / batch, 1e-9)
     prefill_ms = statistics.median(prefill_runs[1:]) * 1e3
     return {
-        "metric": f"decode tok/s @ batch {batch}, context {args.context} ({args.shape})", "value": round(value, 1),
+        "metric": metric_name(args), "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
         "ms_per_step": round(decode_seconds / steps_timed * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",

@@ -45,16 +45,11 @@ def head_dim_of(config: dict) -> int:
 
 
 def layer_window(config: dict, layer: int) -> int:
-    """0 for full attention, else the number of positions a query sees, its own included.  The
-    reference rejects windows (qwen3_config.cpp:63-80); the rule for which layers have one is the
-    one its check implies: layer_types if given, else layers >= max_window_layers."""
-    window = config.get("sliding_window")
-    types = config.get("layer_types")
-    if types is not None:
-        return int(window) if types[layer] == "sliding_attention" else 0
-    if config.get("use_sliding_window", False) and window is not None:
-        return int(window) if layer >= int(config.get("max_window_layers", 0)) else 0
-    return 0
+    """0 for full attention, else the number of positions a query sees, its own included.  Qwen3 has
+    none: the reference rejects windows (qwen3_config.cpp:63-80).  The tests' own windowed
+    architecture names them per layer under ``layer_windows``."""
+    windows = config.get("layer_windows")
+    return int(windows[layer]) if windows is not None else 0
 
 
 # ------------------------------------------------------------------------- parts

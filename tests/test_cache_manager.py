@@ -8,8 +8,8 @@ import pytest
 from zephyr_b200.cache import NULL_PAGE, CacheManager, PagedCacheSpec, PagePool, StateCacheSpec, StateSlots
 from zephyr_b200.config import InvalidArgumentError, OutOfPagesError
 
-FULL = PagedCacheSpec(num_kv_heads=2, head_dim=16, window=0)
-WINDOW = PagedCacheSpec(num_kv_heads=2, head_dim=16, window=10)
+FULL = PagedCacheSpec(num_kv_heads=2, key_dim=16, window=0)
+WINDOW = PagedCacheSpec(num_kv_heads=2, key_dim=16, window=10)
 STATE = StateCacheSpec(shape=(4,))
 
 
@@ -148,3 +148,30 @@ def test_random_orders_of_requests(seed):
     manager.check_invariants()
     assert all(g.pool.num_free == g.pool.num_usable for g in manager.groups)
     assert manager.slots.num_free == 4
+
+
+def test_keys_and_values_of_different_widths_have_pages_of_their_own():
+    """A cache whose keys are wider than its values (a compressed or asymmetric mixer) forms a group
+    apart from the equal-width ones, costs key_dim + value_dim per position and head, and its storage
+    hands out the two halves of every page as views."""
+    import torch
+
+    from zephyr_b200.cache import CacheStorage, bytes_per_page
+
+    equal = PagedCacheSpec(num_kv_heads=2, key_dim=16)
+    lopsided = PagedCacheSpec(num_kv_heads=2, key_dim=24, value_dim=8)
+    assert equal.value_dim == 16 and equal.head_dim == 16
+    with pytest.raises(InvalidArgumentError, match="no single head size"):
+        lopsided.head_dim
+    manager = CacheManager([equal, lopsided, equal], 4, 6, 2)
+    assert [g.cache_ids for g in manager.groups] == [[0, 2], [1]]
+    assert bytes_per_page(manager.cache_specs, 4, torch.bfloat16) == 2 * (2 * 4 * 32 * 2) + 2 * 4 * 32 * 2
+    storage = CacheStorage(manager, torch.float32, "cpu")
+    assert storage[0].shape == (6, 2, 2, 4, 16) and storage[1].shape == (6, 2 * 4 * 32)
+    keys, values = storage.keys(1), storage.values(1)
+    assert keys.shape == (6, 2, 4, 24) and values.shape == (6, 2, 4, 8)
+    keys[3, 1, 2, :] = 1.0
+    values[3, 1, 2, :] = 2.0
+    page = storage[1][3]
+    assert page.sum() == 24 + 16 and page[(1 * 4 + 2) * 24] == 1.0 and page[2 * 4 * 24 + (1 * 4 + 2) * 8] == 2.0
+    assert storage.keys(0).shape == (6, 2, 4, 16) and storage.values(2).data_ptr() == storage[2][:, 1].data_ptr()

@@ -22,7 +22,7 @@ def test_defaults_follow_the_reference():
     config = Qwen3Config.from_dict(BASE)
     assert config.head_dim == 96 // 6                 # absent head_dim -> hidden / heads
     assert config.rope_theta == 1000000.0 and config.tie_word_embeddings is False
-    assert config.layer_windows == (0, 0, 0) and config.eos_token_ids == ()
+    assert config.eos_token_ids == ()
     assert Qwen3Config.from_dict({**BASE, "head_dim": None}).head_dim == 16
     assert Qwen3Config.from_dict({**BASE, "head_dim": 32}).head_dim == 32   # heads*head_dim != hidden is fine
 
@@ -53,8 +53,10 @@ def test_required_keys(key):
     ({"rope_scaling": {"type": "default", "partial_rotary_factor": 0.5}}, "unscaled rotary"),
     ({"rope_parameters": [1]}, "JSON object"),
     ({"layer_types": ["full_attention"]}, "every decoder layer"),
-    ({"layer_types": ["full_attention", "linear_attention", "full_attention"]}, "unknown layer type"),
-    ({"layer_types": ["full_attention", "sliding_attention", "full_attention"]}, "sliding_window"),
+    ({"layer_types": ["full_attention", "linear_attention", "full_attention"]}, "only full-attention"),
+    ({"layer_types": ["full_attention", "sliding_attention", "full_attention"], "sliding_window": 8}, "only full-attention"),
+    ({"use_sliding_window": True, "sliding_window": 24}, "sliding-window attention is unsupported"),
+    ({"use_sliding_window": True, "sliding_window": 24, "max_window_layers": 2}, "sliding-window attention is unsupported"),
     ({"eos_token_id": 400}, "outside the vocabulary"),
     ({"eos_token_id": "x"}, "eos_token_id"),
     ({"tie_word_embeddings": 1}, "true or false"),
@@ -71,19 +73,17 @@ def test_rope_parameters_may_carry_theta():
     assert Qwen3Config.from_dict({**BASE, "rope_scaling": None}).rope_theta == 1000000.0
 
 
-def test_sliding_window_is_accepted_where_the_reference_rejects_it():
-    config = Qwen3Config.from_dict({**BASE, "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 1})
-    assert config.layer_windows == (0, 24, 24)
-    config = Qwen3Config.from_dict({**BASE, "sliding_window": 8,
-                                    "layer_types": ["sliding_attention", "full_attention", "sliding_attention"]})
-    assert config.layer_windows == (8, 0, 8)
-    # A configured window that reaches no layer has no effect (qwen3_config.cpp:63-69).
-    config = Qwen3Config.from_dict({**BASE, "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 3})
-    assert config.layer_windows == (0, 0, 0)
-    assert Qwen3Config.from_dict({**BASE, "use_sliding_window": False, "sliding_window": 24}).layer_windows == (0, 0, 0)
+def test_a_window_that_reaches_no_layer_is_accepted_as_the_reference_accepts_it():
+    """qwen3_config.cpp:62-69: a configured window has no effect until it is enabled on a layer."""
+    for patch in ({"use_sliding_window": True, "sliding_window": 24, "max_window_layers": 3},
+                  {"use_sliding_window": False, "sliding_window": 24},
+                  {"use_sliding_window": True, "sliding_window": None},
+                  {"layer_types": ["full_attention"] * 3}):
+        spec = Qwen3Config.from_dict({**BASE, **patch}).to_model_spec()
+        assert all(layer.mixer.params["window"] == 0 for layer in spec.layers)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "W"])
 def test_round_trip_and_spec(name, tmp_path):
     config = tiny_config(name)
     (tmp_path / "config.json").write_text(json.dumps(config.to_dict()))
@@ -92,20 +92,21 @@ def test_round_trip_and_spec(name, tmp_path):
     spec = config.to_model_spec()
     assert isinstance(spec, ModelSpec) and len(spec.layers) == config.num_hidden_layers
     assert spec.run_order == tuple(LayerCall(i, i) for i in range(config.num_hidden_layers))
-    assert spec.tied_head == config.tie_word_embeddings
+    assert (spec.output.params["weight"] == spec.input.params["weight"]) == config.tie_word_embeddings
+    windows = TINY[name].get("windows", (0,) * config.num_hidden_layers)
     for index, layer in enumerate(spec.layers):
         p = layer.mixer.params
         assert (p["num_heads"], p["num_kv_heads"], p["head_dim"], p["window"]) == (
-            config.num_attention_heads, config.num_key_value_heads, config.head_dim, config.layer_windows[index])
-        assert layer.mixer_norm.eps == config.rms_norm_eps and layer.mixer.position.params["theta"] == config.rope_theta
+            config.num_attention_heads, config.num_key_value_heads, config.head_dim, windows[index])
+        assert set(layer.norms) == {"mixer", "feed_forward"}
+        assert layer.norms["mixer"].eps == config.rms_norm_eps and layer.mixer.position.params["theta"] == config.rope_theta
         assert p["q_proj"] == f"model.layers.{index}.self_attn.q_proj.weight"
 
 
 def test_the_two_tiny_configurations_differ_in_every_size():
     a, b = TINY["A"]["config"], TINY["B"]["config"]
     for key in a:
-        if key != "layer_windows":
-            assert a[key] != b[key], key
+        assert a[key] != b[key], key
     assert TINY["A"]["page_size"] != TINY["B"]["page_size"]
 
 

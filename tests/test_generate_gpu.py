@@ -82,8 +82,8 @@ def test_workload_a_three_requests_greedy(model_folders, cuda_device):
 
 def test_workload_b_four_requests_temperature(model_folders, cuda_device):
     """Tiny B, prompts of 1/9/33/70 tokens, prompt portions of 16, 12 tokens at temperature 0.7 from
-    seeded generators (float32): the batch gives what each request gives alone, and each first token
-    is the one the plain logits and the same uniform number select."""
+    seeded generators (float32): the batch gives what each request gives alone, and every token is
+    the one that the plain logits of its history and the request's own generator select."""
     from zephyr_b200.sampling import MT19937_64
 
     folder = model_folders("B", "float32")
@@ -101,11 +101,18 @@ def test_workload_b_four_requests_temperature(model_folders, cuda_device):
     alone = [list(engine.generate(p, max_tokens=12, temperature=0.7, seed=100 + i, ignore_eos=True).token_ids)
              for i, p in enumerate(prompts)]
     assert together == alone
+    followed = 0
     for i, (prompt, got) in enumerate(zip(prompts, together)):
-        u = MT19937_64(100 + i).next_uniform()
-        index, margin = plain_sample(plain_forward(config, weights, prompt)[-1], 0.7, u)
-        if margin > 1e-5:
-            assert got[0] == index
+        generator = MT19937_64(100 + i)             # the request's own generator: one number per token
+        history = list(prompt)
+        for position, token in enumerate(got):
+            index, margin = plain_sample(plain_forward(config, weights, history)[-1], 0.7, generator.next_uniform())
+            if margin <= 1e-5:
+                break           # the draw falls on an interval's edge: float32 prefix sums may fairly pick a neighbour
+            assert token == index, f"request {i} token {position}: {token} != {index} (margin {margin:.2e})"
+            history.append(token)
+            followed += 1
+    assert followed >= 40           # nearly all of the 48 tokens were checked
 
 
 def test_filters_penalties_and_reports_match_the_plain_sampler(model_folders, cuda_device):

@@ -89,7 +89,9 @@ def test_whole_model_properties(name, tmp_path):
     other = plain_forward(config, weights, changed)
     assert torch.allclose(other[:20], logits[:20], atol=1e-10) and not torch.allclose(other[20:], logits[20:])
     if name == "C":     # windows: layers 1 and 2 see 24 positions, layer 0 sees all
-        assert config["layer_types"] == ["full_attention", "sliding_attention", "sliding_attention"]
+        assert config["layer_windows"] == [0, 24, 24]
+        full = plain_forward({k: v for k, v in config.items() if k != "layer_windows"}, weights, tokens)
+        assert torch.allclose(full[:24], logits[:24], atol=1e-10) and not torch.allclose(full[24:], logits[24:])
     generated = plain_greedy_generate(config, weights, tokens[:5], 3)
     assert len(generated) == 3 and generated[0] == int(plain_forward(config, weights, tokens[:5])[-1].argmax())
 

@@ -1,8 +1,10 @@
 """The engine against the plain implementation under every way of cutting the work, in 32-bit and
-in bfloat16, on three tiny configurations: each request alone and whole; most of it in one step and
-the last 32 tokens one by one; portions of changing size down to two tokens; and mixed, up to four
-live requests with so few pages that they are used again (pages given back are filled with NaN, so a
-kernel that reads a page it should not shows up as a non-finite logit)."""
+in bfloat16: each request alone and whole; most of it in one step and the last 32 tokens one by one;
+portions of changing size down to two tokens; mixed, up to four live requests with so few pages that
+they are used again (pages given back are filled with NaN, so a kernel that reads a page it should
+not shows up as a non-finite logit); and the tails of several requests decoded together.  The
+configurations are the tiny ones (A, B), the windowed test architecture (C, W), and D, E, F, which
+have the head size and layer widths of the benchmarked models and so run the kernels those run."""
 
 import json
 import os
@@ -13,15 +15,18 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from replay_util import (collect, first_mismatch, peak_tokens, random_tokens, run_in_process, trace_mixed,
-                         trace_portions, trace_tail, trace_whole)
+from replay_util import (collect, first_mismatch, peak_tokens, random_tokens, run_in_process, trace_batched_tail,
+                         trace_mixed, trace_portions, trace_tail, trace_whole)
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 128, 45, 33, 100, 5, 17, 64], "B": [1, 9, 33, 70, 150, 256, 41, 96],
-           "C": [60, 130, 250, 40, 90, 33, 17, 200]}
-TRACES = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions, "mixed": trace_mixed}
+           "C": [60, 130, 250, 40, 90, 33, 17, 200], "W": [60, 130, 250, 40, 300, 33, 17, 200],
+           "D": [300, 600, 129, 257, 64, 40, 513, 17], "E": [200, 520, 64, 129, 300, 33], "F": [300, 40, 130, 70]}
+TRACES = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions, "mixed": trace_mixed,
+          "batched": trace_batched_tail}
+NAMES = ["A", "B", "C", "W", "D", "E", "F"]
 
 
 def make_requests(name: str) -> dict[str, list[int]]:
@@ -29,9 +34,9 @@ def make_requests(name: str) -> dict[str, list[int]]:
     return {f"r{i}": random_tokens(vocab, n, seed=1000 * ord(name) + i) for i, n in enumerate(LENGTHS[name])}
 
 
-@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed", "batched"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", NAMES)
 def test_replay_matches_plain(model_folders, cuda_device, name, dtype, mode):
     folder = model_folders(name, dtype)
     requests = make_requests(name)
@@ -39,27 +44,30 @@ def test_replay_matches_plain(model_folders, cuda_device, name, dtype, mode):
     outputs = run_in_process(folder, dtype, steps, TINY[name]["page_size"])
     rows = collect(steps, outputs)
     assert len(rows) >= sum(1 for _ in requests)
-    first, worst, where = first_mismatch(rows, requests, folder, dtype)
+    first, worst, where = first_mismatch(rows, requests, folder, dtype, f"{name} {mode}")
     assert first is None, (f"{name} {dtype} {mode}: first wrong logits at request {first[0]} position {first[1]}: "
                            f"error {first[2]:.3e} > {first[3]:.1e}; worst {worst:.3e} at {where}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_cuttings_agree_with_each_other(model_folders, cuda_device, dtype):
-    """The same (request, position) gives the same logits however the tokens were cut, beyond rounding."""
-    name = "B"
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_cuttings_agree_with_each_other(model_folders, cuda_device, name, dtype):
+    """The same (request, position) gives the same logits however the tokens were cut, beyond rounding
+    (twice the bound of one run against the plain implementation)."""
+    from replay_util import tolerance
+
     folder = model_folders(name, dtype)
     requests = make_requests(name)
     results = {}
     for mode, build in TRACES.items():
         steps = build(requests)
         results[mode] = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
-    tol = 2e-4 if dtype == "float32" else 0.04
     for key, row in results["whole"].items():
         for mode in ("portions", "mixed"):
-            assert np.abs(results[mode][key] - row).max() <= tol, (mode, key)
-    for key, row in results["tail"].items():
-        assert np.abs(results["whole"][key] - row).max() <= tol, ("tail", key)
+            assert np.abs(results[mode][key] - row).max() <= 2 * tolerance(dtype, row), (mode, key)
+    for mode in ("tail", "batched"):
+        for key, row in results[mode].items():
+            assert np.abs(results["whole"][key] - row).max() <= 2 * tolerance(dtype, row), (mode, key)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -218,33 +226,42 @@ def test_prepared_steps_and_tokens_from_the_device(model_folders, cuda_device, d
         runner.step(fresh, stale, device_tokens=torch.zeros(3, dtype=torch.int32, device=cuda_device))
 
 
-def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeypatch):
+CHAIN_LENGTHS = {"B": (30, 35, 40), "C": (30, 35, 40), "W": (60, 35, 90), "D": (200, 270, 140), "E": (100, 260, 70),
+                 "F": (40, 80, 130)}
+
+
+@pytest.mark.parametrize("name", ["B", "C", "W", "D", "E", "F"])
+def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeypatch, name):
     """Decode steps of a few tokens run as fused chains of a layer's products.  A product the chain
-    kernel refuses (its input too long for shared memory, on a large model) runs as kernels of its
-    own between two chains: here the down projections are refused by hand.  Whole chains, partial
-    chains and no chains all agree with the plain implementation, and so does the decode attention
-    that does the position encoding and the cache write itself (the engine uses it for large batches)."""
+    kernel refuses (its input too long for shared memory: the down projection of the 8B widths in F)
+    runs as kernels of its own between two chains; on the other configurations the down projections
+    are refused by hand.  Whole chains, partial chains and no chains all agree with the plain
+    implementation, and so does the decode attention that does the position encoding and the cache
+    write itself (the engine uses it for large batches).  The traces decode the tails of three
+    requests together, and mix portions with single tokens."""
     from zephyr_b200.engine.replay import TraceReplayer
     from zephyr_b200.kernels import ops
 
-    for name in ("B", "C"):
-        folder = model_folders(name, "bfloat16")
-        config = TINY[name]["config"]
-        requests = {f"r{i}": random_tokens(config["vocab_size"], 30 + 5 * i, seed=900 + i) for i in range(3)}
-        steps = trace_mixed(requests, seed=11, tail=20)
+    folder = model_folders(name, "bfloat16")
+    config = TINY[name]["config"]
+    requests = {f"r{i}": random_tokens(config["vocab_size"], n, seed=900 + i) for i, n in enumerate(CHAIN_LENGTHS[name])}
+    down_shape = (config["hidden_size"], config["intermediate_size"])
+    for build in (lambda r: trace_mixed(r, seed=11, tail=20), lambda r: trace_batched_tail(r, tail=24)):
+        steps = build(requests)
         for mode in ("whole", "partial", "off", "one kernel"):
             with monkeypatch.context() as patch:
                 refused = []
-                if mode == "partial":
-                    real = ops.fused_chain_stage_supported
+                real = ops.fused_chain_stage_supported
 
-                    def picky(tokens, w, normed_input, swiglu):
-                        if tuple(w.shape) == (config["hidden_size"], config["intermediate_size"]):      # a down projection
-                            refused.append(tokens)
-                            return False
-                        return real(tokens, w, normed_input, swiglu)
-                    patch.setattr(ops, "fused_chain_stage_supported", picky)
+                def picky(tokens, w, normed_input, swiglu):
+                    taken = real(tokens, w, normed_input, swiglu)
+                    if tuple(w.shape) == down_shape and (mode == "partial" or not taken):
+                        refused.append(tokens)
+                        return False
+                    return taken
+                patch.setattr(ops, "fused_chain_stage_supported", picky)
                 replayer = TraceReplayer(folder, "bfloat16", peak_tokens(steps), page_size=TINY[name]["page_size"], max_requests=4)
+                replayer.runner.poison_freed_pages = True
                 chains = replayer.runner.model.chains
                 assert chains is not None and chains.supports(3)
                 replayer.runner.model.use_chains = mode != "off"
@@ -252,7 +269,128 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
                     for block in replayer.runner.model.layers:
                         block.mixer.fuse_decode_rows = 1
                 outputs = {s["step"]: replayer.step(s) for s in steps}
-                assert (mode == "partial") == bool(refused)
+                # F's down projection (K = 12288) does not fit beside the weight ring: refused for real.
+                assert bool(refused) == (mode == "partial" or (name == "F" and mode != "off")), (mode, refused)
             rows = collect(steps, {k: v for k, v in outputs.items() if v is not None})
-            first, worst, where = first_mismatch(rows, requests, folder, "bfloat16")
+            first, worst, where = first_mismatch(rows, requests, folder, "bfloat16", f"{name} chains {mode}")
             assert first is None, f"{name} {mode}: {first}; worst {worst:.3e} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_decoding_across_the_bounds_of_the_decode_graphs(model_folders, cuda_device, name, dtype):
+    """Decode graphs are keyed by a power-of-two bound on the longest context (256, 512, 1024).  Two
+    requests decode from below 256 to beyond it, a third joins, and all three go on past 512: every
+    change of the bound captures a new graph with another split plan while the requests are live.
+    Steps are described ahead (``prepare``) and get their tokens on the device (``device_tokens``)
+    across the changes, as the engine runs them.  Every logit is compared with the plain model."""
+    import torch
+
+    from zephyr_b200.engine import StepEntry
+    from zephyr_b200.engine.replay import TraceReplayer
+
+    folder = model_folders(name, dtype)
+    vocab = TINY[name]["config"]["vocab_size"]
+    requests = {"a": random_tokens(vocab, 290, seed=1), "b": random_tokens(vocab, 300, seed=2),
+                "c": random_tokens(vocab, 540, seed=3)}
+    runner = TraceReplayer(folder, dtype, 1280, page_size=TINY[name]["page_size"], max_requests=4).runner
+    runner.poison_freed_pages = True
+    fed, rows = {}, {}
+
+    def prefill(rid, count):
+        assert runner.add_request(rid)
+        logits = runner.step([StepEntry(rid, requests[rid][:count], (count - 1,))])
+        rows[(rid, count - 1)] = logits[0].cpu().numpy()
+        fed[rid] = count
+
+    def decode(live, steps):
+        bounds = set()
+        for turn in range(steps):
+            entries = [StepEntry(rid, [requests[rid][fed[rid]]], (0,)) for rid in live]
+            key = runner._graph_key(entries)
+            bounds.add(key[1])
+            placeholders = [StepEntry(rid, [-1], (0,)) for rid in live]
+            prepared = runner.prepare(placeholders)
+            if prepared is not None and turn % 2 == 0:
+                tokens = torch.tensor([requests[rid][fed[rid]] for rid in live], dtype=torch.int32, device=cuda_device)
+                logits = runner.step(placeholders, prepared, device_tokens=tokens)
+            else:
+                logits = runner.step(entries, prepared)      # prepared may be None: a graph not captured yet
+            got = logits.cpu().numpy()
+            for index, rid in enumerate(live):
+                rows[(rid, fed[rid])] = got[index].copy()
+                fed[rid] += 1
+            runner.check()
+            runner.manager.check_invariants()
+        return bounds
+
+    prefill("a", 246)
+    prefill("b", 250)
+    assert decode(["a", "b"], 20) == {256, 512}                 # b passes 256 after six steps
+    prefill("c", 500)
+    assert decode(["a", "b", "c"], 24) == {512, 1024}           # c passes 512 after twelve
+    decode_graphs = [k for k in runner._graphs if isinstance(k[0], int)]
+    assert sorted(decode_graphs) == [(2, 256), (2, 512), (3, 512), (3, 1024)]
+    first, worst, where = first_mismatch(rows, requests, folder, dtype, f"{name} graph bounds")
+    assert first is None, f"{name} {dtype}: {first}; worst {worst:.3e} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_shape_graphs_are_evicted_and_captured_again(model_folders, cuda_device, dtype):
+    """A step shape other than decode-only is captured when it comes a second time, and at most 16 such
+    graphs are kept.  Eighteen shapes come twice each, so the first ones are evicted; then the first
+    shape comes again, twice, and is captured again.  Every step agrees with the plain model."""
+    from zephyr_b200.engine import StepEntry
+    from zephyr_b200.engine.replay import TraceReplayer
+
+    name = "D"
+    folder = model_folders(name, dtype)
+    tokens = random_tokens(TINY[name]["config"]["vocab_size"], 2 * sum(range(2, 20)) + 8, seed=9)
+    requests = {"s": tokens}
+    runner = TraceReplayer(folder, dtype, 512, page_size=TINY[name]["page_size"], max_requests=2).runner
+    assert runner.add_request("s")
+    rows, fed = {}, 0
+    sizes = [n for n in range(2, 20) for _ in (0, 1)] + [2, 2, 2]
+    captured_first = []
+    for n in sizes:
+        logits = runner.step([StepEntry("s", tokens[fed:fed + n], (0, n - 1))]).cpu().numpy()
+        rows[("s", fed)], rows[("s", fed + n - 1)] = logits[0].copy(), logits[1].copy()
+        fed += n
+        shaped = [k for k in runner._graphs if not isinstance(k[0], int)]
+        assert len(shaped) <= runner.MAX_SHAPE_GRAPHS
+        captured_first.append(any(k[0] == ((2, (0, 1)),) for k in shaped))
+    runner.check()
+    assert captured_first[1] and not captured_first[35]         # captured at its second coming, evicted later
+    assert not captured_first[36] and captured_first[37] and captured_first[38]     # counted again, captured again
+    first, worst, where = first_mismatch(rows, {"s": tokens[:fed]}, folder, dtype, f"{name} eviction")
+    assert first is None, f"{dtype}: {first}; worst {worst:.3e} at {where}"
+
+
+def test_the_full_0_6b_shape_in_float32(cuda_device, tmp_path):
+    """The check run of the benchmarked model: all 28 layers of the Qwen3-0.6B shape with its whole
+    vocabulary in true 32-bit arithmetic, a prompt of 24 tokens in two portions and two decoded
+    tokens, three rows of logits against the plain implementation."""
+    import torch
+
+    from plain_qwen3 import load_model_folder, plain_forward
+    from zephyr_b200.config import Qwen3Config
+    from zephyr_b200.weights import write_random_model
+
+    config = Qwen3Config(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+                         num_attention_heads=16, num_key_value_heads=8, head_dim=128, max_position_embeddings=4096,
+                         rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True)
+    folder = write_random_model(config, 7, tmp_path / "qwen3_0_6b_float32", dtype=torch.float32)
+    tokens = random_tokens(config.vocab_size, 26, seed=6)
+    steps = [{"step": 0, "entries": [{"id": "p", "tokens": tokens[:15], "want": [14]}], "end": []},
+             {"step": 1, "entries": [{"id": "p", "tokens": tokens[15:24], "want": [8]}], "end": []},
+             {"step": 2, "entries": [{"id": "p", "tokens": tokens[24:25], "want": []}], "end": []},
+             {"step": 3, "entries": [{"id": "p", "tokens": tokens[25:26], "want": [0]}], "end": ["p"]}]
+    rows = collect(steps, run_in_process(folder, "float32", steps, 16))
+    assert sorted(rows) == [("p", 14), ("p", 23), ("p", 25)]
+    plain_config, weights = load_model_folder(folder)
+    expected = plain_forward(plain_config, weights, tokens).numpy()
+    for (_, position), got in rows.items():
+        error = float(np.abs(got.astype(np.float64) - expected[position]).max())
+        bound = 1e-4 * max(1.0, float(np.abs(expected[position]).max()))
+        print(f"[logits] 0.6B float32 position {position}: error {error:.3e}, bound {bound:.1e}")
+        assert error <= bound, (position, error)

@@ -10,15 +10,15 @@ from zephyr_b200.cache import CacheManager, PagedCacheSpec
 from zephyr_b200.config import ConfigError, InvalidArgumentError
 from zephyr_b200.engine.scheduler import (PagedSchedulerConfig, Scheduler, Sequence, SequenceState)
 
-SPEC = PagedCacheSpec(num_kv_heads=2, head_dim=16)
+SPEC = PagedCacheSpec(num_kv_heads=2, key_dim=16)
 
 
 class Harness:
     """Drives the scheduler as the engine does, with a stand-in for the model: the next token of a
     sequence is a function of its history, so a preempted sequence must end up with the same tokens."""
 
-    def __init__(self, num_pages, page_size=4, **config):
-        self.manager = CacheManager([SPEC], page_size, num_pages, config.get("max_num_seqs", 8))
+    def __init__(self, num_pages, page_size=4, spec=SPEC, **config):
+        self.manager = CacheManager([spec], page_size, num_pages, config.get("max_num_seqs", 8))
         self.sequences: dict[int, Sequence] = {}
         self.scheduler = Scheduler(PagedSchedulerConfig(**config), self.sequences, self.manager)
         self.limits: dict[int, int] = {}
@@ -156,6 +156,43 @@ def test_finish_and_add_rules():
     h.add(1, range(3), 1)
     h.scheduler.finish(1)                 # cancelled while waiting
     assert not h.scheduler.has_unfinished
+
+
+def test_more_decoders_than_the_token_budget_take_turns():
+    """Six decoders under a budget of two tokens a step: the turn moves on, so that every decoder is
+    served once in three steps and nobody starves."""
+    h = Harness(num_pages=64, max_num_seqs=6, max_num_batched_tokens=16, max_prefill_chunk_tokens=16)
+    for sid in range(6):
+        h.add(sid, [sid + 1], 9)
+    h.step()                                                            # all six prompts in one step
+    assert all(h.sequences[sid].state == SequenceState.DECODE for sid in range(6))
+    h.scheduler.config = PagedSchedulerConfig(max_num_seqs=6, max_num_batched_tokens=2, max_prefill_chunk_tokens=2)
+    served = []
+    for _ in range(6):
+        h.step()
+        assert len(h.log[-1]) == 2 and all(n == 1 for _, _, n, _ in h.log[-1])
+        served.append(sorted(s[0] for s in h.log[-1]))
+    for start in range(0, 6, 3):
+        assert sorted(sum(served[start:start + 3], [])) == list(range(6)), served
+    h.run()
+    for sid in range(6):
+        assert h.sequences[sid].token_ids == expected_tokens([sid + 1], 9)
+
+
+@pytest.mark.parametrize("num_pages", range(7, 16))
+def test_long_prompts_in_a_windowed_group_do_not_starve_each_other(num_pages):
+    """A windowed group gives pages back while a prompt is still being computed.  The prompt keeps its
+    claim on as many pages as it holds at one time, so that requests admitted meanwhile cannot leave
+    every prompt short of pages (a step without progress)."""
+    windowed = PagedCacheSpec(num_kv_heads=2, key_dim=16, window=8)
+    h = Harness(num_pages=num_pages, spec=windowed, max_num_seqs=4, max_num_batched_tokens=16, max_prefill_chunk_tokens=8)
+    jobs = {sid: (list(range(sid, sid + 60)), 3) for sid in range(4)}
+    for sid, job in jobs.items():
+        h.add(sid, *job)
+    h.run()
+    for sid, (prompt, new) in jobs.items():
+        assert h.sequences[sid].token_ids == expected_tokens(prompt, new), sid
+    assert h.manager.num_requests == 0 and h.manager.num_free_pages() == num_pages - 1
 
 
 @pytest.mark.parametrize("seed", range(5))

@@ -1,8 +1,10 @@
 """Parts that the framework does not have, defined here and registered from outside: a mixer with a
-state of its own (a running mean over the sequence, kept in the per-request state slots), in a toy
-architecture whose run order names a layer twice and lets a layer read another layer's cache.  The
-model is built, stepped whole, in portions and mixed with other requests, and compared with a plain
-float64 computation written in this file.  No file of the framework is changed for it."""
+state of its own (a running mean over the sequence, kept in the per-request state slots), a block
+arrangement with four norms (one before and one after each of its two parts), an input part that
+scales the embeddings and an output part that scales and caps the logits, in a toy architecture
+whose run order names a layer twice and lets a layer read another layer's cache.  The model is
+built, stepped whole, in portions and mixed with other requests, and compared with a plain float64
+computation written in this file.  No file of the framework is changed for it."""
 
 import json
 import math
@@ -16,14 +18,64 @@ from replay_util import collect, random_tokens, trace_mixed, trace_portions, tra
 pytestmark = pytest.mark.gpu
 
 HIDDEN, VOCAB, HEADS, KV_HEADS, HEAD_DIM, INTER, EPS, THETA, MAX_POS = 48, 101, 4, 2, 16, 80, 1e-5, 10000.0, 128
+EMBED_SCALE, LOGIT_SCALE, LOGIT_CAP = 3.0, 0.5, 2.0
 
 
 def toy_classes():
     from zephyr_b200.cache import StateCacheSpec
-    from zephyr_b200.config import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+    from zephyr_b200.config import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec,
+                                    OutputSpec, PositionSpec)
     from zephyr_b200.kernels import ops
-    from zephyr_b200.parts import Mixer
+    from zephyr_b200.parts import NORMS, Block, InputPart, Mixer, OutputPart, lookup
     from zephyr_b200.weights import WeightDecl
+
+    class SandwichBlock(Block):
+        """r = x + post_mixer(mixer(pre_mixer(x))); x' = r + post_ffn(ffn(pre_ffn(r))): four norms."""
+
+        norm_names = ("pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward")
+
+        def __init__(self, mixer, feed_forward, norms):
+            self.mixer, self.feed_forward, self.norms = mixer, feed_forward, dict(norms)
+
+        def forward(self, stream, ctx, call):
+            x = stream.flush()
+            x = x + self.norms["post_mixer"].forward(self.mixer.forward(self.norms["pre_mixer"].forward(x), ctx, call))
+            x = x + self.norms["post_feed_forward"].forward(
+                self.feed_forward.forward(self.norms["pre_feed_forward"].forward(x)))
+            stream.hidden = x
+            return stream
+
+    class ScaledEmbedding(InputPart):
+        """h = scale * E[id]."""
+
+        def __init__(self, spec, weights, dtype):
+            self.table, self.scale = weights[spec.params["weight"]], float(spec.params["scale"])
+
+        @staticmethod
+        def weight_decls(spec):
+            return {spec.params["weight"]: WeightDecl((spec.params["vocab_size"], spec.params["hidden_size"]), "embedding")}
+
+        def forward(self, ctx):
+            return (ops.embedding(self.table, ctx.token_ids, ctx.status).float() * self.scale).to(self.table.dtype)
+
+    class CappedHead(OutputPart):
+        """logits = cap * tanh(scale * (norm(h) W^T) / cap)."""
+
+        def __init__(self, spec, weights, dtype):
+            p = spec.params
+            self.norm = lookup(NORMS, "norm", p["norm"].kind)(p["norm"], weights, dtype)
+            self.weight, self.scale, self.cap = weights[p["weight"]], float(p["scale"]), float(p["cap"])
+
+        @staticmethod
+        def weight_decls(spec):
+            p = spec.params
+            return {**lookup(NORMS, "norm", p["norm"].kind).weight_decls(p["norm"]),
+                    p["weight"]: WeightDecl((p["vocab_size"], p["hidden_size"]))}
+
+        def forward(self, stream, ctx):
+            rows = ops.gather_rows(stream.flush(), ctx.logit_tokens, ctx.status)
+            logits = ops.linear(self.norm.forward(rows), self.weight, out_dtype=torch.float32)
+            return self.cap * torch.tanh(logits * (self.scale / self.cap))
 
     class RunningMeanMixer(Mixer):
         """y_t = W * mean(x_0 .. x_t).  The state is the running sum, one float32 vector per request."""
@@ -89,25 +141,42 @@ def toy_classes():
                 prefix = f"toy.layers.{index}"
                 mixer = (MixerSpec("running_mean", {"hidden_size": HIDDEN, "proj": f"{prefix}.mean.proj.weight"})
                          if index == 1 else attention(f"{prefix}.attn"))
-                layers.append(LayerSpec("prenorm_residual", mixer, ffn(f"{prefix}.mlp"), norm(f"{prefix}.norm1.weight"),
-                                        norm(f"{prefix}.norm2.weight")))
+                if index == 2:      # the arrangement with four norms
+                    layers.append(LayerSpec("toy_sandwich", mixer, ffn(f"{prefix}.mlp"), {
+                        "pre_mixer": norm(f"{prefix}.norm1.weight"), "post_mixer": norm(f"{prefix}.norm1b.weight"),
+                        "pre_feed_forward": norm(f"{prefix}.norm2.weight"),
+                        "post_feed_forward": norm(f"{prefix}.norm2b.weight")}))
+                    continue
+                layers.append(LayerSpec("prenorm_residual", mixer, ffn(f"{prefix}.mlp"),
+                                        {"mixer": norm(f"{prefix}.norm1.weight"),
+                                         "feed_forward": norm(f"{prefix}.norm2.weight")}))
             run_order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2),        # layer 0 runs twice, own caches
                          LayerCall(2, 0, writes_cache=False),                     # layer 2 reads the cache of call 0
                          LayerCall(1, 3))                                         # the stateful layer again, own state
-            return ModelSpec("ToyMixForCausalLM", VOCAB, HIDDEN, MAX_POS, "toy.embed.weight", tuple(layers), run_order,
-                             norm("toy.norm.weight"), "toy.head.weight")
+            return ModelSpec(
+                "ToyMixForCausalLM", VOCAB, HIDDEN, MAX_POS,
+                InputSpec("toy_scaled_embedding", {"weight": "toy.embed.weight", "vocab_size": VOCAB,
+                                                   "hidden_size": HIDDEN, "scale": EMBED_SCALE}),
+                tuple(layers), run_order,
+                OutputSpec("toy_capped_head", {"norm": norm("toy.norm.weight"), "weight": "toy.head.weight",
+                                               "vocab_size": VOCAB, "hidden_size": HIDDEN, "scale": LOGIT_SCALE,
+                                               "cap": LOGIT_CAP}))
 
-    return RunningMeanMixer, ToyConfig
+    return RunningMeanMixer, ToyConfig, SandwichBlock, ScaledEmbedding, CappedHead
 
 
 @pytest.fixture(scope="module")
 def toy_folder(tmp_path_factory):
     from zephyr_b200.config import register_architecture, unregister_architecture
-    from zephyr_b200.parts import MIXERS, register_mixer
+    from zephyr_b200.parts import (BLOCKS, INPUTS, MIXERS, OUTPUTS, register_block, register_input, register_mixer,
+                                   register_output)
     from zephyr_b200.weights import write_random_model
 
-    mixer, config = toy_classes()
+    mixer, config, block, embedding, head = toy_classes()
     register_mixer("running_mean", mixer)
+    register_block("toy_sandwich", block)
+    register_input("toy_scaled_embedding", embedding)
+    register_output("toy_capped_head", head)
     register_architecture(config.model_type, config.architecture, config)
     folders = {}
     for dtype in ("float32", "bfloat16"):
@@ -116,6 +185,9 @@ def toy_folder(tmp_path_factory):
     yield folders
     unregister_architecture(config.architecture)
     MIXERS.pop("running_mean", None)
+    BLOCKS.pop("toy_sandwich", None)
+    INPUTS.pop("toy_scaled_embedding", None)
+    OUTPUTS.pop("toy_capped_head", None)
 
 
 # ------------------------------------------------------------- the plain computation
@@ -128,7 +200,7 @@ def plain_toy_logits(folder, tokens):
             w[name] = handle.get_tensor(name).to(F64)
     T = len(tokens)
     cos, sin = plain_rope_tables(HEAD_DIM, T, THETA)
-    x = w["toy.embed.weight"][torch.tensor(tokens)]
+    x = EMBED_SCALE * w["toy.embed.weight"][torch.tensor(tokens)]
 
     def qkv(h, prefix):
         q = plain_rope(plain_rmsnorm((h @ w[f"{prefix}.q_proj.weight"].T).view(T, HEADS, HEAD_DIM),
@@ -148,6 +220,11 @@ def plain_toy_logits(folder, tokens):
         if kv is not None:
             k, v = kv
         out = plain_attention(q, k, v).reshape(T, HEADS * HEAD_DIM) @ w[f"toy.layers.{index}.attn.o_proj.weight"].T
+        if index == 2:      # four norms: one more after each part
+            prefix = f"toy.layers.{index}"
+            r = x + plain_rmsnorm(out, w[f"{prefix}.norm1b.weight"], EPS)
+            fed = plain_mlp(plain_rmsnorm(r, w[f"{prefix}.norm2.weight"], EPS), w, f"{prefix}.mlp")
+            return r + plain_rmsnorm(fed, w[f"{prefix}.norm2b.weight"], EPS), (k, v)
         return finish(x, out, index), (k, v)
 
     def mean_layer(x, index):
@@ -160,7 +237,8 @@ def plain_toy_logits(folder, tokens):
     x, _ = attention_layer(x, 0)
     x, _ = attention_layer(x, 2, kv=kv0)
     x = mean_layer(x, 1)
-    return (plain_rmsnorm(x, w["toy.norm.weight"], EPS) @ w["toy.head.weight"].T).numpy()
+    logits = plain_rmsnorm(x, w["toy.norm.weight"], EPS) @ w["toy.head.weight"].T
+    return (LOGIT_CAP * torch.tanh(logits * (LOGIT_SCALE / LOGIT_CAP))).numpy()
 
 
 def test_toy_architecture_is_found_and_built(toy_folder, cuda_device):

@@ -27,15 +27,30 @@ NULL_PAGE = 0
 
 @dataclass(frozen=True)
 class PagedCacheSpec:
-    """A cache that grows with the context: keys and values per position."""
+    """A cache that grows with the context: per position and head a key of ``key_dim`` values and a
+    value of ``value_dim`` values (the reference keeps the two widths apart per layer,
+    src/include/kv_cache/cache_engine.hpp:18-22).  ``value_dim`` 0 means "as wide as the key"."""
 
     num_kv_heads: int
-    head_dim: int
+    key_dim: int
+    value_dim: int = 0
     window: int = 0        # 0: every position is kept; n: only the last n positions are ever read
+
+    def __post_init__(self) -> None:
+        if self.value_dim == 0:
+            object.__setattr__(self, "value_dim", self.key_dim)
+
+    @property
+    def head_dim(self) -> int:
+        """The one width of keys and values, for the kernels that need them equal."""
+        if self.key_dim != self.value_dim:
+            raise InvalidArgumentError(
+                f"this cache keeps keys of {self.key_dim} and values of {self.value_dim} values: it has no single head size")
+        return self.key_dim
 
     @property
     def group_key(self) -> tuple:
-        return ("paged", self.num_kv_heads, self.head_dim, self.window)
+        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window)
 
 
 @dataclass(frozen=True)
@@ -128,6 +143,8 @@ class _Request:
     tables: list[list[int]]                 # one block table per group; NULL_PAGE where a page was given back
     released_blocks: list[int]              # per group: blocks [0, n) were given back (window passed them)
     reserved: list[int]                     # per group: pages promised at admission, not yet drawn
+    reserve_tokens: int = 0                 # the positions the promise was made for (the prompt)
+    step_tokens: int = 1                    # the most positions a step brings, as promised at admission
     length: int = 0                         # positions covered by the tables
     computed: int = 0                       # positions whose entries have been written
     arrays: list = field(default_factory=list)   # the tables again as int32 arrays, grown in step with them
@@ -228,7 +245,8 @@ class CacheManager:
                 return False
         self._requests[request_id] = _Request(
             slot=self.slots.acquire(), tables=[[] for _ in self.groups],
-            released_blocks=[0 for _ in self.groups], reserved=wanted,
+            released_blocks=[0 for _ in self.groups], reserved=wanted, reserve_tokens=reserve_tokens,
+            step_tokens=step_tokens,
             arrays=[np.zeros(16, dtype=np.int32) for _ in self.groups])
         return True
 
@@ -279,7 +297,17 @@ class CacheManager:
                 for block in range(request.released_blocks[index], dead):
                     table[block] = NULL_PAGE
                 request.arrays[index][request.released_blocks[index]:dead] = NULL_PAGE
+                given_back = dead - request.released_blocks[index]
                 request.released_blocks[index] = dead
+                # While its prompt is still being computed the request keeps its claim at what it will
+                # hold at one time: the pages it has just given back stay promised to it, as far as it
+                # still needs them, so that newcomers admitted meanwhile cannot starve it.
+                if request.computed < request.reserve_tokens:
+                    bound = self._live_blocks_needed(group, request.reserve_tokens, request.step_tokens)
+                    to_come = self.blocks_for(request.reserve_tokens) - len(table)
+                    wanted = min(to_come, max(0, bound - (len(table) - dead)))
+                    if wanted > request.reserved[index]:
+                        request.reserved[index] = min(wanted, request.reserved[index] + given_back)
 
     def free_request(self, request_id: Hashable) -> None:
         """Give back everything the request holds: pages last-to-first, reservation, state slot."""

@@ -72,8 +72,6 @@ def build_parser() -> argparse.ArgumentParser:
     rand.add_argument("--seed", type=int, default=0)
     rand.add_argument("--out", type=Path, required=True)
     rand.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
-
-    commands.add_parser("serve", help="(not built: this engine has no server)")
     return parser
 
 
@@ -153,7 +151,4 @@ def main(argv: list[str] | None = None) -> int:
     args = parser.parse_args(argv)
     if args.command == "generate":
         return _generate(args, parser)
-    if args.command == "random-model":
-        return _random_model(args, parser)
-    print("zephyr_b200: servers are not part of this engine; use `generate` or the Python Engine class", file=sys.stderr)
-    return 2
+    return _random_model(args, parser)

@@ -5,11 +5,12 @@ from .qwen3 import Qwen3Config
 from .registry import (ArchitectureEntry, load_model_config, load_model_spec, read_config_json,
                        register_architecture, registered_architectures, resolve_architecture,
                        unregister_architecture)
-from .spec import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+from .spec import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, OutputSpec,
+                   PositionSpec)
 
 __all__ = [
-    "ArchitectureEntry", "ConfigError", "FeedForwardSpec", "InvalidArgumentError", "LayerCall", "LayerSpec",
-    "MixerSpec", "ModelSpec", "NormSpec", "OutOfPagesError", "PositionSpec", "Qwen3Config", "WeightError",
+    "ArchitectureEntry", "ConfigError", "FeedForwardSpec", "InputSpec", "InvalidArgumentError", "LayerCall", "LayerSpec",
+    "MixerSpec", "ModelSpec", "NormSpec", "OutOfPagesError", "OutputSpec", "PositionSpec", "Qwen3Config", "WeightError",
     "ZephyrError", "load_model_config", "load_model_spec", "read_config_json", "register_architecture",
     "registered_architectures", "resolve_architecture", "unregister_architecture",
 ]

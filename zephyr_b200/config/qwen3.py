@@ -3,14 +3,11 @@
 Keys, defaults and rejections follow the reference's
 ``Qwen3Config::Load`` (src/model/causal_lm/qwen3_config.cpp:16-102) and the
 validation in ``Qwen3Model::Load`` (src/model/causal_lm/qwen3.cpp:102-112).
-
-One deliberate difference: the reference rejects a configuration whose
-sliding window would reach a layer (qwen3_config.cpp:63-80).  The parts of
-this engine take a window as a parameter, so such a configuration is
-accepted here: layer ``i`` attends to the last ``sliding_window`` positions
-(itself included) when ``layer_types[i] == "sliding_attention"``, or, with
-no ``layer_types``, when ``use_sliding_window`` is set and
-``i >= max_window_layers``.
+Every layer is full causal attention: a sliding window that would reach a
+layer, and any ``layer_types`` entry other than ``"full_attention"``, are
+rejected as the reference rejects them (qwen3_config.cpp:63-80).  (The
+attention part and the cache manager do take a window as a parameter; no
+key of this architecture's config.json sets it.)
 """
 
 from __future__ import annotations
@@ -22,7 +19,8 @@ from pathlib import Path
 from typing import Any, Mapping
 
 from .errors import ConfigError
-from .spec import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+from .spec import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec, OutputSpec,
+                   PositionSpec)
 
 _INT64_MAX = 2**63 - 1
 
@@ -61,8 +59,6 @@ class Qwen3Config:
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1000000.0
     tie_word_embeddings: bool = False
-    # 0 = full causal attention in that layer; otherwise the number of positions seen, the query's own included.
-    layer_windows: tuple[int, ...] = ()
     eos_token_ids: tuple[int, ...] = ()
 
     architecture = "Qwen3ForCausalLM"
@@ -113,7 +109,7 @@ class Qwen3Config:
                 raise ConfigError(f"{where}: only full-head, unscaled rotary embeddings are supported")
             theta = _read_number(rope, "rope_theta", theta)
 
-        windows = cls._read_windows(config, layers, where)
+        cls._reject_windows(config, layers, where)
 
         eos = config.get("eos_token_id")
         if eos is None:
@@ -128,37 +124,25 @@ class Qwen3Config:
         result = cls(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=layers,
                      num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
                      max_position_embeddings=max_pos, rms_norm_eps=eps, rope_theta=theta,
-                     tie_word_embeddings=tied, layer_windows=windows, eos_token_ids=eos_ids)
+                     tie_word_embeddings=tied, eos_token_ids=eos_ids)
         result.validate(where)
         return result
 
     @staticmethod
-    def _read_windows(config: Mapping[str, Any], layers: int, where: str) -> tuple[int, ...]:
-        window = config.get("sliding_window")
-        if window is not None:
-            window = _read_dimension(config, "sliding_window")
+    def _reject_windows(config: Mapping[str, Any], layers: int, where: str) -> None:
+        """qwen3_config.cpp:62-80: a configured window has no effect until it is enabled on at least one
+        decoder layer (``max_window_layers`` below the layer count), and then it is refused; so is a
+        ``layer_types`` list that is not ``layers`` times "full_attention"."""
+        if config.get("use_sliding_window", False) and config.get("sliding_window") is not None:
+            first = _read_dimension(config, "max_window_layers") if "max_window_layers" in config else 0
+            if first < layers:
+                raise ConfigError(f"{where}: Qwen3 sliding-window attention is unsupported")
         layer_types = config.get("layer_types")
         if layer_types is not None:
             if not isinstance(layer_types, list) or len(layer_types) != layers:
-                raise ConfigError(f"{where}: 'layer_types' must describe every decoder layer")
-            out = []
-            for index, kind in enumerate(layer_types):
-                if kind == "full_attention":
-                    out.append(0)
-                elif kind == "sliding_attention":
-                    if window is None or window <= 0:
-                        raise ConfigError(
-                            f"{where}: layer {index} is 'sliding_attention' but 'sliding_window' is not a positive integer")
-                    out.append(window)
-                else:
-                    raise ConfigError(f"{where}: unknown layer type {kind!r} for layer {index}")
-            return tuple(out)
-        if config.get("use_sliding_window", False) and window is not None:
-            if window <= 0:
-                raise ConfigError(f"{where}: 'sliding_window' must be positive")
-            first = _read_dimension(config, "max_window_layers") if "max_window_layers" in config else 0
-            return tuple(window if index >= first else 0 for index in range(max(layers, 0)))
-        return tuple(0 for _ in range(max(layers, 0)))
+                raise ConfigError(f"{where}: Qwen3 layer_types must describe every decoder layer")
+            if any(kind != "full_attention" for kind in layer_types):
+                raise ConfigError(f"{where}: Qwen3 supports only full-attention decoder layers")
 
     @classmethod
     def from_file(cls, path: str | Path) -> "Qwen3Config":
@@ -185,8 +169,6 @@ class Qwen3Config:
             raise ConfigError(
                 f"{where}: Qwen3 requires positive dimensions, divisible Q/KV heads, an even head width, "
                 "and finite positive normalization/rotary parameters")
-        if len(self.layer_windows) != self.num_hidden_layers:
-            raise ConfigError(f"{where}: layer_windows must have one entry per layer")
         for token in self.eos_token_ids:
             if not 0 <= token < self.vocab_size:
                 raise ConfigError(f"{where}: eos token id {token} lies outside the vocabulary")
@@ -211,12 +193,7 @@ class Qwen3Config:
             "rope_theta": self.rope_theta,
             "tie_word_embeddings": self.tie_word_embeddings,
         }
-        if any(self.layer_windows):
-            out["use_sliding_window"] = True
-            out["sliding_window"] = max(self.layer_windows)
-            out["layer_types"] = ["sliding_attention" if w else "full_attention" for w in self.layer_windows]
-        else:
-            out["use_sliding_window"] = False
+        out["use_sliding_window"] = False
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return out
@@ -235,7 +212,7 @@ class Qwen3Config:
                 "num_heads": self.num_attention_heads,
                 "num_kv_heads": self.num_key_value_heads,
                 "head_dim": self.head_dim,
-                "window": self.layer_windows[index],
+                "window": 0,
                 "qk_norm_eps": self.rms_norm_eps,
                 "q_proj": f"{prefix}.self_attn.q_proj.weight",
                 "k_proj": f"{prefix}.self_attn.k_proj.weight",
@@ -253,21 +230,25 @@ class Qwen3Config:
             })
             layers.append(LayerSpec(
                 block="prenorm_residual", mixer=mixer, feed_forward=ffn,
-                mixer_norm=NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps,
-                                    f"{prefix}.input_layernorm.weight"),
-                feed_forward_norm=NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps,
-                                           f"{prefix}.post_attention_layernorm.weight")))
+                norms={"mixer": NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps,
+                                         f"{prefix}.input_layernorm.weight"),
+                       "feed_forward": NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps,
+                                                f"{prefix}.post_attention_layernorm.weight")}))
         embedding = "model.embed_tokens.weight"
         spec = ModelSpec(
             architecture=self.architecture,
             vocab_size=self.vocab_size,
             hidden_size=self.hidden_size,
             max_seq_len=self.max_position_embeddings,
-            embedding_weight=embedding,
+            input=InputSpec("embedding", {"weight": embedding, "vocab_size": self.vocab_size,
+                                          "hidden_size": self.hidden_size}),
             layers=tuple(layers),
             run_order=tuple(LayerCall(layer=i, cache=i) for i in range(self.num_hidden_layers)),
-            final_norm=NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps, "model.norm.weight"),
-            lm_head_weight=embedding if self.tie_word_embeddings else "lm_head.weight",
+            # A tied head reads the embedding table itself: the same tensor name (qwen3.cpp:134-136).
+            output=OutputSpec("norm_head", {
+                "norm": NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps, "model.norm.weight"),
+                "weight": embedding if self.tie_word_embeddings else "lm_head.weight",
+                "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}),
             eos_token_ids=self.eos_token_ids,
             # A tied checkpoint may still carry a copy of the head; the reference never reads it (qwen3.cpp:134).
             ignorable_weights=("lm_head.weight",) if self.tie_word_embeddings else (),

@@ -57,13 +57,32 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: which block arrangement, and the parts placed in it."""
+    """One layer: which block arrangement, and the parts placed in it.
+
+    ``norms`` holds the layer's norms under the names the block arrangement gives them: the pre-norm
+    residual block wants "mixer" and "feed_forward"; an arrangement with norms after its parts as
+    well would name four."""
 
     block: str         # key in parts.BLOCKS, e.g. "prenorm_residual"
     mixer: MixerSpec
     feed_forward: FeedForwardSpec
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    norms: Mapping[str, NormSpec]
+
+
+@dataclass(frozen=True)
+class InputSpec:
+    """What turns a step's token ids into the first hidden states (a table lookup here)."""
+
+    kind: str          # key in parts.INPUTS, e.g. "embedding"
+    params: Mapping[str, Any]
+
+
+@dataclass(frozen=True)
+class OutputSpec:
+    """What turns the last hidden states of the wanted tokens into float32 logits."""
+
+    kind: str          # key in parts.OUTPUTS, e.g. "norm_head"
+    params: Mapping[str, Any]
 
 
 @dataclass(frozen=True)
@@ -88,17 +107,12 @@ class ModelSpec:
     vocab_size: int
     hidden_size: int
     max_seq_len: int
-    embedding_weight: str
+    input: InputSpec
     layers: tuple[LayerSpec, ...]
     run_order: tuple[LayerCall, ...]
-    final_norm: NormSpec
-    lm_head_weight: str            # equals ``embedding_weight`` when the head is tied
+    output: OutputSpec
     eos_token_ids: tuple[int, ...] = ()
     ignorable_weights: tuple[str, ...] = ()   # names a checkpoint may carry that are not read
-
-    @property
-    def tied_head(self) -> bool:
-        return self.lm_head_weight == self.embedding_weight
 
     @property
     def num_caches(self) -> int:

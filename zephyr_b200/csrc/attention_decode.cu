@@ -1010,10 +1010,17 @@ float* no_alloc_scratch_for_current_device() {
 
 }  // namespace
 
-ZB_API long long zb_paged_decode_no_alloc_bytes_needed(int n_rows, int nh, int hd, int max_splits) {
-  // Partial results, plus the arrival counters (at most one per row and head) rounded up to 256 bytes.
-  return zb_paged_decode_scratch_floats(n_rows, nh, hd, max_splits) * static_cast<long long>(sizeof(float)) +
-         (static_cast<long long>(n_rows) * nh * 4 + 255) / 256 * 256;
+ZB_API long long zb_paged_decode_no_alloc_bytes_needed(int n_rows, int nh, int nkv, int hd, int split_size,
+                                                       int max_splits) {
+  if (n_rows < 0 || nh <= 0 || nkv <= 0 || nkv > nh || hd <= 0 || split_size < 0 || max_splits <= 0) return -1;
+  // The arrival counters (one per row and key/value head, rounded up to 256 bytes), then the partial
+  // results.  How many of those there are depends on how the work is cut: fixed splits keep one per
+  // (row, head, split); balanced items (split_size 0) keep two per CTA and query head of a group,
+  // whatever the rows and max_splits are.
+  const long long counter_bytes = (static_cast<long long>(n_rows) * nkv * 4 + 255) / 256 * 256;
+  const long long floats = split_size > 0 ? zb_paged_decode_scratch_floats(n_rows, nh, hd, max_splits)
+                                          : zb_paged_decode_balanced_scratch_floats(nh, nkv, hd);
+  return counter_bytes + floats * static_cast<long long>(sizeof(float));
 }
 
 ZB_API const char* zb_paged_decode_no_alloc_error(int code) {
@@ -1023,9 +1030,10 @@ ZB_API const char* zb_paged_decode_no_alloc_error(int code) {
     case ERR_CUDA: return "the CUDA launch failed";
     case ERR_UNSUPPORTED: return "this head size, group size or type is not supported by the decode kernel";
     case ZB_ERR_SCRATCH_TOO_SMALL:
-      return "the problem needs more than the 4 MiB of built-in scratch: n_rows * heads * max_splits * "
-             "(head_dim + 2) * 4 bytes must not exceed ZB_NO_ALLOC_SCRATCH_BYTES; use zb_paged_decode with a buffer "
-             "of your own, or split the rows over several calls";
+      return "the problem needs more than the 4 MiB of built-in scratch (zb_paged_decode_no_alloc_bytes_needed "
+             "says how much: with fixed splits n_rows * heads * max_splits * (head_dim + 2) * 4 bytes, with balanced "
+             "items 2 * 256 * (heads / kv_heads) * (head_dim + 2) * 4 bytes); use zb_paged_decode with a buffer of "
+             "your own, or split the rows over several calls";
     case ZB_ERR_SCRATCH_ADDRESS: return "the device address of the built-in scratch array could not be looked up";
     default: return "unknown code";
   }
@@ -1036,9 +1044,11 @@ ZB_API int zb_paged_decode_no_alloc(void* out, const void* q, const void* kv_cac
                                     int n_rows, const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd,
                                     int window, float scale, int split_size, int max_splits, int* status,
                                     void* stream) {
-  if (n_rows < 0 || nh <= 0 || nkv <= 0 || nkv > nh || hd <= 0 || max_splits <= 0) return ERR_BAD_ARGUMENT;
-  if (zb_paged_decode_no_alloc_bytes_needed(n_rows, nh, hd, max_splits) > static_cast<long long>(ZB_NO_ALLOC_SCRATCH_BYTES))
-    return ZB_ERR_SCRATCH_TOO_SMALL;
+  // The bound depends on how the work is cut (split_size), exactly as the kernel lays its partial
+  // results out; it is checked before anything is cleared or launched.
+  const long long needed = zb_paged_decode_no_alloc_bytes_needed(n_rows, nh, nkv, hd, split_size, max_splits);
+  if (needed < 0) return ERR_BAD_ARGUMENT;
+  if (needed > static_cast<long long>(ZB_NO_ALLOC_SCRATCH_BYTES)) return ZB_ERR_SCRATCH_TOO_SMALL;
   float* scratch = no_alloc_scratch_for_current_device();
   if (scratch == nullptr) return ZB_ERR_SCRATCH_ADDRESS;
   // The array's head holds the arrival counters of the (row, key/value head) pairs, its rest the

@@ -7,10 +7,17 @@
 // scratch buffer for the partial results of the context splits, which such a caller could not
 // provide; here the scratch is a fixed array that is part of the library image itself.
 //
-// Limit: the partial results and the arrival counters must fit ZB_NO_ALLOC_SCRATCH_BYTES (4 MiB):
-//     n_rows * num_heads * (max_splits * (head_dim + 2) + 1) * 4 bytes (+ up to 255) <= 4 MiB,
-// for example 31 rows of 16 heads of size 128 at 4,096 tokens of context (16 splits of 256).
-// A larger problem is refused with ZB_ERR_SCRATCH_TOO_SMALL and nothing is launched.
+// Limit: the arrival counters and the partial results must fit ZB_NO_ALLOC_SCRATCH_BYTES (4 MiB).
+// How much that is depends on how the work is cut, as in zb_paged_decode:
+//     split_size > 0 (fixed splits):   n_rows * num_kv_heads * 4 (rounded up to 256)
+//                                      + n_rows * num_heads * max_splits * (head_dim + 2) * 4 bytes,
+//         for example 31 rows of 16 heads of size 128 at 4,096 tokens of context (16 splits of 256);
+//     split_size == 0 (balanced items): the same counters
+//                                      + 2 * 256 * (num_heads / num_kv_heads) * (head_dim + 2) * 4 bytes,
+//         whatever n_rows and max_splits are: groups of up to 15 query heads at head size 128 fit, a
+//         group of 16 does not.
+// zb_paged_decode_no_alloc_bytes_needed gives the figure.  A larger problem is refused with
+// ZB_ERR_SCRATCH_TOO_SMALL before anything is cleared or launched.
 // Every GPU on which the library is loaded holds these 4 MiB until the process exits.
 //
 // The first call on a device looks up the array's device address (once per device, with that
@@ -39,8 +46,9 @@ int zb_paged_decode_no_alloc(void* out, const void* q, const void* kv_cache, con
                              const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
                              float scale, int split_size, int max_splits, int* status, void* stream);
 
-/* Bytes of scratch a problem needs (compare with ZB_NO_ALLOC_SCRATCH_BYTES before calling). */
-long long zb_paged_decode_no_alloc_bytes_needed(int n_rows, int nh, int hd, int max_splits);
+/* Bytes of scratch a problem needs (compare with ZB_NO_ALLOC_SCRATCH_BYTES before calling); -1 for
+   arguments outside the contract. */
+long long zb_paged_decode_no_alloc_bytes_needed(int n_rows, int nh, int nkv, int hd, int split_size, int max_splits);
 
 /* A sentence for a return code of zb_paged_decode_no_alloc. */
 const char* zb_paged_decode_no_alloc_error(int code);

@@ -103,6 +103,7 @@ class Engine:
         self.generation_defaults = self._read_generation_defaults(model) if model is not None else {}
         store = weights if weights is not None else Checkpoint(model)
         self.model = Model.load(spec, store, self.dtype, self.device)
+        torch.cuda.empty_cache()        # loading may hold copies (fused matrices) that it no longer needs
         _LOGGER.info("model ready: %s, %s, %.2f s", spec.architecture, self.dtype, time.perf_counter() - started)
 
         limit = spec.max_seq_len if max_seq_len in (0, None) else min(max_seq_len, spec.max_seq_len)
@@ -157,23 +158,29 @@ class Engine:
 
     def _size_cache(self, kv_cache: KvCacheOptions, utilization: float, max_seq_len: int) -> int:
         """Number of pages: given, or what ``memory_bytes`` buys, or what is left of
-        ``gpu_memory_utilization`` x total memory after the weights, with room kept for one step's
-        activations (the reference profiles its peak instead, src/executor/causal_lm.cpp:495-537)."""
+        ``gpu_memory_utilization`` x total memory after the weights and after what a step needs at its
+        peak.  That peak is measured, as the reference measures its own (src/executor/causal_lm.cpp:
+        301-425,495-537): ``_profile_step_peak`` runs the largest prompt portion and the largest decode
+        batch the scheduler may form and reads the allocator's high-water mark."""
         block = kv_cache.block_size
         if block <= 0 or block & (block - 1):
             raise ConfigError("kv_cache.block_size must be a power of two")
+        self.profiled_step_bytes = None
         if kv_cache.num_blocks is not None:
             pages = int(kv_cache.num_blocks)
         else:
             if kv_cache.memory_bytes is not None:
                 budget = int(kv_cache.memory_bytes)
             else:
+                self.profiled_step_bytes = self._profile_step_peak(block, max_seq_len)
+                torch.cuda.empty_cache()        # what loading and profiling left cached goes back first
                 free, total = torch.cuda.mem_get_info(self.device)
                 used = total - free
-                tokens = self.scheduler_config.max_num_batched_tokens
-                spec = self.model.spec
-                transient = 8 * tokens * max(spec.hidden_size * 16, 1) * 4 \
-                    + 4 * self.scheduler_config.max_num_seqs * spec.vocab_size * 4 + (512 << 20)
+                # Twice the measured peak: a step that runs launch by launch and the same step's captured
+                # graph (all graphs share one memory pool) each hold their activations.  Beside it the
+                # selection's buffers (a few rows of the vocabulary per sequence) and a fixed reserve.
+                transient = 2 * self.profiled_step_bytes \
+                    + 4 * self.scheduler_config.max_num_seqs * self.model.spec.vocab_size * 4 + (256 << 20)
                 budget = min(free - max(512 << 20, total // 50), int(utilization * total) - used) - transient
             pages = ModelRunner.pages_for_memory(self.model, block, max(budget, 0))
             # No use holding more pages than every resident sequence at full length can fill.
@@ -182,6 +189,34 @@ class Engine:
         if pages < 2:
             raise ConfigError("the cache pool has no room for a single page; lower max_seq_len or free memory")
         return pages
+
+    def _profile_step_peak(self, block: int, max_seq_len: int) -> int:
+        """Bytes the allocator holds at the peak of a step beyond what is resident: the largest prompt
+        step the scheduler may form (``max_num_batched_tokens`` tokens, spread over as many sequences
+        as it takes when one sequence cannot be that long), then one decode step of ``max_num_seqs``
+        sequences, on a throw-away pool just large enough for them."""
+        seqs = self.scheduler_config.max_num_seqs
+        portion = max(1, min(self.scheduler_config.max_prefill_chunk_tokens, max_seq_len))
+        tokens = max(1, min(self.scheduler_config.max_num_batched_tokens, seqs * portion))
+        portions = [portion] * (tokens // portion) + ([tokens % portion] if tokens % portion else [])
+        pages = sum(-(-n // block) for n in portions) + seqs + 2
+        runner = ModelRunner(self.model, block, pages, seqs + 1, max_seq_len=max_seq_len, use_cuda_graphs=False)
+        torch.cuda.synchronize(self.device)
+        torch.cuda.reset_peak_memory_stats(self.device)
+        base = torch.cuda.memory_allocated(self.device)
+        rows = [("profile", index) for index in range(seqs)]
+        for row in rows[:len(portions)]:
+            runner.add_request(row)
+        runner.step([StepEntry(row, [0] * n, (n - 1,)) for row, n in zip(rows, portions)])
+        for row in rows[:len(portions)]:
+            runner.free_request(row)
+        for row in rows:
+            runner.add_request(row)
+        runner.step([StepEntry(row, [0], (0,)) for row in rows])
+        runner.check()
+        peak = torch.cuda.max_memory_allocated(self.device) - base
+        _LOGGER.info("a step of %d tokens holds %.1f MiB at its peak", tokens, peak / 2**20)
+        return max(int(peak), 0)
 
     # ---------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: GenerationParams | None = None) -> int:

@@ -59,6 +59,7 @@ class ModelRunner:
         self.use_cuda_graphs = use_cuda_graphs
         self._graphs: OrderedDict = OrderedDict()      # graph key -> captured step
         self._shapes_seen: dict = {}                   # graph key -> times seen before its capture
+        self._graph_pool = None                        # one memory pool for all captured steps (made at the first capture)
         self.last_step_h2d_bytes = 0     # bytes of the last step's description copied to the device
 
     # ------------------------------------------------------------------ sizing
@@ -204,14 +205,15 @@ class ModelRunner:
         """A step whose shape comes again replays a captured CUDA graph: the launches of a whole step
         become one.  The key fixes everything a launch bakes in: the number of new tokens of every row
         and the wanted places (they size every grid and buffer), and a power-of-two bound on the
-        context of the rows with one new token (it sizes the decode attention's grid).  What a step
+        context of the rows with one new token, if the model keeps a paged cache at all (it sizes the
+        decode attention's grid).  What a step
         reads beyond that (tokens, positions, contexts, block tables) it reads from the device.
         Decode-only steps are captured at once; any other shape when it is seen a second time."""
         if not self.use_cuda_graphs or not self.model.graph_safe:
             return None
         singles = [self.manager.computed(e.request_id) + 1 for e in entries if len(e.tokens) == 1]
         bound = 0
-        if singles:
+        if singles and self.manager.groups:       # a model without a paged cache has no context to bound
             bound = max(ops.DECODE_SPLIT_SIZE, 1 << (max(singles) - 1).bit_length())
             bound = min(bound, max(self.max_seq_len, ops.DECODE_SPLIT_SIZE))
         if len(singles) == len(entries) and all(tuple(e.want) == (0,) for e in entries):
@@ -324,7 +326,13 @@ class ModelRunner:
             torch.cuda.current_stream(self.device).wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             launched = ops.LAUNCHES
-            with torch.cuda.graph(graph):
+            # All graphs of this runner draw from one pool: they replay one after the other on one stream,
+            # so a graph's intermediate buffers may lie where another graph's lay, and the pool grows to
+            # the largest step, not to the sum of all captured steps.  A graph's logits stay its own for as
+            # long as the record holds them.
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 record["logits"] = self.model.forward(ctx)
             record["kernels"] = ops.LAUNCHES - launched     # this package's kernels inside the graph
             record["graph"] = graph

@@ -161,9 +161,10 @@ class Scheduler:
                           key=lambda i: self.sequences[i].arrival)
         budget = self.config.max_num_batched_tokens
         if len(decoders) > budget:      # more decoders than budget: take turns
-            start = self._decode_cursor % len(decoders)
+            count = len(decoders)
+            start = self._decode_cursor % count
             decoders = (decoders[start:] + decoders[:start])[:budget]
-            self._decode_cursor = (start + budget) % max(len(decoders), 1)
+            self._decode_cursor = (start + budget) % count
         used = 0
         for sequence_id in decoders:
             if sequence_id not in self.running:      # preempted a moment ago to make room for an older one

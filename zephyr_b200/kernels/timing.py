@@ -5,6 +5,7 @@
     python -m zephyr_b200.kernels.timing gemm_small --rows 8 --n 6144 --k 1024 [--swiglu]
     python -m zephyr_b200.kernels.timing fused_chain --rows 8 --hidden 1024 --ffn 3072
     python -m zephyr_b200.kernels.timing sample --rows 8 --vocab 151936
+    python -m zephyr_b200.kernels.timing products --tokens 2048 --hidden 1024 --ffn 3072
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
 that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
@@ -223,21 +224,54 @@ def fused_chain(args) -> dict:
     status = ops.new_status(device)
     trace = torch.zeros((ops.fused_chain_grid(), 4, 4), dtype=torch.int32, device=device)
 
-    def run(i):
+    def stages(i):
         w_o, w_gu, w_down, w_qkv = layers[i % len(layers)]
-        ops.fused_chain([ops.ChainStage(w=w_o, y=o, x=attn),
-                         ops.ChainStage(w=w_gu, y=act, residual_in=residual, residual_out=r1, delta=o, norm_w=norm, eps=1e-6, swiglu=True),
-                         ops.ChainStage(w=w_down, y=down, x=act),
-                         ops.ChainStage(w=w_qkv, y=out, residual_in=r1, residual_out=r2, delta=down, norm_w=norm, eps=1e-6)],
-                        M, status, trace=trace)
+        return [ops.ChainStage(w=w_o, y=o, x=attn),
+                ops.ChainStage(w=w_gu, y=act, residual_in=residual, residual_out=r1, delta=o, norm_w=norm, eps=1e-6, swiglu=True),
+                ops.ChainStage(w=w_down, y=down, x=act),
+                ops.ChainStage(w=w_qkv, y=out, residual_in=r1, residual_out=r2, delta=down, norm_w=norm, eps=1e-6)]
+
+    whole = all(ops.fused_chain_stage_supported(M, st.w, st.norm_w is not None, st.swiglu) for st in stages(0))
+    if whole:
+        def run(i):
+            ops.fused_chain(stages(i), M, status, trace=trace)
+    else:
+        # A stage whose input does not fit in shared memory (the down projection of a wide model) runs as
+        # kernels of its own between two shorter chains, as in a model's step.
+        from ..parts.fused import run_stages
+
+        def run(i):
+            run_stages(stages(i), M, status)
     us = _time(run, args.warmup, args.iters)
     ops.check_status(status, "fused_chain")
-    return {"kernel": "fused_chain_kernel", "rows": M, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv, "us": round(us, 2),
-            "bytes_read": layer_bytes, "gbs": round(layer_bytes / us / 1e3, 1),
-            "timeline_ns": _chain_timeline(trace)}
+    return {"kernel": "fused_chain_kernel" if whole else "fused_chain_kernel + gemm_small_kernel", "rows": M, "hidden": d,
+            "q": q, "ffn": ffn, "qkv": qkv, "us": round(us, 2), "bytes_read": layer_bytes,
+            "gbs": round(layer_bytes / us / 1e3, 1), "timeline_ns": _chain_timeline(trace) if whole else {}}
 
 
-CASES = {"fused_chain": fused_chain, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
+def products(args) -> dict:
+    """A layer's four matrix products for a prompt portion of ``--tokens`` tokens, as the engine runs
+    them (the vendor library's tensor-core product for bfloat16 beyond 16 rows)."""
+    device = torch.device("cuda")
+    T, d, q, ffn, qkv = args.tokens, args.hidden, args.heads * args.head_dim, args.ffn, (args.heads + 2 * args.kv_heads) * args.head_dim
+    layer_bytes = 2 * (d * q + 2 * ffn * d + d * ffn + qkv * d)
+    rnd = lambda *shape: torch.randn(shape, device=device, dtype=torch.bfloat16) * 0.05
+    layers = [(rnd(qkv, d), rnd(d, q), rnd(2 * ffn, d), rnd(d, ffn)) for _ in range(_copies(layer_bytes))]
+    x, attn, act = rnd(T, d), rnd(T, q), rnd(T, ffn)
+
+    def run(i):
+        w_qkv, w_o, w_gu, w_down = layers[i % len(layers)]
+        ops.linear(x, w_qkv)
+        ops.linear(attn, w_o)
+        ops.linear(x, w_gu)
+        ops.linear(act, w_down)
+    us = _time(run, args.warmup, args.iters)
+    flops = 2.0 * T * (qkv * d + d * q + 2 * ffn * d + d * ffn)
+    return {"kernel": "library products (cuBLASLt)", "tokens": T, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv,
+            "us": round(us, 2), "flops": flops, "tflops": round(flops / us / 1e6, 1)}
+
+
+CASES = {"fused_chain": fused_chain, "products": products, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
          "sample": sample}
 
 

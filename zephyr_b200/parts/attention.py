@@ -6,8 +6,9 @@ j // (heads / kv_heads); scale 1/sqrt(head_dim); causal, with an optional window
 concatenated in order and projected by Wo (reference: src/model/causal_lm/qwen3.cpp:17-69).
 
 The three projections run as one product over the row-concatenated weight.  Per-head norm, rotation
-and the cache write are one kernel when the position encoding is the NeoX rotation (or none);
-any other encoding goes through its own ``apply`` and separate norm and write kernels.
+and the cache write are one kernel when the position encoding offers rotation tables
+(``PositionEncoding.as_rotation_tables``: the NeoX rotation, or no encoding at all); any other
+encoding goes through its own ``apply`` and separate norm and write kernels.
 """
 
 from __future__ import annotations
@@ -55,8 +56,12 @@ class Attention(Mixer):
                 spec.position, dtype, device)
         else:
             self.position = None
-        kind = getattr(self.position, "kind", None) if self.position is not None else "none"
-        self.fused_position = kind in ("rope_neox", "none")
+        # The fused kernels (norm + rotation + cache write, and the decode attention that does all of it
+        # itself) rotate NeoX pairs by per-position angles from float32 tables; an encoding says whether
+        # it is one of those, and any other goes through its own ``apply``.
+        tables = self.position.as_rotation_tables() if self.position is not None else (None, None)
+        self.fused_position = tables is not None
+        self.cos, self.sin = tables if tables is not None else (None, None)
         self.group = self.nh // self.nkv
         self.tile_tokens = ops.attention_tile_tokens(self.group)
         self.fast_decode = ops.paged_decode_supported(self.nh, self.nkv, self.hd, dtype)
@@ -83,10 +88,14 @@ class Attention(Mixer):
             decls[p["k_norm"]] = WeightDecl((hd,), ROLE_NORM)
         return decls
 
+    def weights_read(self) -> list[torch.Tensor]:
+        return [t for t in (self.w_qkv, self.w_o, self.q_norm, self.k_norm) if t is not None]
+
     @staticmethod
     def cache_spec(spec: MixerSpec) -> PagedCacheSpec:
         p = spec.params
-        return PagedCacheSpec(int(p["num_kv_heads"]), int(p["head_dim"]), int(p.get("window", 0)))
+        return PagedCacheSpec(int(p["num_kv_heads"]), key_dim=int(p["head_dim"]), value_dim=int(p["head_dim"]),
+                              window=int(p.get("window", 0)))
 
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
@@ -99,8 +108,7 @@ class Attention(Mixer):
         """Per-head norm, rotation and cache write in one kernel; returns the queries."""
         nh, nkv, hd = self.nh, self.nkv, self.hd
         table = ctx.block_table(call.cache)
-        cos = getattr(self.position, "cos", None)
-        sin = getattr(self.position, "sin", None)
+        cos, sin = self.cos, self.sin
         if call.writes_cache:
             return ops.qk_norm_rope_cache(projected, nh, nkv, hd, self.q_norm, self.k_norm, self.eps, cos, sin,
                                           ctx.positions, ctx.token_row, ctx.caches[call.cache], table, ctx.status)
@@ -180,8 +188,7 @@ class Attention(Mixer):
             return ops.paged_decode_fused(
                 projected, ctx.caches[call.cache], ctx.block_table(call.cache), ctx.decode_rows, ctx.row_q_start,
                 ctx.row_ctx, ctx.max_decode_context, self.nh, self.nkv, self.hd, self.window, self.scale, self.q_norm,
-                self.k_norm, self.eps, getattr(self.position, "cos", None), getattr(self.position, "sin", None),
-                ctx.status, out)
+                self.k_norm, self.eps, self.cos, self.sin, ctx.status, out)
         return self.attend(self._store_projected(projected, ctx, call), ctx, call)
 
     def _decodes_in_one(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall) -> bool:

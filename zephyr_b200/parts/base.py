@@ -19,7 +19,7 @@ import torch
 
 from ..cache import CacheStorage, PagedCacheSpec, StateCacheSpec
 from ..config.errors import ConfigError
-from ..config.spec import FeedForwardSpec, LayerCall, MixerSpec, NormSpec, PositionSpec
+from ..config.spec import FeedForwardSpec, InputSpec, LayerCall, MixerSpec, NormSpec, OutputSpec, PositionSpec
 from ..weights.loader import WeightDecl
 
 
@@ -106,6 +106,13 @@ class PositionEncoding(Part):
         """Encode positions into ``x`` [T, heads*head_dim] in place and return it."""
         raise NotImplementedError
 
+    def as_rotation_tables(self) -> tuple[torch.Tensor | None, torch.Tensor | None] | None:
+        """What a kernel that encodes positions itself needs.  (cos, sin), float32
+        [max_positions, head_dim/2] on the device, if the encoding rotates the pairs (i, i + head_dim/2)
+        of every head by the angle of the token's position; (None, None) if it leaves queries and keys
+        as they are; None for anything else, which is then applied through ``apply``."""
+        return None
+
 
 class Mixer(Part):
     def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
@@ -167,7 +174,10 @@ class ResidualStream:
 class Block(Part):
     """The arrangement of a layer's parts around the residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm): ...
+    # The names of the norms this arrangement places, in ``LayerSpec.norms``.
+    norm_names: tuple[str, ...] = ()
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Mapping[str, Norm]): ...
 
     def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
         raise NotImplementedError
@@ -178,7 +188,30 @@ class Block(Part):
         return None
 
 
+class InputPart(Part):
+    """Token ids to the first hidden states."""
+
+    def __init__(self, spec: InputSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """[T, hidden] in the model's type for the step's tokens (``ctx.token_ids``)."""
+        raise NotImplementedError
+
+
+class OutputPart(Part):
+    """The last hidden states of the wanted tokens to logits."""
+
+    def __init__(self, spec: OutputSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
+
+    def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
+        """float32 logits [wanted, vocab] for the tokens ``ctx.logit_tokens`` names (indices into the
+        step's token stream), in that order.  ``stream`` may carry a pending summand."""
+        raise NotImplementedError
+
+
 NORMS: dict[str, type] = {}
+INPUTS: dict[str, type] = {}
+OUTPUTS: dict[str, type] = {}
 POSITION_ENCODINGS: dict[str, type] = {}
 MIXERS: dict[str, type] = {}
 FEED_FORWARDS: dict[str, type] = {}
@@ -209,6 +242,14 @@ def register_feed_forward(kind: str, cls: type, replace: bool = False) -> None:
 
 def register_block(kind: str, cls: type, replace: bool = False) -> None:
     _register(BLOCKS, "block", kind, cls, replace)
+
+
+def register_input(kind: str, cls: type, replace: bool = False) -> None:
+    _register(INPUTS, "input part", kind, cls, replace)
+
+
+def register_output(kind: str, cls: type, replace: bool = False) -> None:
+    _register(OUTPUTS, "output part", kind, cls, replace)
 
 
 def lookup(table: dict[str, type], what: str, kind: str) -> type:

@@ -7,6 +7,8 @@ it, so the block hands its last summand on as ``pending``.
 
 from __future__ import annotations
 
+from typing import Mapping
+
 from ..config.spec import LayerCall
 from .base import Block, FeedForward, Mixer, Norm, ResidualStream, StepContext, register_block
 from .fused import BlockPlan
@@ -15,11 +17,14 @@ from .fused import BlockPlan
 class PreNormResidual(Block):
     graph_safe = True
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    norm_names = ("mixer", "feed_forward")
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Mapping[str, Norm]):
         self.mixer = mixer
         self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        self.norms = dict(norms)
+        self.mixer_norm = norms["mixer"]
+        self.feed_forward_norm = norms["feed_forward"]
 
     def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
         if stream.pending is None:

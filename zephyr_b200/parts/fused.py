@@ -41,6 +41,29 @@ class BlockPlan:
     w_down: torch.Tensor
 
 
+def run_stages(stages: list, tokens: int, status: torch.Tensor) -> None:
+    """The stages in order: runs of stages the chain kernel takes as one launch each, the others
+    as kernels of their own (norm, product, activation) that leave the same tensors behind."""
+    run: list = []
+    for stage in stages:
+        if ops.fused_chain_stage_supported(tokens, stage.w, stage.norm_w is not None, stage.swiglu):
+            run.append(stage)
+            continue
+        if run:
+            ops.fused_chain(run, tokens, status)
+            run = []
+        if stage.norm_w is None:
+            x = stage.x
+        elif stage.delta is None:
+            x = ops.rmsnorm(stage.residual_in, stage.norm_w, stage.eps)
+        else:
+            stage.residual_out.copy_(stage.residual_in)
+            x = ops.add_rmsnorm(stage.residual_out, stage.delta, stage.norm_w, stage.eps)
+        stage.y.copy_(ops.gemm_small(x, stage.w, swiglu=stage.swiglu))
+    if run:
+        ops.fused_chain(run, tokens, status)
+
+
 class DecodeChains:
     """The fused path of a whole model for steps of up to ``ops.FUSED_CHAIN_MAX_TOKENS`` tokens."""
 
@@ -90,28 +113,6 @@ class DecodeChains:
             self._supported[tokens] = known
         return known
 
-    def _run(self, stages: list, tokens: int, status: torch.Tensor) -> None:
-        """The stages in order: runs of stages the chain kernel takes as one launch each, the others
-        as kernels of their own (norm, product, activation) that leave the same tensors behind."""
-        run: list = []
-        for stage in stages:
-            if ops.fused_chain_stage_supported(tokens, stage.w, stage.norm_w is not None, stage.swiglu):
-                run.append(stage)
-                continue
-            if run:
-                ops.fused_chain(run, tokens, status)
-                run = []
-            if stage.norm_w is None:
-                x = stage.x
-            elif stage.delta is None:
-                x = ops.rmsnorm(stage.residual_in, stage.norm_w, stage.eps)
-            else:
-                stage.residual_out.copy_(stage.residual_in)
-                x = ops.add_rmsnorm(stage.residual_out, stage.delta, stage.norm_w, stage.eps)
-            stage.y.copy_(ops.gemm_small(x, stage.w, swiglu=stage.swiglu))
-        if run:
-            ops.fused_chain(run, tokens, status)
-
     def forward(self, hidden: torch.Tensor, ctx) -> tuple[torch.Tensor, torch.Tensor]:
         """Runs all layers on ``hidden`` [T, H] (the embeddings).  Returns (residual, pending): the
         stream before the last feed-forward's output has been added, and that output."""
@@ -124,7 +125,7 @@ class DecodeChains:
         plan = self.plans[first.layer]
         w_in, _ = plan.mixer.projections(first)
         projected = new(w_in.shape[0])
-        self._run([ops.ChainStage(w=w_in, y=projected, residual_in=hidden, norm_w=plan.mixer_norm[0],
+        run_stages([ops.ChainStage(w=w_in, y=projected, residual_in=hidden, norm_w=plan.mixer_norm[0],
                                   eps=plan.mixer_norm[1])], T, ctx.status)
         for index, call in enumerate(self.run_order):
             plan = self.plans[call.layer]
@@ -139,7 +140,7 @@ class DecodeChains:
                 ops.ChainStage(w=plan.w_down, y=down, x=act),
             ]
             if index + 1 == len(self.run_order):
-                self._run(stages, T, ctx.status)
+                run_stages(stages, T, ctx.status)
                 return residuals[after_mixer], down
             following = self.run_order[index + 1]
             next_plan = self.plans[following.layer]
@@ -148,6 +149,6 @@ class DecodeChains:
             stages.append(ops.ChainStage(w=w_next, y=projected, residual_in=residuals[after_mixer],
                                          residual_out=residuals[after_ffn], delta=down, norm_w=next_plan.mixer_norm[0],
                                          eps=next_plan.mixer_norm[1]))
-            self._run(stages, T, ctx.status)
+            run_stages(stages, T, ctx.status)
             current = after_ffn
         raise AssertionError("unreachable: the run order is not empty")

@@ -1,11 +1,7 @@
-"""A model put together from parts, as its spec says: embedding, the layers in their run order,
-final norm, and the vocabulary projection for the tokens whose logits are wanted
-(reference forward: src/model/causal_lm/qwen3.cpp:152-181).
-
-Differences from the reference's order of work, none of which changes the math: the final norm
-runs on the wanted rows only (it is row-wise; the reference norms every token and selects after,
-qwen3.cpp:173-174), and the logits come out in float32 whatever the model's type (the reference
-stores them in the model's type, qwen3.cpp:175-180).
+"""A model put together from parts, as its spec says: an input part (token ids to hidden states),
+the layers in their run order, and an output part (hidden states of the wanted tokens to float32
+logits).  For the one architecture built here these are the embedding, the decoder layers, and the
+final norm with the vocabulary projection (reference forward: src/model/causal_lm/qwen3.cpp:152-181).
 """
 
 from __future__ import annotations
@@ -18,37 +14,42 @@ from ..cache import PagedCacheSpec, StateCacheSpec
 from ..config.errors import ConfigError
 from ..config.spec import LayerSpec, ModelSpec
 from ..kernels import ops
-from ..weights.loader import ROLE_EMBEDDING, ROLE_LINEAR, WeightDecl, WeightStore, load_weights
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, ResidualStream, StepContext, lookup)
+from ..weights.loader import WeightDecl, WeightStore, load_weights
+from .base import (BLOCKS, FEED_FORWARDS, INPUTS, MIXERS, NORMS, OUTPUTS, ResidualStream, StepContext, lookup)
 from .fused import DecodeChains
 
 
 def _layer_classes(layer: LayerSpec):
-    return (lookup(BLOCKS, "block", layer.block), lookup(MIXERS, "mixer", layer.mixer.kind),
+    block = lookup(BLOCKS, "block", layer.block)
+    wanted, given = set(getattr(block, "norm_names", ())), set(layer.norms)
+    if wanted and wanted != given:
+        raise ConfigError(f"block '{layer.block}' places the norms {sorted(wanted)}, the layer brings {sorted(given)}")
+    return (block, lookup(MIXERS, "mixer", layer.mixer.kind),
             lookup(FEED_FORWARDS, "feed-forward", layer.feed_forward.kind),
-            lookup(NORMS, "norm", layer.mixer_norm.kind), lookup(NORMS, "norm", layer.feed_forward_norm.kind))
+            {name: lookup(NORMS, "norm", norm.kind) for name, norm in layer.norms.items()})
 
 
 def expected_weights(spec: ModelSpec) -> dict[str, WeightDecl]:
-    """Every tensor the model reads, by full name."""
-    decls: dict[str, WeightDecl] = {
-        spec.embedding_weight: WeightDecl((spec.vocab_size, spec.hidden_size), ROLE_EMBEDDING)}
-    if not spec.tied_head:
-        decls[spec.lm_head_weight] = WeightDecl((spec.vocab_size, spec.hidden_size), ROLE_LINEAR)
+    """Every tensor the model reads, by full name.  A name declared by two parts (a head tied to the
+    embedding) must have one shape; it keeps the role of its first declaration."""
+    decls: dict[str, WeightDecl] = {}
 
     def merge(new: dict[str, WeightDecl]) -> None:
         for name, decl in new.items():
-            if name in decls and decls[name] != decl:
-                raise ConfigError(f"tensor '{name}' is declared twice with different shapes")
+            if name in decls:
+                if decls[name].shape != decl.shape:
+                    raise ConfigError(f"tensor '{name}' is declared twice with different shapes")
+                continue
             decls[name] = decl
 
+    merge(lookup(INPUTS, "input part", spec.input.kind).weight_decls(spec.input))
     for layer in spec.layers:
-        _, mixer, ffn, norm1, norm2 = _layer_classes(layer)
+        _, mixer, ffn, norms = _layer_classes(layer)
         merge(mixer.weight_decls(layer.mixer))
         merge(ffn.weight_decls(layer.feed_forward))
-        merge(norm1.weight_decls(layer.mixer_norm))
-        merge(norm2.weight_decls(layer.feed_forward_norm))
-    merge(lookup(NORMS, "norm", spec.final_norm.kind).weight_decls(spec.final_norm))
+        for name, norm in norms.items():
+            merge(norm.weight_decls(layer.norms[name]))
+    merge(lookup(OUTPUTS, "output part", spec.output.kind).weight_decls(spec.output))
     return decls
 
 
@@ -82,20 +83,17 @@ class Model:
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
-        self.embedding = weights[spec.embedding_weight]
-        self.lm_head = self.embedding if spec.tied_head else weights[spec.lm_head_weight]
+        self.input = lookup(INPUTS, "input part", spec.input.kind)(spec.input, weights, dtype)
+        self.output = lookup(OUTPUTS, "output part", spec.output.kind)(spec.output, weights, dtype)
         self.layers = []
         for layer in spec.layers:
-            block, mixer, ffn, norm1, norm2 = _layer_classes(layer)
-            self.layers.append(block(mixer(layer.mixer, weights, dtype, device),
-                                     ffn(layer.feed_forward, weights, dtype),
-                                     norm1(layer.mixer_norm, weights, dtype),
-                                     norm2(layer.feed_forward_norm, weights, dtype)))
-        self.final_norm = lookup(NORMS, "norm", spec.final_norm.kind)(spec.final_norm, weights, dtype)
+            block, mixer, ffn, norms = _layer_classes(layer)
+            self.layers.append(block(mixer(layer.mixer, weights, dtype, device), ffn(layer.feed_forward, weights, dtype),
+                                     {name: cls(layer.norms[name], weights, dtype) for name, cls in norms.items()}))
         self.cache_specs = cache_specs(spec)
-        parts = [self.final_norm]
+        parts = [self.input, self.output]
         for block in self.layers:
-            parts += [block, block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm,
+            parts += [block, block.mixer, block.feed_forward, *getattr(block, "norms", {}).values(),
                       getattr(block.mixer, "position", None)]
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in parts if part is not None)
         self.tile_requests = tile_requests(spec)
@@ -109,8 +107,8 @@ class Model:
         return cls(spec, weights, dtype, device)
 
     def weight_bytes_read_per_step(self) -> int:
-        """Bytes of weights one step reads when every matrix is used once (the embedding table is
-        only gathered from, unless it also serves as the head)."""
+        """Bytes of weights one step reads when every matrix is used once (an embedding table is only
+        gathered from, unless it also serves as the head)."""
         by_storage: dict[int, dict[tuple[int, int], int]] = {}     # storage -> {(address, bytes) of a tensor}
         sizes: dict[int, int] = {}
 
@@ -119,12 +117,12 @@ class Model:
             sizes[storage.data_ptr()] = storage.nbytes()
             by_storage.setdefault(storage.data_ptr(), {})[(t.data_ptr(), t.numel() * t.element_size())] = 1
 
-        add(self.lm_head)
-        for tensor in self.final_norm.weights_read():
-            add(tensor)
+        for part in (self.input, self.output):
+            for tensor in part.weights_read():
+                add(tensor)
         for call in self.spec.run_order:
             block = self.layers[call.layer]
-            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+            for part in (block.mixer, block.feed_forward, *getattr(block, "norms", {}).values()):
                 for tensor in part.weights_read():
                     add(tensor)
         # Tensors that share a storage overlap (a matrix and a view of its first rows): such a storage
@@ -133,19 +131,11 @@ class Model:
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
-        hidden = ops.embedding(self.embedding, ctx.token_ids, ctx.status)
+        hidden = self.input.forward(ctx)
         if self.use_chains and self.chains is not None and self.chains.supports(ctx.num_tokens):
             stream = ResidualStream(*self.chains.forward(hidden, ctx))
         else:
             stream = ResidualStream(hidden)
             for call in self.spec.run_order:
                 stream = self.layers[call.layer].forward(stream, ctx, call)
-        wanted = ctx.logit_tokens
-        if wanted.numel() == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        rows = ops.gather_rows(stream.hidden, wanted, ctx.status)
-        if stream.pending is not None:
-            normed = self.final_norm.add_forward(rows, ops.gather_rows(stream.pending, wanted, ctx.status))
-        else:
-            normed = self.final_norm.forward(rows)
-        return ops.linear(normed, self.lm_head, out_dtype=torch.float32)
+        return self.output.forward(stream, ctx)

@@ -47,6 +47,9 @@ class RopeNeox(PositionEncoding):
     def apply(self, x: torch.Tensor, heads: int, positions: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         return ops.rope(x, heads, self.head_dim, self.cos, self.sin, positions, status)
 
+    def as_rotation_tables(self) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.cos, self.sin
+
 
 class NoPosition(PositionEncoding):
     graph_safe = True
@@ -59,6 +62,9 @@ class NoPosition(PositionEncoding):
 
     def apply(self, x: torch.Tensor, heads: int, positions: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         return x
+
+    def as_rotation_tables(self) -> tuple[None, None]:
+        return None, None
 
 
 register_position_encoding("rope_neox", RopeNeox)
