@@ -1,8 +1,10 @@
 """A plain, slow implementation of the dense Qwen3 decoder, the yardstick of the tests.
 
 It rests on the reference's formulas, cited function by function (paths are the reference
-project's own); the reference's model code is CUDA-only and cannot run on a CPU, so no output of
-it is compared here.  Whole sequences, no cache, float64 arithmetic, one function per part, and no
+project's own).  The reference's model code is CUDA-only and cannot run on a CPU; its output on a
+B200 for the tiny configuration B (greedy tokens and full rows of log-probabilities) is stored under
+tests/golden/ with the script that made it, and tests/test_reference_anchor.py compares this
+implementation with it.  Whole sequences, no cache, float64 arithmetic, one function per part, and no
 code shared with the engine: this file imports nothing from ``zephyr_b200`` and reads model folders
 with the ``safetensors`` package.
 

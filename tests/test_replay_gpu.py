@@ -270,7 +270,7 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
                         block.mixer.fuse_decode_rows = 1
                 outputs = {s["step"]: replayer.step(s) for s in steps}
                 # F's down projection (K = 12288) does not fit beside the weight ring: refused for real.
-                assert bool(refused) == (mode == "partial" or (name == "F" and mode != "off")), (mode, refused)
+                assert bool(refused) == (mode == "partial" or name == "F"), (mode, refused)
             rows = collect(steps, {k: v for k, v in outputs.items() if v is not None})
             first, worst, where = first_mismatch(rows, requests, folder, "bfloat16", f"{name} chains {mode}")
             assert first is None, f"{name} {mode}: {first}; worst {worst:.3e} at {where}"
