@@ -621,6 +621,35 @@ def test_paged_decode_far_key(ops, cuda_device):
         assert (got[1:2] - expected).abs().max() <= tol(torch.bfloat16, 2.0)
 
 
+@pytest.mark.parametrize("split_size", [None, 0, 64])
+@pytest.mark.parametrize("hd,page,window", [(128, 16, 300), (64, 8, 24), (32, 8, 129)])
+def test_paged_decode_window_edge(ops, cuda_device, hd, page, window, split_size):
+    """The window's edge on the fast decode path: the new token at position 1000 sees the positions
+    above 1000 - window.  A key made to dominate the softmax just inside the window (1001 - window)
+    decides the output; the same key one position further back (1000 - window) must not count at all.
+    The pages that lie wholly before the window are given back by the cache manager: the table holds
+    the null page there, whose contents are NaN here, so a kernel that reads them shows up."""
+    nh, nkv = 8, 4
+    for key, visible in ((1001 - window, True), (1000 - window, False)):
+        q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, torch.bfloat16, nh, nkv, hd, page, [1, 1], [1000, 1000],
+                                                      410, spike=(1, key))
+        table = meta["table"].clone()
+        table[:, : (1001 - window) // page] = 0           # released blocks: the null page, all NaN
+        assert torch.isnan(cache[0]).all()
+        rows = torch.tensor([0, 1], dtype=torch.int32, device=cuda_device)
+        status = ops.new_status(cuda_device)
+        out = torch.zeros_like(q)
+        ops.paged_decode(q, cache, table, rows, meta["row_q_start"], meta["row_ctx"], 1001, nh, nkv, hd, window,
+                         1 / math.sqrt(hd), status, out=out, split_size=split_size)
+        ops.check_status(status)
+        got = out.double().cpu().view(-1, nh, hd)
+        assert torch.isfinite(got).all()
+        expected = ref_attention_row(qs[1].double(), Ks[1].double(), Vs[1].double(), 1000, 1, window, nh, nkv)
+        assert (got[1:2] - expected).abs().max() <= tol(torch.bfloat16, 2.0)
+        near = (got[1, 0] - Vs[1][key].double()[0]).abs().max()
+        assert (near <= 0.05) == visible, (key, float(near))
+
+
 def test_kernels_refuse_what_they_do_not_take(ops, cuda_device):
     assert not ops.paged_decode_supported(16, 8, 128, torch.float32)
     assert not ops.paged_decode_supported(34, 2, 128, torch.bfloat16)     # 17 heads per group

@@ -189,10 +189,22 @@ class ModelRunner:
         """Describe the step and bring the description to the device: one pinned buffer, one copy."""
         arrays, info = self._describe(entries)
         sizes = [a.size for a in arrays]
-        host = torch.empty(max(1, sum(sizes)), dtype=torch.int32, pin_memory=True)
+        # A ring of pinned buffers, grown when a step needs more: a buffer is written again only after
+        # the copy that last read it is done.
+        total = max(1, sum(sizes))
+        turn = self._eager_turn = (getattr(self, "_eager_turn", -1) + 1) % 4
+        ring = self.__dict__.setdefault("_eager_ring", [None] * 4)
+        if ring[turn] is None or ring[turn][0].numel() < total:
+            ring[turn] = (torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True), None)
+        host, copied = ring[turn]
+        if copied is not None:
+            copied.synchronize()
         if sum(sizes):
             np.concatenate(arrays, out=host.numpy()[:sum(sizes)])
-        device = host.to(self.device, non_blocking=True)
+        device = host[:total].to(self.device, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        ring[turn] = (host, event)
         self.last_step_h2d_bytes = 4 * sum(sizes)
         return self._context_from(device, sizes, info)
 
