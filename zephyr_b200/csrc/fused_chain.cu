@@ -14,8 +14,11 @@
 //     form (cp.async.bulk).  Completion is counted on an mbarrier per slot.  Weights depend on nothing, so the copies of later stages are in
 //     flight while earlier stages compute and while the CTAs wait for each other: the launch reads
 //     the chain's weights as one stream;
-//   * eight consumer warps form the products on tensor cores (m16n8k16, the tokens on the 16-row
-//     side, 8 weight rows on the other, float32 accumulators).  The stage's input, a few rows, lies
+//   * eight consumer warps form the products on tensor cores (m16n8k16, float32 accumulators; for
+//     up to 8 tokens two tiles of 8 weight rows on the 16-row side and the tokens on the other, for
+//     more the tokens on the 16-row side and one tile on the other: warp-level products run at a
+//     fraction of the tensor cores' rate on this GPU, and a stage of a wide model spends as long on
+//     them as on its weights' way from memory, so none should be spent on rows that do not exist).  The stage's input, a few rows, lies
 //     in shared memory.  A CTA owns whole rows of W_s over the full K, so no sum crosses CTAs; its
 //     warps split K and add their parts in warp order, so every result is a fixed-order sum;
 //   * stages are separated by a barrier across the grid (an arrival counter in global memory; the
@@ -123,10 +126,12 @@ __device__ __forceinline__ void tiled_copy_g2s(void* smem_dst, const CUtensorMap
                ::"r"(smem_u32(smem_dst)), "l"(map), "r"(0), "r"(segment), "r"(row), "r"(smem_u32(bar)) : "memory");
 }
 
-// HI: more than 8 tokens, so the second half of the 16 token rows is in use.
-template <bool HI>
+// HI: more than 8 tokens, so the second half of the 16 token rows is in use.  FLIP (up to 8 tokens
+// only): the weights take the tensor cores' 16-row side, two tiles at a time.
+template <bool HI, bool FLIP>
 __global__ void __launch_bounds__(CH_THREADS, 1)
 fused_chain_kernel(const __grid_constant__ ChainArgs a) {
+  static_assert(!(HI && FLIP), "the tokens fit the 8-column side only up to 8");
   extern __shared__ unsigned char smem_unaligned[];
   // Swizzled tiles want 1024-byte alignment.
   unsigned char* smem_raw = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
@@ -481,41 +486,89 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
           xl[j] = ok[j] && lo_ok ? lds128(xs_lo + x_chunk + x_at[j]) : make_uint4(0, 0, 0, 0);
           xh[j] = ok[j] && hi_ok ? lds128(xs_hi + x_chunk + x_at[j]) : make_uint4(0, 0, 0, 0);
         }
+        if (!FLIP) {
 #pragma unroll
-        for (int u = 0; u < CH_GROUP_TILES; ++u) {
-          if (u >= n_tiles) break;
-          const int slot = seq & (R - 1);
-          const unsigned parity = (seq >> a.ring_shift) & 1;
-          ++seq;
-          if (failed) continue;
-          if (!wait(&full[slot], parity)) {
-            if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, s, cta);
-            abort_flag = 1;
-            failed = true;
-            continue;
+          for (int u = 0; u < CH_GROUP_TILES; ++u) {
+            if (u >= n_tiles) break;
+            const int slot = seq & (R - 1);
+            const unsigned parity = (seq >> a.ring_shift) & 1;
+            ++seq;
+            if (failed) continue;
+            if (!wait(&full[slot], parity)) {
+              if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, s, cta);
+              abort_flag = 1;
+              failed = true;
+              continue;
+            }
+            const unsigned wslot = ring_s + static_cast<unsigned>(slot) * CH_SLOT_BYTES;
+            uint4 wv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = ok[j] ? lds128(wslot + w_at[j]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const unsigned a0[4] = {xl[j].x, xh[j].x, xl[j].y, xh[j].y};
+              const unsigned a1[4] = {xl[j].z, xh[j].z, xl[j].w, xh[j].w};
+              mma_bf16_16816(acc[u], a0, wv[j].x, wv[j].y);
+              mma_bf16_16816(acc[u], a1, wv[j].z, wv[j].w);
+            }
+            __syncwarp();
+            if (lane == 0) chain_mbar_arrive(&empty[slot]);
           }
-          const unsigned wslot = ring_s + static_cast<unsigned>(slot) * CH_SLOT_BYTES;
-          uint4 wv[4];
+        } else {
+          // Up to 8 tokens: the weights take the 16-row side, two tiles at a time (the lane's row of
+          // either), and the tokens the 8-column side, so no half of a product is wasted on rows of
+          // tokens that do not exist.  acc[u / 2] then holds, for lane (g, t4), weight row g of tile u
+          // (elements 0, 1) and of tile u + 1 (elements 2, 3) at tokens 2 t4 and 2 t4 + 1.
 #pragma unroll
-          for (int j = 0; j < 4; ++j) wv[j] = ok[j] ? lds128(wslot + w_at[j]) : make_uint4(0, 0, 0, 0);
+          for (int u = 0; u < CH_GROUP_TILES; u += 2) {
+            if (u >= n_tiles) break;
+            const bool pair = u + 1 < n_tiles;
+            const int slot0 = seq & (R - 1), slot1 = (seq + 1) & (R - 1);
+            const unsigned parity0 = (seq >> a.ring_shift) & 1, parity1 = ((seq + 1) >> a.ring_shift) & 1;
+            seq += pair ? 2 : 1;
+            if (failed) continue;
+            if (!wait(&full[slot0], parity0) || (pair && !wait(&full[slot1], parity1))) {
+              if (lane == 0 && !abort_flag) report(a.status, STATUS_COPY_TIMEOUT, s, cta);
+              abort_flag = 1;
+              failed = true;
+              continue;
+            }
+            const unsigned w0 = ring_s + static_cast<unsigned>(slot0) * CH_SLOT_BYTES;
+            const unsigned w1 = ring_s + static_cast<unsigned>(slot1) * CH_SLOT_BYTES;
+            uint4 wl[4], wh[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const unsigned a0[4] = {xl[j].x, xh[j].x, xl[j].y, xh[j].y};
-            const unsigned a1[4] = {xl[j].z, xh[j].z, xl[j].w, xh[j].w};
-            mma_bf16_16816(acc[u], a0, wv[j].x, wv[j].y);
-            mma_bf16_16816(acc[u], a1, wv[j].z, wv[j].w);
+            for (int j = 0; j < 4; ++j) {
+              wl[j] = ok[j] ? lds128(w0 + w_at[j]) : make_uint4(0, 0, 0, 0);
+              wh[j] = ok[j] && pair ? lds128(w1 + w_at[j]) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const unsigned a0[4] = {wl[j].x, wh[j].x, wl[j].y, wh[j].y};
+              const unsigned a1[4] = {wl[j].z, wh[j].z, wl[j].w, wh[j].w};
+              mma_bf16_16816(acc[u >> 1], a0, xl[j].x, xl[j].y);
+              mma_bf16_16816(acc[u >> 1], a1, xl[j].z, xl[j].w);
+            }
+            __syncwarp();
+            if (lane == 0) {
+              chain_mbar_arrive(&empty[slot0]);
+              if (pair) chain_mbar_arrive(&empty[slot1]);
+            }
           }
-          __syncwarp();
-          if (lane == 0) chain_mbar_arrive(&empty[slot]);
         }
       }
-      // Lane (g, t4) holds tokens g and g + 8 at weight rows 2 t4 and 2 t4 + 1 of each tile.
+      // The warps' parts go to shared memory as [tile][token][weight row].  More than 8 tokens: lane
+      // (g, t4) holds tokens g and g + 8 at weight rows 2 t4 and 2 t4 + 1 of each tile.
 #pragma unroll
       for (int u = 0; u < CH_GROUP_TILES; ++u) {
         if (u >= n_tiles) break;
         float* dst = red + ((warp * CH_GROUP_TILES + u) * RM) * 8;
-        *reinterpret_cast<float2*>(dst + g * 8 + 2 * t4) = make_float2(acc[u][0], acc[u][1]);
-        if (HI) *reinterpret_cast<float2*>(dst + (g + 8) * 8 + 2 * t4) = make_float2(acc[u][2], acc[u][3]);
+        if (!FLIP) {
+          *reinterpret_cast<float2*>(dst + g * 8 + 2 * t4) = make_float2(acc[u][0], acc[u][1]);
+          if (HI) *reinterpret_cast<float2*>(dst + (g + 8) * 8 + 2 * t4) = make_float2(acc[u][2], acc[u][3]);
+        } else {
+          dst[(2 * t4) * 8 + g] = acc[u >> 1][(u & 1) * 2];
+          dst[(2 * t4 + 1) * 8 + g] = acc[u >> 1][(u & 1) * 2 + 1];
+        }
       }
       chain_consumer_barrier();
       const int n_out = (n_tiles / T) * RM * 8;          // outputs of the group: [block][token][row]
@@ -557,6 +610,16 @@ fused_chain_kernel(const __grid_constant__ ChainArgs a) {
       __threadfence();
     }
   }
+}
+
+// Chains whose weights come to at most this many bytes a CTA put the weights on the tensor cores'
+// 16-row side when there are at most 8 tokens (half as many products).  Measured on three shapes at
+// batch 8 and 1: a chain of 32 MB (0.2 MB a CTA) takes 4.7 % off a decode step, one of 50 MB (0.34 MB)
+// 1 to 2 %; chains of 105 MB (0.7 MB a CTA) and more, whose stream from memory is what counts, lose
+// up to 5 % (a pair of tiles is waited for together).
+inline long long& chain_flip_max_bytes() {
+  static long long bytes = 640ll << 10;
+  return bytes;
 }
 
 size_t chain_smem_bytes(int slots, int xs_rows, int xs_row_bytes) {
@@ -608,6 +671,13 @@ ZB_API int zb_fused_chain_stage_supported(int M, int N, int K, int prologue, int
 }
 
 ZB_API int zb_fused_chain_max_stages() { return CH_MAX_STAGES; }
+
+// The limit described at chain_flip_max_bytes (bytes of weights per CTA and launch); returns the old one.
+ZB_API long long zb_fused_chain_set_flip_bytes(long long bytes) {
+  const long long before = chain_flip_max_bytes();
+  chain_flip_max_bytes() = bytes;
+  return before;
+}
 
 // Whether the kernels of a decode step (position encoding with cache write, decode attention, chain)
 // are launched as programmatic dependents of the kernel before them (on by default).  Returns the
@@ -676,19 +746,20 @@ ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, in
   a.ring_shift = 0;
   while ((1 << a.ring_shift) < slots) ++a.ring_shift;
   const size_t smem = chain_smem_bytes(slots, xs_rows, a.xs_row_bytes);
-  const void* kernel = M > 8 ? reinterpret_cast<const void*>(fused_chain_kernel<true>)
-                             : reinterpret_cast<const void*>(fused_chain_kernel<false>);
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-    return ERR_CUDA;
+  long long weight_bytes = 0;
+  for (int s = 0; s < n_stages; ++s) weight_bytes += static_cast<long long>(in[s].N) * in[s].K * 2;
   int device = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-      (M > 8 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_chain_kernel<true>, CH_THREADS, smem)
-             : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_chain_kernel<false>, CH_THREADS, smem)) != cudaSuccess)
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
     return ERR_CUDA;
-  if (per_sm < 1) return ERR_UNSUPPORTED;
-  return M > 8 ? launch_dependent(fused_chain_kernel<true>, dim3(sms), dim3(CH_THREADS), smem,
-                                  static_cast<cudaStream_t>(stream), true, a)
-               : launch_dependent(fused_chain_kernel<false>, dim3(sms), dim3(CH_THREADS), smem,
-                                  static_cast<cudaStream_t>(stream), true, a);
+  const bool flip = M <= 8 && weight_bytes / (sms > 0 ? sms : 1) <= chain_flip_max_bytes();
+  const auto launch = [&](auto kernel) -> int {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, CH_THREADS, smem) != cudaSuccess)
+      return ERR_CUDA;
+    if (per_sm < 1) return ERR_UNSUPPORTED;
+    return launch_dependent(kernel, dim3(sms), dim3(CH_THREADS), smem, static_cast<cudaStream_t>(stream), true, a);
+  };
+  if (M > 8) return launch(fused_chain_kernel<true, false>);
+  return flip ? launch(fused_chain_kernel<false, true>) : launch(fused_chain_kernel<false, false>);
 }

@@ -87,6 +87,7 @@ _SIGNATURES = {
     "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
     "zb_fused_chain_max_stages": [],
     "zb_fused_chain_grid": [],
+    "zb_fused_chain_set_flip_bytes": [c_longlong],
     "zb_set_dependent_launch": [c_int],
     "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_sample_chunks": [c_int],
