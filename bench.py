@@ -444,12 +444,25 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
+    parser.add_argument("--only", choices=("prefill", "decode"), default=None,
+                        help="time only the 2048-token prefill, or only the decode step, and print a short line "
+                             "(the program a profiler is pointed at)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.only is not None and args.impl == "ours":
+        engine, config, _ = build_engine(args.shape, args.layers, args.batch, args.context, prefill_together=1)
+        if args.only == "prefill":
+            ms = device_prefill(engine, PREFILL_TOKENS, 3, args.steps)
+            print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": config.num_hidden_layers, "ms": round(ms, 4)}))
+        else:
+            ms, launches, _ = device_decode(engine, args.batch, args.context, args.warmup, args.steps, None)
+            print(json.dumps({"only": "decode", "batch": args.batch, "layers": config.num_hidden_layers, "ms_per_step": round(ms, 4),
+                              "gpu_launches": launches}))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
