@@ -102,8 +102,20 @@ __host__ __device__ __forceinline__ int kv_element_index(int i, int pos, int hea
   return ((chunk ^ kv_swizzle(pos, head_dim * elem_bytes / 16)) * per_chunk) + (i - chunk * per_chunk);
 }
 
+// What the CUDA runtime said when a call of this library last failed (zb_last_cuda_error hands it out).
+inline const char*& last_cuda_error_text() {
+  static const char* text = "no CUDA call of this library has failed";
+  return text;
+}
+// True, with the runtime's words kept, if `e` is an error.
+inline bool cuda_failed(cudaError_t e) {
+  if (e == cudaSuccess) return false;
+  last_cuda_error_text() = cudaGetErrorString(e);
+  return true;
+}
+
 inline int launch_result() {
-  return cudaPeekAtLastError() == cudaSuccess ? OK : ERR_CUDA;
+  return cuda_failed(cudaPeekAtLastError()) ? ERR_CUDA : OK;
 }
 
 // Programmatic dependent launch.  A kernel launched with `launch_dependent` may start while the
@@ -144,7 +156,7 @@ inline int launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, si
   }
   config.attrs = attributes;
   config.numAttrs = n;
-  return cudaLaunchKernelEx(&config, kernel, Params(args)...) == cudaSuccess ? launch_result() : ERR_CUDA;
+  return cuda_failed(cudaLaunchKernelEx(&config, kernel, Params(args)...)) ? ERR_CUDA : launch_result();
 }
 
 }  // namespace zb

@@ -465,3 +465,6 @@ ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int b
   return dtype == DTYPE_F32 ? silu_mul_launch<float>(out, gu, T, I, s)
                             : silu_mul_launch<__nv_bfloat16>(out, gu, T, I, s);
 }
+
+// The CUDA runtime's words for the last call of this library that failed (return code 2).
+ZB_API const char* zb_last_cuda_error() { return last_cuda_error_text(); }

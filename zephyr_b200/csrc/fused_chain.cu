@@ -749,13 +749,13 @@ ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, in
   long long weight_bytes = 0;
   for (int s = 0; s < n_stages; ++s) weight_bytes += static_cast<long long>(in[s].N) * in[s].K * 2;
   int device = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&device) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+  if (cuda_failed(cudaGetDevice(&device)) ||
+      cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)))
     return ERR_CUDA;
   const bool flip = M <= 8 && weight_bytes / (sms > 0 ? sms : 1) <= chain_flip_max_bytes();
   const auto launch = [&](auto kernel) -> int {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, CH_THREADS, smem) != cudaSuccess)
+    if (cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))) ||
+        cuda_failed(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, CH_THREADS, smem)))
       return ERR_CUDA;
     if (per_sm < 1) return ERR_UNSUPPORTED;
     return launch_dependent(kernel, dim3(sms), dim3(CH_THREADS), smem, static_cast<cudaStream_t>(stream), true, a);

@@ -116,6 +116,8 @@ def library() -> ctypes.CDLL:
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
+            lib.zb_last_cuda_error.argtypes = []
+            lib.zb_last_cuda_error.restype = ctypes.c_char_p
             lib.zb_paged_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
             lib.zb_paged_decode_scratch_floats.restype = c_longlong
             lib.zb_paged_decode_balanced_scratch_floats.argtypes = [c_int, c_int, c_int]
@@ -139,7 +141,9 @@ def _check(rc: int, name: str, kernels: int = 1) -> None:
     if rc != 0:
         detail = ""
         if rc == 2:
-            detail = f" ({torch.cuda.get_device_name()}; the library holds sm_100a code only)"
+            said = library().zb_last_cuda_error()
+            detail = (f": {said.decode() if said else 'unknown'} ({torch.cuda.get_device_name()}; "
+                      "the library holds sm_100a code only)")
         raise KernelError(f"{name}: {_RC_TEXT.get(rc, f'error {rc}')}{detail}")
 
 
