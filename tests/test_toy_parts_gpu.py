@@ -1,7 +1,9 @@
 """Parts that the framework does not have, defined here and registered from outside: a mixer with a
 state of its own (a running mean over the sequence, kept in the per-request state slots), a block
-arrangement with four norms (one before and one after each of its two parts), an input part that
-scales the embeddings and an output part that scales and caps the logits, in a toy architecture
+arrangement with four norms (one before and one after each of its two parts), a feed-forward that
+routes every token over three small experts, a position encoding that rotates neighbouring pairs
+(and so takes the attention's general path, outside the fused kernels), an input part that scales
+the embeddings and an output part that scales and caps the logits, in a toy architecture
 whose run order names a layer twice and lets a layer read another layer's cache.  The model is
 built, stepped whole, in portions and mixed with other requests, and compared with a plain float64
 computation written in this file.  No file of the framework is changed for it."""
@@ -12,13 +14,14 @@ import math
 import pytest
 import torch
 
-from plain_qwen3 import F64, plain_attention, plain_mlp, plain_rmsnorm, plain_rope, plain_rope_tables
+from plain_qwen3 import F64, plain_attention, plain_mlp, plain_rmsnorm
 from replay_util import collect, random_tokens, trace_mixed, trace_portions, trace_tail, trace_whole
 
 pytestmark = pytest.mark.gpu
 
 HIDDEN, VOCAB, HEADS, KV_HEADS, HEAD_DIM, INTER, EPS, THETA, MAX_POS = 48, 101, 4, 2, 16, 80, 1e-5, 10000.0, 128
 EMBED_SCALE, LOGIT_SCALE, LOGIT_CAP = 3.0, 0.5, 2.0
+EXPERTS, EXPERT_INTER, ROUTER_SHARPNESS = 3, 24, 4.0
 
 
 def toy_classes():
@@ -26,8 +29,55 @@ def toy_classes():
     from zephyr_b200.config import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec, NormSpec,
                                     OutputSpec, PositionSpec)
     from zephyr_b200.kernels import ops
-    from zephyr_b200.parts import NORMS, Block, InputPart, Mixer, OutputPart, lookup
+    from zephyr_b200.parts import NORMS, Block, FeedForward, InputPart, Mixer, OutputPart, PositionEncoding, lookup
     from zephyr_b200.weights import WeightDecl
+
+    class NeighbourPairRope(PositionEncoding):
+        """Rotates the pairs (2i, 2i + 1) of every head by position * theta^(-2i / head_dim).  It offers
+        no rotation tables, so the attention applies it through ``apply`` and runs its own norm and
+        cache-write kernels around it."""
+
+        def __init__(self, spec, dtype, device):
+            self.head_dim = spec.head_dim
+            index = torch.arange(0, spec.head_dim, 2, dtype=torch.float32)
+            self.inv_freq = (float(spec.params["theta"]) ** (-index / spec.head_dim)).to(device)
+
+        def apply(self, x, heads, positions, status):
+            T = x.shape[0]
+            pairs = x.view(T, heads, self.head_dim // 2, 2).float()
+            angle = positions.to(torch.float32)[:, None] * self.inv_freq[None, :]
+            c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            rotated = torch.stack([pairs[..., 0] * c - pairs[..., 1] * s, pairs[..., 1] * c + pairs[..., 0] * s], dim=-1)
+            x.copy_(rotated.view(T, heads * self.head_dim).to(x.dtype))
+            return x
+
+    class SoftRoutedExperts(FeedForward):
+        """y = sum_e softmax(sharpness * (x R^T))_e * down_e(silu(gate_e x) * up_e x): a router and a
+        handful of small experts, every token weighting all of them."""
+
+        def __init__(self, spec, weights, dtype):
+            p = spec.params
+            self.router, self.sharpness = weights[p["router"]], float(p["sharpness"])
+            self.experts = [tuple(weights[f"{p['prefix']}.{e}.{name}.weight"] for name in ("gate_proj", "up_proj", "down_proj"))
+                            for e in range(int(p["experts"]))]
+
+        @staticmethod
+        def weight_decls(spec):
+            p = spec.params
+            decls = {p["router"]: WeightDecl((p["experts"], p["hidden_size"]))}
+            for e in range(int(p["experts"])):
+                decls[f"{p['prefix']}.{e}.gate_proj.weight"] = WeightDecl((p["intermediate_size"], p["hidden_size"]))
+                decls[f"{p['prefix']}.{e}.up_proj.weight"] = WeightDecl((p["intermediate_size"], p["hidden_size"]))
+                decls[f"{p['prefix']}.{e}.down_proj.weight"] = WeightDecl((p["hidden_size"], p["intermediate_size"]))
+            return decls
+
+        def forward(self, x):
+            share = torch.softmax(ops.linear(x, self.router, out_dtype=torch.float32) * self.sharpness, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e, (gate, up, down) in enumerate(self.experts):
+                hidden = ops.silu_mul(torch.cat([ops.linear(x, gate), ops.linear(x, up)], dim=1))
+                out += share[:, e:e + 1] * ops.linear(hidden, down).float()
+            return out.to(x.dtype)
 
     class SandwichBlock(Block):
         """r = x + post_mixer(mixer(pre_mixer(x))); x' = r + post_ffn(ffn(pre_ffn(r))): four norms."""
@@ -117,7 +167,7 @@ def toy_classes():
             return {"model_type": self.model_type, "architectures": [self.architecture]}
 
         def to_model_spec(self):
-            position = PositionSpec("rope_neox", HEAD_DIM, MAX_POS, {"theta": THETA})
+            position = PositionSpec("toy_neighbour_rope", HEAD_DIM, MAX_POS, {"theta": THETA})
 
             def norm(name):
                 return NormSpec("rmsnorm", HIDDEN, EPS, name)
@@ -141,6 +191,14 @@ def toy_classes():
                 prefix = f"toy.layers.{index}"
                 mixer = (MixerSpec("running_mean", {"hidden_size": HIDDEN, "proj": f"{prefix}.mean.proj.weight"})
                          if index == 1 else attention(f"{prefix}.attn"))
+                if index == 1:      # the stateful mixer, and the routed feed-forward
+                    routed = FeedForwardSpec("toy_soft_experts", {
+                        "hidden_size": HIDDEN, "intermediate_size": EXPERT_INTER, "experts": EXPERTS,
+                        "sharpness": ROUTER_SHARPNESS, "router": f"{prefix}.router.weight", "prefix": f"{prefix}.experts"})
+                    layers.append(LayerSpec("prenorm_residual", mixer, routed,
+                                            {"mixer": norm(f"{prefix}.norm1.weight"),
+                                             "feed_forward": norm(f"{prefix}.norm2.weight")}))
+                    continue
                 if index == 2:      # the arrangement with four norms
                     layers.append(LayerSpec("toy_sandwich", mixer, ffn(f"{prefix}.mlp"), {
                         "pre_mixer": norm(f"{prefix}.norm1.weight"), "post_mixer": norm(f"{prefix}.norm1b.weight"),
@@ -162,18 +220,21 @@ def toy_classes():
                                                "vocab_size": VOCAB, "hidden_size": HIDDEN, "scale": LOGIT_SCALE,
                                                "cap": LOGIT_CAP}))
 
-    return RunningMeanMixer, ToyConfig, SandwichBlock, ScaledEmbedding, CappedHead
+    return RunningMeanMixer, ToyConfig, SandwichBlock, ScaledEmbedding, CappedHead, NeighbourPairRope, SoftRoutedExperts
 
 
 @pytest.fixture(scope="module")
 def toy_folder(tmp_path_factory):
     from zephyr_b200.config import register_architecture, unregister_architecture
-    from zephyr_b200.parts import (BLOCKS, INPUTS, MIXERS, OUTPUTS, register_block, register_input, register_mixer,
-                                   register_output)
+    from zephyr_b200.parts import (BLOCKS, FEED_FORWARDS, INPUTS, MIXERS, OUTPUTS, POSITION_ENCODINGS, register_block,
+                                   register_feed_forward, register_input, register_mixer, register_output,
+                                   register_position_encoding)
     from zephyr_b200.weights import write_random_model
 
-    mixer, config, block, embedding, head = toy_classes()
+    mixer, config, block, embedding, head, rope, experts = toy_classes()
     register_mixer("running_mean", mixer)
+    register_position_encoding("toy_neighbour_rope", rope)
+    register_feed_forward("toy_soft_experts", experts)
     register_block("toy_sandwich", block)
     register_input("toy_scaled_embedding", embedding)
     register_output("toy_capped_head", head)
@@ -188,6 +249,8 @@ def toy_folder(tmp_path_factory):
     BLOCKS.pop("toy_sandwich", None)
     INPUTS.pop("toy_scaled_embedding", None)
     OUTPUTS.pop("toy_capped_head", None)
+    POSITION_ENCODINGS.pop("toy_neighbour_rope", None)
+    FEED_FORWARDS.pop("toy_soft_experts", None)
 
 
 # ------------------------------------------------------------- the plain computation
@@ -199,14 +262,22 @@ def plain_toy_logits(folder, tokens):
         for name in handle.keys():
             w[name] = handle.get_tensor(name).to(F64)
     T = len(tokens)
-    cos, sin = plain_rope_tables(HEAD_DIM, T, THETA)
+    index = torch.arange(0, HEAD_DIM, 2, dtype=torch.float32)
+    angle = (torch.arange(T, dtype=torch.float32)[:, None] * (THETA ** (-index / HEAD_DIM))[None, :]).to(F64)
+    cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+
+    def rotate(v):          # pairs (2i, 2i + 1) of every head
+        pairs = v.view(T, v.shape[1], HEAD_DIM // 2, 2)
+        return torch.stack([pairs[..., 0] * cos - pairs[..., 1] * sin, pairs[..., 1] * cos + pairs[..., 0] * sin],
+                           dim=-1).view(v.shape)
+
     x = EMBED_SCALE * w["toy.embed.weight"][torch.tensor(tokens)]
 
     def qkv(h, prefix):
-        q = plain_rope(plain_rmsnorm((h @ w[f"{prefix}.q_proj.weight"].T).view(T, HEADS, HEAD_DIM),
-                                     w[f"{prefix}.q_norm.weight"], EPS), range(T), cos, sin)
-        k = plain_rope(plain_rmsnorm((h @ w[f"{prefix}.k_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM),
-                                     w[f"{prefix}.k_norm.weight"], EPS), range(T), cos, sin)
+        q = rotate(plain_rmsnorm((h @ w[f"{prefix}.q_proj.weight"].T).view(T, HEADS, HEAD_DIM),
+                                 w[f"{prefix}.q_norm.weight"], EPS))
+        k = rotate(plain_rmsnorm((h @ w[f"{prefix}.k_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM),
+                                 w[f"{prefix}.k_norm.weight"], EPS))
         v = (h @ w[f"{prefix}.v_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM)
         return q, k, v
 
@@ -228,9 +299,14 @@ def plain_toy_logits(folder, tokens):
         return finish(x, out, index), (k, v)
 
     def mean_layer(x, index):
-        h = plain_rmsnorm(x, w[f"toy.layers.{index}.norm1.weight"], EPS)
+        prefix = f"toy.layers.{index}"
+        h = plain_rmsnorm(x, w[f"{prefix}.norm1.weight"], EPS)
         means = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=F64)[:, None]
-        return finish(x, means @ w[f"toy.layers.{index}.mean.proj.weight"].T, index)
+        r = x + means @ w[f"{prefix}.mean.proj.weight"].T
+        fed = plain_rmsnorm(r, w[f"{prefix}.norm2.weight"], EPS)
+        share = torch.softmax(fed @ w[f"{prefix}.router.weight"].T * ROUTER_SHARPNESS, dim=-1)
+        out = sum(share[:, e:e + 1] * plain_mlp(fed, w, f"{prefix}.experts.{e}") for e in range(EXPERTS))
+        return r + out
 
     x, kv0 = attention_layer(x, 0)
     x = mean_layer(x, 1)
