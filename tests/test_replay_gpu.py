@@ -276,6 +276,40 @@ def test_decode_chains_whole_partial_and_off(model_folders, cuda_device, monkeyp
             assert first is None, f"{name} {mode}: {first}; worst {worst:.3e} at {where}"
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_two_halves_of_a_decode_step_side_by_side(model_folders, cuda_device, name):
+    """A decode step of many requests runs as two halves on two streams, each on half the SMs, with
+    workspaces of their own (the model does that from 12 requests up; here from 2).  The tails of four
+    requests decoded together, first as one batch, then in two lanes: both agree with the plain
+    implementation, and the lanes were really used."""
+    from zephyr_b200.kernels import ops
+
+    folder = model_folders(name, "bfloat16")
+    vocab = TINY[name]["config"]["vocab_size"]
+    requests = {f"r{i}": random_tokens(vocab, n, seed=1300 + i) for i, n in enumerate((90, 140, 70, 200))}
+    steps = trace_batched_tail(requests, tail=40)
+    seen = []
+    real = ops.lane
+
+    def two_lanes(replayer):
+        replayer.runner.model.lanes_min_rows = 2
+
+        class counted(real):
+            def __enter__(self):
+                seen.append(self.index)
+                return super().__enter__()
+        ops.lane = counted
+
+    try:
+        for prepare in (None, two_lanes):
+            rows = collect(steps, run_in_process(folder, "bfloat16", steps, TINY[name]["page_size"], prepare=prepare))
+            first, worst, where = first_mismatch(rows, requests, folder, "bfloat16", f"{name} lanes {prepare is not None}")
+            assert first is None, f"{name} lanes={prepare is not None}: {first}; worst {worst:.3e} at {where}"
+    finally:
+        ops.lane = real
+    assert 0 in seen and 1 in seen
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_decoding_across_the_bounds_of_the_decode_graphs(model_folders, cuda_device, name, dtype):

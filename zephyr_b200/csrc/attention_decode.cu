@@ -813,6 +813,7 @@ int decode_launch(DecodeArgs& a, cudaStream_t stream) {
   if (cudaGetDevice(&device) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
     return ERR_CUDA;
+  sms = shared_sm_count(sms);
   // One persistent CTA per SM.  Fixed splits: max_splits items per pair.  Balanced: max_splits is the
   // most tiles a pair can have, and an item is at most a pair's tiles or a range's, whichever is less.
   const long long units = static_cast<long long>(a.n_rows) * a.nkv * a.max_splits;

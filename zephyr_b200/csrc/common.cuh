@@ -129,6 +129,15 @@ inline int launch_result() {
 __device__ __forceinline__ void wait_for_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// How many CTAs a persistent kernel of this library (the decode attention, the chain of small
+// products) takes at most: 0 means one per SM.  Two halves of a batch that run side by side on two
+// streams are given half the SMs each.
+inline int& sm_share() {
+  static int ctas = 0;
+  return ctas;
+}
+inline int shared_sm_count(int sms) { return sm_share() > 0 && sm_share() < sms ? sm_share() : sms; }
+
 inline bool& dependent_launch_enabled() {
   static bool enabled = true;
   return enabled;

@@ -672,6 +672,13 @@ ZB_API int zb_fused_chain_stage_supported(int M, int N, int K, int prologue, int
 
 ZB_API int zb_fused_chain_max_stages() { return CH_MAX_STAGES; }
 
+// CTAs that the persistent kernels of later launches take at most (0: one per SM); returns the old setting.
+ZB_API int zb_set_sm_share(int ctas) {
+  const int before = sm_share();
+  sm_share() = ctas < 0 ? 0 : ctas;
+  return before;
+}
+
 // The limit described at chain_flip_max_bytes (bytes of weights per CTA and launch); returns the old one.
 ZB_API long long zb_fused_chain_set_flip_bytes(long long bytes) {
   const long long before = chain_flip_max_bytes();
@@ -694,7 +701,7 @@ ZB_API int zb_fused_chain_grid() {
   if (cudaGetDevice(&device) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
     return 0;
-  return sms;
+  return shared_sm_count(sms);
 }
 
 // `trace`: null, or zb_fused_chain_grid() * n_stages * 4 ints on the device that receive every CTA's
@@ -753,6 +760,7 @@ ZB_API int zb_fused_chain(const void* stages, int n_stages, int M, int* sync, in
       cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)))
     return ERR_CUDA;
   const bool flip = M <= 8 && weight_bytes / (sms > 0 ? sms : 1) <= chain_flip_max_bytes();
+  sms = shared_sm_count(sms);
   const auto launch = [&](auto kernel) -> int {
     if (cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))) ||
         cuda_failed(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, CH_THREADS, smem)))

@@ -87,6 +87,7 @@ _SIGNATURES = {
     "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
     "zb_fused_chain_max_stages": [],
     "zb_fused_chain_grid": [],
+    "zb_set_sm_share": [c_int],
     "zb_fused_chain_set_flip_bytes": [c_longlong],
     "zb_set_dependent_launch": [c_int],
     "zb_fused_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -403,11 +404,36 @@ def paged_decode_scratch_floats(n_rows: int, nh: int, hd: int, max_splits: int) 
 # (contents irrelevant between calls) and the arrival counters (zero between calls: the kernel
 # leaves them as it found them).  Buffers are only ever added, never freed or moved, because
 # captured graphs hold their addresses.
-_decode_buffers: dict[torch.device, list[tuple[torch.Tensor, torch.Tensor]]] = {}
+_decode_buffers: dict[tuple[torch.device, int], list[tuple[torch.Tensor, torch.Tensor]]] = {}
+
+# Two halves of a batch may run side by side on two streams (``parts.Model``): each is a lane with
+# workspaces of its own (the decode kernel's partial results and counters, the chain's barrier
+# counters), and the persistent kernels take half the SMs each.
+LANE = 0
+
+
+class lane:
+    """``with ops.lane(1, ctas): ...``: launches inside use lane 1's workspaces and at most ``ctas``
+    CTAs per persistent kernel (0: one per SM)."""
+
+    def __init__(self, index: int, ctas: int = 0):
+        self.index, self.ctas = index, ctas
+
+    def __enter__(self):
+        global LANE
+        self.before = (LANE, int(library().zb_set_sm_share(int(self.ctas))))
+        LANE = self.index
+        return self
+
+    def __exit__(self, *exc):
+        global LANE
+        LANE = self.before[0]
+        library().zb_set_sm_share(self.before[1])
+        return False
 
 
 def _decode_workspace(device: torch.device, floats: int, counters: int) -> tuple[torch.Tensor, torch.Tensor]:
-    pool = _decode_buffers.setdefault(device, [])
+    pool = _decode_buffers.setdefault((device, LANE), [])
     for scratch, count in pool:
         if scratch.numel() >= floats and count.numel() >= counters:
             return scratch, count
@@ -433,10 +459,13 @@ _SM_COUNT: dict[int, int] = {}
 
 
 def _sm_count() -> int:
+    """SMs a persistent kernel launched now may take (all, or the current lane's share)."""
     device = torch.cuda.current_device()
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    return _SM_COUNT[device]
+    share = int(library().zb_set_sm_share(0))
+    library().zb_set_sm_share(share)
+    return min(_SM_COUNT[device], share) if share > 0 else _SM_COUNT[device]
 
 
 def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
@@ -683,8 +712,8 @@ def fused_chain_max_stages() -> int:
 
 
 # The arrival counters of the chain kernel's barrier, per device: zero between launches.
-_chain_sync: dict[torch.device, torch.Tensor] = {}
-_chain_rows: dict[torch.device, torch.Tensor] = {}
+_chain_sync: dict[tuple[torch.device, int], torch.Tensor] = {}
+_chain_rows: dict[tuple[torch.device, int], torch.Tensor] = {}
 
 
 def set_dependent_launch(enabled: bool) -> bool:
@@ -733,10 +762,10 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
                          and st.residual_out.is_contiguous() and st.residual_out.data_ptr() != st.residual_in.data_ptr(),
                          "residual_out must be a second contiguous [tokens, K] buffer")
                 slot.delta, slot.ldd, slot.residual_out = st.delta.data_ptr(), st.delta.stride(0), st.residual_out.data_ptr()
-    device = stages[0].w.device
+    device = (stages[0].w.device, LANE)
     sync = _chain_sync.get(device)
     if sync is None:
-        sync = _chain_sync[device] = torch.zeros(2, dtype=torch.int32, device=device)
+        sync = _chain_sync[device] = torch.zeros(2, dtype=torch.int32, device=stages[0].w.device)
     if trace is not None:
         _cuda(trace)
         _require(trace.dtype == torch.int32 and trace.is_contiguous()
@@ -745,7 +774,8 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
     longest = max((st.w.shape[1] for st in stages if st.norm_w is not None), default=0)
     scratch = _chain_rows.get(device)
     if longest and (scratch is None or scratch.numel() < FUSED_CHAIN_MAX_TOKENS * longest):
-        scratch = _chain_rows[device] = torch.empty(FUSED_CHAIN_MAX_TOKENS * longest, dtype=torch.bfloat16, device=device)
+        scratch = _chain_rows[device] = torch.empty(FUSED_CHAIN_MAX_TOKENS * longest, dtype=torch.bfloat16,
+                                                    device=stages[0].w.device)
     _check(library().zb_fused_chain(ctypes.addressof(packed), len(stages), int(tokens), _ptr(sync), _ptr(status),
                                     _ptr(trace), _ptr(scratch) if longest else None, _stream()), "fused_chain")
 

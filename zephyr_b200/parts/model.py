@@ -6,6 +6,7 @@ final norm with the vocabulary projection (reference forward: src/model/causal_l
 
 from __future__ import annotations
 
+import dataclasses
 from typing import Mapping
 
 import torch
@@ -100,6 +101,18 @@ class Model:
         # Steps of a few tokens run as fused chains of products where every block offers its pieces.
         self.chains = DecodeChains.build(self.layers, spec.run_order, spec.hidden_size, dtype)
         self.use_chains = True
+        # A decode step of a small model is bound by latency: a layer's chain of small products waits on
+        # barriers while the memory system idles, and its attention streams the cache while the tensor
+        # cores idle.  Two halves of the batch, each on half the SMs and on a stream of its own, fill each
+        # other's pauses.  It pays where the cache a layer reads outweighs the layer's weights (which are
+        # then read twice) and each half still has rows enough to keep its SMs busy: measured on the
+        # Qwen3-0.6B shape at context 4096, 16 requests gain 9 % (2.53 -> 2.29 ms a step), 8 lose 5 %.
+        self.lanes_min_rows = 12
+        self.lanes_max_layer_bytes = 64 << 20
+        self._lanes_ok = (self.chains is not None and self.graph_safe
+                          and all(getattr(block.mixer, "fast_decode", False) for block in self.layers))
+        self._layer_bytes = None
+        self._side_stream = None
 
     @classmethod
     def load(cls, spec: ModelSpec, store: WeightStore, dtype: torch.dtype, device: torch.device | str) -> "Model":
@@ -129,11 +142,57 @@ class Model:
         # counts once, and never for more than it holds.
         return sum(min(sizes[storage], sum(size for _, size in tensors)) for storage, tensors in by_storage.items())
 
+    def _lane_split(self, ctx: StepContext) -> int:
+        """How many of the step's rows go to the first of two lanes; 0 if the step runs as one."""
+        rows = ctx.num_rows
+        if (not self._lanes_ok or rows < self.lanes_min_rows or ctx.num_decode_rows != rows or ctx.num_tokens != rows):
+            return 0
+        if self._layer_bytes is None:
+            self._layer_bytes = (self.weight_bytes_read_per_step() - sum(
+                t.numel() * t.element_size() for t in self.output.weights_read())) // max(len(self.spec.run_order), 1)
+        if self._layer_bytes > self.lanes_max_layer_bytes:
+            return 0
+        first = (rows + 1) // 2
+        return first if self.chains.supports(first) and self.chains.supports(rows - first) else 0
+
+    @staticmethod
+    def _rows_of(ctx: StepContext, r0: int, r1: int) -> StepContext:
+        """The rows r0..r1 of a step in which every row brings one token, as a step of their own: a
+        row's number is then also its token's place in the stream, so the first n entries of the index
+        vectors that count rows or tokens serve any n rows."""
+        n = r1 - r0
+        return dataclasses.replace(
+            ctx, num_tokens=n, num_rows=n, token_ids=ctx.token_ids[r0:r1], positions=ctx.positions[r0:r1],
+            token_row=ctx.token_row[:n], row_q_start=ctx.row_q_start[:n], row_q_len=ctx.row_q_len[r0:r1],
+            row_ctx=ctx.row_ctx[r0:r1], state_slots=ctx.state_slots[r0:r1],
+            block_tables=[table[r0:r1] for table in ctx.block_tables], logit_tokens=ctx.logit_tokens[:0],
+            decode_rows=ctx.decode_rows[:n], num_decode_rows=n, host_q_len=ctx.host_q_len[r0:r1],
+            host_ctx=ctx.host_ctx[r0:r1], host_slots=ctx.host_slots[r0:r1])
+
+    def _forward_in_two_lanes(self, hidden: torch.Tensor, ctx: StepContext, first: int):
+        main = torch.cuda.current_stream(self.device)
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        side = self._side_stream
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        rows = ctx.num_rows
+        side.wait_stream(main)
+        with ops.lane(0, sms // 2):
+            head = self.chains.forward(hidden[:first], self._rows_of(ctx, 0, first))
+        with torch.cuda.stream(side), ops.lane(1, sms - sms // 2):
+            tail = self.chains.forward(hidden[first:], self._rows_of(ctx, first, rows))
+        main.wait_stream(side)
+        return torch.cat([head[0], tail[0]]), torch.cat([head[1], tail[1]])
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
         hidden = self.input.forward(ctx)
         if self.use_chains and self.chains is not None and self.chains.supports(ctx.num_tokens):
-            stream = ResidualStream(*self.chains.forward(hidden, ctx))
+            first = self._lane_split(ctx)
+            if first:
+                stream = ResidualStream(*self._forward_in_two_lanes(hidden, ctx, first))
+            else:
+                stream = ResidualStream(*self.chains.forward(hidden, ctx))
         else:
             stream = ResidualStream(hidden)
             for call in self.spec.run_order:
