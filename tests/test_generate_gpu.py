@@ -49,7 +49,8 @@ def assert_greedy_agrees(got, expected, margins, tolerance):
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "float32"), ("B", "bfloat16"),
-                                        ("C", "bfloat16")])
+                                        ("C", "bfloat16"), ("W", "bfloat16"), ("D", "float32"), ("D", "bfloat16"),
+                                        ("E", "bfloat16")])
 def test_greedy_generation_matches_plain(model_folders, cuda_device, name, dtype):
     folder = model_folders(name, dtype)
     config, weights = load_model_folder(folder)
@@ -60,7 +61,11 @@ def test_greedy_generation_matches_plain(model_folders, cuda_device, name, dtype
         expected, margins = plain_greedy_with_margins(config, weights, prompt, 8)
         assert output.prompt_token_ids == tuple(prompt) and output.status.value == "completed"
         assert output.choices[0].finish_reason.value == "length" and output.usage.completion_tokens == 8
-        assert_greedy_agrees(list(output.token_ids), expected, margins, 2e-4 if dtype == "float32" else 0.04)
+        # A first difference is forgiven where the plain logits' two best lie closer than twice the bound on
+        # the engine's error (8 units in the last place of the row's largest logit in bfloat16).
+        last = plain_forward(config, weights, prompt)[-1]
+        bound = 1e-4 * max(1.0, float(last.abs().max())) if dtype == "float32" else 8 * 2.0 ** -8 * float(last.abs().max())
+        assert_greedy_agrees(list(output.token_ids), expected, margins, 2 * bound)
     assert engine.runner.manager.num_requests == 0
     engine.runner.manager.check_invariants()
 

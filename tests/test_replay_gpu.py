@@ -100,7 +100,7 @@ def test_trace_run_program(model_folders, cuda_device, tmp_path, dtype):
 
 def test_long_decoding(model_folders, cuda_device):
     """A short prompt, then 200 tokens one by one, across many page edges."""
-    for name, dtype in (("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16")):
+    for name, dtype in (("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16"), ("W", "bfloat16"), ("D", "bfloat16")):
         folder = model_folders(name, dtype)
         tokens = random_tokens(TINY[name]["config"]["vocab_size"], 230, seed=77)
         requests = {"long": tokens}
