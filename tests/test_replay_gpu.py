@@ -110,6 +110,36 @@ def test_long_decoding(model_folders, cuda_device):
         assert first is None, f"{name} {dtype}: {first}; worst {worst:.3e} at {where}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_contexts_as_long_as_the_benchmarks(model_folders, cuda_device, dtype):
+    """A prompt of 4100 tokens in portions of 2048, 1500 and 552, then 24 tokens one by one (the decode
+    graph's bound goes from 4096 to the model's limit), beside a second request of 2300 tokens that
+    decodes along: the prompt kernels' long rows of tiles, the decode kernel's items over hundreds of
+    pages, and logits of positions beyond 4096."""
+    name = "L"
+    folder = model_folders(name, dtype)
+    vocab = TINY[name]["config"]["vocab_size"]
+    requests = {"long": random_tokens(vocab, 4124, seed=41), "other": random_tokens(vocab, 2324, seed=42)}
+    steps, fed = [], {"long": 0, "other": 0}
+
+    def feed(items, end=()):
+        entries = []
+        for rid, count, want in items:
+            entries.append({"id": rid, "tokens": requests[rid][fed[rid]:fed[rid] + count], "want": want})
+            fed[rid] += count
+        steps.append({"step": len(steps), "entries": entries, "end": list(end)})
+
+    feed([("long", 2048, [0, 2047])])
+    feed([("long", 1500, [1499]), ("other", 2300, [2299])])
+    feed([("long", 552, [0, 551])])
+    for turn in range(24):
+        feed([("long", 1, [0]), ("other", 1, [0])], end=("long", "other") if turn == 23 else ())
+    rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+    assert ("long", 4123) in rows and ("other", 2323) in rows
+    first, worst, where = first_mismatch(rows, requests, folder, dtype, f"{name} long contexts")
+    assert first is None, f"{dtype}: {first}; worst {worst:.3e} at {where}"
+
+
 def test_first_tokens(model_folders, cuda_device):
     """The first tokens of a sequence, one at a time from the very start (position 0 has one key)."""
     for name in ("A", "B", "C"):

@@ -6,7 +6,8 @@ the benchmarked models, so that whole-model tests run the kernels those models r
 smallest model with head size 128 (tensor-core prompt attention, the fast decode attention), E has
 two layers of the 0.6B widths (the fused chain of a decode layer at its benchmarked shape), F one
 layer of the 8B widths (rows longer than 1024 in the chain, and a down projection whose input does
-not fit beside the weight ring in shared memory).
+not fit beside the weight ring in shared memory).  L is one small layer of head size 128 whose position table
+reaches 4608, for contexts as long as the benchmark's.
 
 C and W are NOT Qwen3: they belong to a test-only architecture, ``TinyWindowedForCausalLM``, defined
 and registered here, which is the Qwen3 decoder with a sliding window on some layers (the reference
@@ -47,6 +48,10 @@ TINY = {
     "E": dict(seed=4, page_size=16, config=dict(
         vocab_size=1001, hidden_size=1024, intermediate_size=3072, num_hidden_layers=2, num_attention_heads=16,
         num_key_value_heads=8, head_dim=128, max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=1000000.0,
+        tie_word_embeddings=True)),
+    "L": dict(seed=8, page_size=16, config=dict(       # one small layer with head size 128 and room for long contexts
+        vocab_size=331, hidden_size=128, intermediate_size=264, num_hidden_layers=1, num_attention_heads=2,
+        num_key_value_heads=1, head_dim=128, max_position_embeddings=4608, rms_norm_eps=1e-6, rope_theta=1000000.0,
         tie_word_embeddings=True)),
     "F": dict(seed=5, page_size=16, config=dict(
         vocab_size=517, hidden_size=4096, intermediate_size=12288, num_hidden_layers=1, num_attention_heads=32,
