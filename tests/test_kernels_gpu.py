@@ -189,6 +189,63 @@ def test_gemm_small_refuses(ops, cuda_device):
     assert ops.linear(x, w).shape == (65, 32)                            # the library product takes over
 
 
+# ------------------------------------------------------- the tcgen05 product for many rows
+TC_GEMM_CASES = [(128, 256, 64, 0), (200, 264, 136, 0), (2048, 1024, 3072, 0), (333, 250, 1000, 128), (333, 250, 1000, 256),
+                 (17, 1024, 2048, 128), (1000, 4096, 1024, 256), (129, 8, 8, 0), (2500, 1544, 520, 0)]
+
+
+@pytest.mark.parametrize("M,N,K,block_n", TC_GEMM_CASES)
+def test_gemm_tc_product(ops, cuda_device, M, N, K, block_n):
+    """Rows, columns and depths that end inside a tile, a stage and a swizzled row; more tiles than SMs
+    (a CTA takes several, through both accumulators) and fewer."""
+    x = rand((M, K), torch.bfloat16, cuda_device, 140)
+    w = rand((N, K), torch.bfloat16, cuda_device, 141, 0.1)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    assert ops.gemm_tc_supported(x, w)
+    got = ops.gemm_tc(x, w, block_n=block_n, status=status)
+    expected = x.double() @ w.double().T
+    assert status.tolist()[0] == 0, status.tolist()
+    assert got.shape == (M, N)
+    assert (got.double() - expected).abs().max() <= 4e-3 * max(1.0, float(expected.abs().max()))
+    # rows do not depend on the rows beside them, nor on the tile width
+    other = ops.gemm_tc(x[M // 2:], w, block_n=128 if block_n != 128 else 256, status=status)
+    assert torch.equal(other, got[M // 2:])
+    # strided activations (a slice of a wider buffer)
+    wide = torch.zeros((M, K + 16), dtype=torch.bfloat16, device=cuda_device)
+    wide[:, :K] = x
+    assert torch.equal(ops.gemm_tc(wide[:, :K], w, block_n=block_n, status=status), got)
+    assert status.tolist()[0] == 0
+
+
+@pytest.mark.parametrize("M,I,K,block_n", [(128, 128, 64, 0), (2048, 3072, 1024, 0), (300, 200, 96, 128), (300, 200, 96, 256),
+                                           (1111, 520, 264, 0)])
+def test_gemm_tc_fused_swiglu(ops, cuda_device, M, I, K, block_n):
+    x = rand((M, K), torch.bfloat16, cuda_device, 142)
+    gate = rand((I, K), torch.bfloat16, cuda_device, 143, 0.2)
+    up = rand((I, K), torch.bfloat16, cuda_device, 144, 0.2)
+    w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    got = ops.gemm_tc(x, w, swiglu=True, block_n=block_n, status=status)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    expected = g / (1 + torch.exp(-g)) * u
+    assert status.tolist()[0] == 0, status.tolist()
+    assert got.shape == (M, I) and (got.double() - expected).abs().max() <= 8e-3 * max(1.0, float(expected.abs().max()))
+    # the same sums, activation and rounding as the kernel for few rows
+    few = ops.gemm_small(x[:8].contiguous(), w, swiglu=True)
+    assert (few.double() - got[:8].double()).abs().max() <= 2.0 ** -7 * max(1.0, float(expected[:8].abs().max()))
+
+
+def test_gemm_tc_refuses(ops, cuda_device):
+    x = rand((200, 64), torch.bfloat16, cuda_device, 145)
+    w = rand((32, 64), torch.bfloat16, cuda_device, 146)
+    assert not ops.gemm_tc_supported(x[:, :60], w[:, :60].contiguous())          # K no multiple of 8
+    assert not ops.gemm_tc_supported(x.float(), w.float())
+    assert not ops.gemm_tc_supported(x, w[:24], swiglu=True)                      # gate/up blocks need N % 16 == 0
+    from zephyr_b200.config import InvalidArgumentError
+    with pytest.raises(InvalidArgumentError):
+        ops.gemm_tc(x[:, :60], w[:, :60].contiguous())
+
+
 # ------------------------------------------------------- norm + rotation + cache
 def ref_rope(x, positions, theta):
     """x [T, heads, hd] double; float32 angles as the reference computes them."""

@@ -140,6 +140,29 @@ def test_contexts_as_long_as_the_benchmarks(model_folders, cuda_device, dtype):
     assert first is None, f"{dtype}: {first}; worst {worst:.3e} at {where}"
 
 
+@pytest.mark.parametrize("name", ["D", "E", "F"])
+def test_a_step_of_more_than_a_thousand_rows(model_folders, cuda_device, name):
+    """Four prompts of 270 to 300 tokens in ONE step (1140 rows: the feed-forward's first product runs on
+    the tcgen05 kernel with the activation in its epilogue, through several tiles per CTA), then six
+    decoded tokens each, against the plain implementation."""
+    dtype = "bfloat16"
+    folder = model_folders(name, dtype)
+    vocab = TINY[name]["config"]["vocab_size"]
+    lengths = {"a": 300, "b": 270, "c": 290, "d": 280}
+    requests = {rid: random_tokens(vocab, n + 6, seed=50 + n) for rid, n in lengths.items()}
+    steps = [{"step": 0, "end": [], "entries": [
+        {"id": rid, "tokens": requests[rid][:n], "want": [0, n // 2, n - 1]} for rid, n in lengths.items()]}]
+    for turn in range(6):
+        steps.append({"step": turn + 1, "end": list(lengths) if turn == 5 else [], "entries": [
+            {"id": rid, "tokens": [requests[rid][n + turn]], "want": [0]} for rid, n in lengths.items()]})
+    from zephyr_b200.kernels import ops
+    before = ops.LAUNCH_COUNTS.get("gemm_tc", 0)
+    rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+    assert ops.LAUNCH_COUNTS.get("gemm_tc", 0) > before              # the kernel this test is about did run
+    first, worst, where = first_mismatch(rows, requests, folder, dtype, f"{name} 1140 rows")
+    assert first is None, f"{first}; worst {worst:.3e} at {where}"
+
+
 def test_first_tokens(model_folders, cuda_device):
     """The first tokens of a sequence, one at a time from the very start (position 0 has one key)."""
     for name in ("A", "B", "C"):

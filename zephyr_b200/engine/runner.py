@@ -53,7 +53,7 @@ class ModelRunner:
         self.max_seq_len = min(max_seq_len or model.spec.max_seq_len, model.spec.max_seq_len)
         self.manager = CacheManager(model.cache_specs, page_size, num_pages, max_requests)
         self.storage = CacheStorage(self.manager, model.dtype, model.device)
-        self.status = ops.new_status(model.device)
+        self.status = ops.device_status(model.device)
         self.poison_freed_pages = False      # tests: NaN into every page that is given back
         self.steps = 0
         self.use_cuda_graphs = use_cuda_graphs

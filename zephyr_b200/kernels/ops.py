@@ -82,6 +82,8 @@ _SIGNATURES = {
     "zb_gemm_small_supported": [c_int, c_int, c_int],
     "zb_gemm_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                       c_int, c_void_p],
+    "zb_gemm_tc_supported": [c_int, c_int, c_int, c_longlong, c_int, c_int],
+    "zb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
     "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
@@ -134,11 +136,13 @@ def library_path() -> str:
 
 
 LAUNCHES = 0      # kernels of this package launched so far (the bench reports the count of a timed region)
+LAUNCH_COUNTS: dict[str, int] = {}      # the same by entry point
 
 
 def _check(rc: int, name: str, kernels: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += kernels
+    LAUNCH_COUNTS[name] = LAUNCH_COUNTS.get(name, 0) + kernels
     if rc != 0:
         detail = ""
         if rc == 2:
@@ -175,6 +179,22 @@ def _i32(*tensors: torch.Tensor) -> None:
 def new_status(device: torch.device | str = "cuda") -> torch.Tensor:
     """The device status word kernels report into: [code, detail, index, unused]."""
     return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_device_status: dict = {}
+
+
+def device_status(device: torch.device | str) -> torch.Tensor:
+    """The one status word of a device: kernels that are called without a status word report into it,
+    and a model runner takes it as its own, so that what a product deep inside a part reports
+    (a wait that ran out) is seen by the check after the step."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device(device.type, torch.cuda.current_device())
+    word = _device_status.get(device)
+    if word is None:
+        word = _device_status[device] = new_status(device)
+    return word
 
 
 def check_status(status: torch.Tensor, where: str = "step") -> None:
@@ -658,6 +678,44 @@ def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     _check(library().zb_gemm_small(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                                    DTYPE_CODE[out_dtype], int(swiglu), _stream()), "gemm_small")
     return out
+
+
+GEMM_TC_MIN_ROWS = 1024       # from here on the product with the activation in its epilogue beats the library's
+                              # product followed by the activation kernel (measured at widths 1024 to 5120)
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
+    """True if the tcgen05 product takes x [M, K] times w [N, K] transposed (bfloat16, K a multiple of 8)."""
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.shape[1] == w.shape[1] and x.stride(1) == 1 and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return False
+    M, K = x.shape
+    N = w.shape[0]
+    ldy = (N // 2 if swiglu else N + 7) // 8 * 8
+    return bool(library().zb_gemm_tc_supported(M, N, K, x.stride(0), ldy, int(swiglu)))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int = 0,
+            status: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed on tcgen05 tensor cores, bfloat16 with float32 sums in
+    tensor memory.  With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
+    rows, and the result is silu(gate) * up, [M, N / 2], taken from the float32 sums and rounded once.
+    ``block_n`` (256, 128; 0: chosen) is the width of an output tile.  ``status`` (default: the
+    device's status word) receives a report if a wait inside the kernel ran out."""
+    _cuda(x, w)
+    _require(gemm_tc_supported(x, w, swiglu), "gemm_tc takes bfloat16 x [M, K] and contiguous w [N, K], K a multiple of 8, "
+             "16-byte aligned; with swiglu N a multiple of 16")
+    M, K = x.shape
+    N = w.shape[0]
+    width = N // 2 if swiglu else N
+    ldy = (width + 7) // 8 * 8
+    out = torch.empty((M, ldy), dtype=torch.bfloat16, device=x.device)
+    if status is None:
+        status = device_status(x.device)
+    _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, int(swiglu), int(block_n),
+                                _ptr(status), _stream()), "gemm_tc")
+    return out if ldy == width else out[:, :width]
 
 
 # ------------------------------------------------------------------ chains of small products

@@ -6,6 +6,7 @@
     python -m zephyr_b200.kernels.timing fused_chain --rows 8 --hidden 1024 --ffn 3072
     python -m zephyr_b200.kernels.timing sample --rows 8 --vocab 151936
     python -m zephyr_b200.kernels.timing products --tokens 2048 --hidden 1024 --ffn 3072
+    python -m zephyr_b200.kernels.timing gemm_tc --tokens 2048 --n 6144 --k 1024 [--swiglu] [--library]
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
 that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
@@ -271,7 +272,33 @@ def products(args) -> dict:
             "us": round(us, 2), "flops": flops, "tflops": round(flops / us / 1e6, 1)}
 
 
-CASES = {"fused_chain": fused_chain, "products": products, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
+def gemm_tc(args) -> dict:
+    """One product x [tokens, k] w[n, k]^T on this package's tcgen05 kernel (``--swiglu``: with the
+    activation in its epilogue; ``--library``: the vendor library's product, and the activation
+    kernel after it, on the same operands)."""
+    device = torch.device("cuda")
+    T, N, K = args.tokens, args.n, args.k
+    rnd = lambda *shape: torch.randn(shape, device=device, dtype=torch.bfloat16) * 0.05
+    weights = [rnd(N, K) for _ in range(_copies(2 * N * K))]
+    x = rnd(T, K)
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+
+    def run(i):
+        w = weights[i % len(weights)]
+        if args.library:
+            y = ops.linear(x, w)
+            if args.swiglu:
+                ops.silu_mul(y, blocked=True)
+        else:
+            ops.gemm_tc(x, w, swiglu=args.swiglu, block_n=args.block_n, status=status)
+    us = _time(run, args.warmup, args.iters)
+    flops = 2.0 * T * N * K
+    return {"kernel": "library product" if args.library else "gemm_tc_kernel", "tokens": T, "n": N, "k": K,
+            "swiglu": args.swiglu, "block_n": args.block_n, "us": round(us, 2), "flops": flops,
+            "tflops": round(flops / us / 1e6, 1), "status": status.tolist()}
+
+
+CASES = {"gemm_tc": gemm_tc, "fused_chain": fused_chain, "products": products, "decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm_small": gemm_small,
          "sample": sample}
 
 
@@ -306,6 +333,8 @@ def main(argv=None) -> int:
     parser.add_argument("--sequential-pages", action="store_true",
                         help="block tables that walk the pool in order instead of a random permutation")
     parser.add_argument("--legacy-prefill", action="store_true", help="prompt attention on mma.sync even where tcgen05 applies")
+    parser.add_argument("--library", action="store_true", help="gemm_tc: time the vendor library's product instead")
+    parser.add_argument("--block-n", type=int, default=0, help="gemm_tc: width of an output tile (256, 128; 0: chosen)")
     parser.add_argument("--resident", action="store_true",
                         help="do not rotate operands: what fits in L2 is read from L2")
     args = parser.parse_args(argv)
