@@ -191,7 +191,8 @@ def test_gemm_small_refuses(ops, cuda_device):
 
 # ------------------------------------------------------- the tcgen05 product for many rows
 TC_GEMM_CASES = [(128, 256, 64, 0), (200, 264, 136, 0), (2048, 1024, 3072, 0), (333, 250, 1000, 128), (333, 250, 1000, 256),
-                 (17, 1024, 2048, 128), (1000, 4096, 1024, 256), (129, 8, 8, 0), (2500, 1544, 520, 0)]
+                 (17, 1024, 2048, 128), (1000, 4096, 1024, 256), (129, 8, 8, 0), (2500, 1544, 520, 0),
+                 (256, 256, 64, 2), (300, 520, 200, 2), (2500, 1544, 520, 2), (5000, 6144, 1024, 2)]
 
 
 @pytest.mark.parametrize("M,N,K,block_n", TC_GEMM_CASES)
@@ -218,7 +219,7 @@ def test_gemm_tc_product(ops, cuda_device, M, N, K, block_n):
 
 
 @pytest.mark.parametrize("M,I,K,block_n", [(128, 128, 64, 0), (2048, 3072, 1024, 0), (300, 200, 96, 128), (300, 200, 96, 256),
-                                           (1111, 520, 264, 0)])
+                                           (1111, 520, 264, 0), (300, 200, 96, 2), (2048, 3072, 1024, 2), (1111, 520, 264, 2)])
 def test_gemm_tc_fused_swiglu(ops, cuda_device, M, I, K, block_n):
     x = rand((M, K), torch.bfloat16, cuda_device, 142)
     gate = rand((I, K), torch.bfloat16, cuda_device, 143, 0.2)

@@ -680,7 +680,7 @@ def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     return out
 
 
-GEMM_TC_MIN_ROWS = 1024       # from here on the product with the activation in its epilogue beats the library's
+GEMM_TC_MIN_ROWS = 512        # from here on the product with the activation in its epilogue beats the library's
                               # product followed by the activation kernel (measured at widths 1024 to 5120)
 
 
@@ -701,7 +701,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int
     """x [M, K] times w [N, K] transposed on tcgen05 tensor cores, bfloat16 with float32 sums in
     tensor memory.  With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
     rows, and the result is silu(gate) * up, [M, N / 2], taken from the float32 sums and rounded once.
-    ``block_n`` (256, 128; 0: chosen) is the width of an output tile.  ``status`` (default: the
+    ``block_n`` is the width of an output tile (256, 128; 2: tiles of 256 x 256 on pairs of SMs; 0: chosen).  ``status`` (default: the
     device's status word) receives a report if a wait inside the kernel ran out."""
     _cuda(x, w)
     _require(gemm_tc_supported(x, w, swiglu), "gemm_tc takes bfloat16 x [M, K] and contiguous w [N, K], K a multiple of 8, "
