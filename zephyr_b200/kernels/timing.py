@@ -252,7 +252,8 @@ def fused_chain(args) -> dict:
 
 def products(args) -> dict:
     """A layer's four matrix products for a prompt portion of ``--tokens`` tokens, as the engine runs
-    them (the vendor library's tensor-core product for bfloat16 beyond 16 rows)."""
+    them: the vendor library's tensor-core product for bfloat16 beyond 16 rows, and for gate/up, from
+    ``ops.GEMM_TC_MIN_ROWS`` rows on, this package's tcgen05 product with the activation in its epilogue."""
     device = torch.device("cuda")
     T, d, q, ffn, qkv = args.tokens, args.hidden, args.heads * args.head_dim, args.ffn, (args.heads + 2 * args.kv_heads) * args.head_dim
     layer_bytes = 2 * (d * q + 2 * ffn * d + d * ffn + qkv * d)
@@ -264,11 +265,14 @@ def products(args) -> dict:
         w_qkv, w_o, w_gu, w_down = layers[i % len(layers)]
         ops.linear(x, w_qkv)
         ops.linear(attn, w_o)
-        ops.linear(x, w_gu)
+        if T >= ops.GEMM_TC_MIN_ROWS and ops.gemm_tc_supported(x, w_gu, swiglu=True):
+            ops.gemm_tc(x, w_gu, swiglu=True)
+        else:
+            ops.silu_mul(ops.linear(x, w_gu), blocked=True)
         ops.linear(act, w_down)
     us = _time(run, args.warmup, args.iters)
     flops = 2.0 * T * (qkv * d + d * q + 2 * ffn * d + d * ffn)
-    return {"kernel": "library products (cuBLASLt)", "tokens": T, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv,
+    return {"kernel": "a layer's prompt products (cuBLASLt; gate/up + activation on tcgen05)", "tokens": T, "hidden": d, "q": q, "ffn": ffn, "qkv": qkv,
             "us": round(us, 2), "flops": flops, "tflops": round(flops / us / 1e6, 1)}
 
 
