@@ -13,8 +13,11 @@
 //     tensor memory (2 x BN columns of float32); tcgen05.commit frees the stage for the copies and,
 //     after a tile's last product, hands the accumulator to the epilogue;
 //   * warps 2..5: a thread owns one output row (its TMEM lane), reads 32 columns at a time, applies
-//     the epilogue in float32, rounds once and stores 64 (32 with the activation) contiguous bytes.
-//     While they work on one accumulator the products of the next tile fill the other.
+//     the epilogue in float32, rounds once and puts its pieces into the warp's staging buffer in
+//     shared memory, from where tiled TMA stores of 64 columns x 32 rows write them (rows and columns
+//     beyond the matrix are left out by the copy engine).  While they work on one accumulator the
+//     products of the next tile fill the other.
+// A second form of the kernel runs a tile of 256 x 256 on a pair of SMs (further down).
 // The activation reads the sums in float32, as the decode kernels do (one rounding; the
 // reference rounds gate and up to bfloat16 first, src/layer/mlp.cpp:16-36, src/layer/activation.cu:31-33).
 // Every wait is bounded and reports instead of hanging; tensor memory is given back on every path.
