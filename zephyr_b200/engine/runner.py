@@ -344,7 +344,7 @@ class ModelRunner:
             # long as the record holds them.
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            with ops.capture(graph, pool=self._graph_pool):
                 record["logits"] = self.model.forward(ctx)
             record["kernels"] = ops.LAUNCHES - launched     # this package's kernels inside the graph
             record["graph"] = graph

@@ -7,7 +7,9 @@ any kind: if the library cannot be built or loaded, or a kernel refuses a shape,
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import gc
 import math
 import os
 import struct
@@ -174,6 +176,24 @@ def _cuda(*tensors: torch.Tensor | None) -> None:
 def _i32(*tensors: torch.Tensor) -> None:
     for t in tensors:
         _require(t.dtype == torch.int32 and t.is_contiguous(), "index tensors must be contiguous int32")
+
+
+@contextlib.contextmanager
+def capture(graph: "torch.cuda.CUDAGraph", **kwargs):
+    """``torch.cuda.graph`` with the garbage collector held still.  A collection that happens to run
+    inside a capture may destroy an older CUDA graph (one of a runner that was dropped, kept alive
+    until then by a reference cycle); the runtime forbids that while any stream captures and the
+    capture is lost ("operation failed due to a previous error during capture").  What is
+    unreachable is collected before the capture begins."""
+    gc.collect()
+    enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, **kwargs):
+            yield
+    finally:
+        if enabled:
+            gc.enable()
 
 
 def new_status(device: torch.device | str = "cuda") -> torch.Tensor:

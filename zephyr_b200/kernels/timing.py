@@ -38,7 +38,7 @@ def _time(run, warmup: int, iters: int) -> float:
     stream = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
+        with ops.capture(graph, stream=stream):
             for i in range(iters):
                 run(warmup + i)
         graph.replay()

@@ -91,6 +91,7 @@ class Sampler:
         (sharing the model runner's lets a single read per step cover both)."""
         self.device = torch.device(device)
         self.status = status if status is not None else ops.new_status(self.device)
+        self._pinned_rings: dict = {}
 
     def _launch(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                 generators: Sequence[MT19937_64 | None], histories: Sequence[Sequence[int]] | None,
@@ -155,17 +156,31 @@ class Sampler:
         for p in params:
             p.validate(logits.shape[1])
         out = self._launch(logits, params, generators, histories, prompt_lengths)
-        # One read brings the ids and the status word: every wait for the device costs the step time.
-        combined = torch.cat([out.ids, self.status])
-        host_ids = torch.empty(combined.shape, dtype=combined.dtype, pin_memory=True)
-        host_ids.copy_(combined, non_blocking=True)
+        # One wait brings the ids and the status word: every wait for the device costs the step time.
+        # Both are copied into one pinned buffer taken from a small ring (no kernel, no allocation).
+        count, words = out.ids.numel(), self.status.numel()
+        host_ids = self._pinned("ids", count + words, out.ids.dtype)
+        host_ids[:count].copy_(out.ids, non_blocking=True)
+        host_ids[count:].copy_(self.status, non_blocking=True)
         host_values = None
         if out.logprobs is not None:
-            host_values = torch.empty(out.logprobs.shape, dtype=out.logprobs.dtype, pin_memory=True)
-            host_values.copy_(out.logprobs, non_blocking=True)
+            host_values = self._pinned("values", out.logprobs.numel(), out.logprobs.dtype)
+            host_values.copy_(out.logprobs.reshape(-1), non_blocking=True)
         done = torch.cuda.Event()
         done.record()
         return PendingSample(list(params), out.offsets, logits.shape[1], host_ids, host_values, done, out.ids)
+
+    PINNED_RING = 4       # selections that may be under way or unread at a time (the engine keeps at most two)
+
+    def _pinned(self, what: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A pinned host buffer of ``numel`` elements: the ring's next one, grown when too small."""
+        ring = self._pinned_rings.setdefault((what, dtype), {"turn": 0, "buffers": [None] * self.PINNED_RING})
+        turn = ring["turn"]
+        ring["turn"] = (turn + 1) % self.PINNED_RING
+        buffer = ring["buffers"][turn]
+        if buffer is None or buffer.numel() < numel:
+            buffer = ring["buffers"][turn] = torch.empty(max(numel, 64), dtype=dtype, pin_memory=True)
+        return buffer[:numel]
 
     def finish(self, pending: "PendingSample") -> list[SamplingResult]:
         """Wait for a launched selection; one ``SamplingResult`` per row."""
