@@ -496,22 +496,35 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
       tc_fence_after_sync();
       const float l_row = half_note[n_tiles & 1][0][r] + half_note[n_tiles & 1][1][r];
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-      __nv_bfloat16* dst = a.out + (static_cast<size_t>(tok0 + r) * a.nh + head) * TC_HD;
-#pragma unroll 1
-      for (int c4 = half * (TC_HD / 64); c4 < (half + 1) * (TC_HD / 64); ++c4) {
-        unsigned v[32];
-        tmem_ld32(tmem_o + c4 * 32, v);
-        tc_wait_ld();
-        if (r < n_tok) {
+      // The keys' and values' stages are free by now (every product is complete): each warp puts its 32
+      // rows x 64 columns there, 16-byte pieces permuted by the row so that neither the writes (a
+      // thread a row) nor the reads (eight threads a row) meet in a bank, and then writes whole
+      // 128-byte row pieces, four rows an instruction.  (A thread storing its own row's pieces
+      // touches 32 rows with every instruction, which cost 1.4 us a CTA.)
+      unsigned char* stage_out = kv_s + warp * 4096;
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 o4;
-            o4.x = pack_bf16(__uint_as_float(v[8 * q4]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
-            o4.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
-            o4.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
-            o4.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c4 * 32 + q4 * 8) = o4;
-          }
+      for (int cc = 0; cc < TC_HD / 64; ++cc) {
+        unsigned v[32];
+        tmem_ld32(tmem_o + (half * (TC_HD / 64) + cc) * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 o4;
+          o4.x = pack_bf16(__uint_as_float(v[8 * q4]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+          o4.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+          o4.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+          o4.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage_out + lane * 128 + (((cc * 4 + q4) ^ (lane & 7)) << 4)) = o4;
+        }
+      }
+      __syncwarp();
+      const int row_base = (warp & 3) * 32, piece = lane & 7;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3);
+        if (row_base + rr < n_tok) {
+          const uint4 o4 = *reinterpret_cast<const uint4*>(stage_out + rr * 128 + ((piece ^ (rr & 7)) << 4));
+          *reinterpret_cast<uint4*>(a.out + (static_cast<size_t>(tok0 + row_base + rr) * a.nh + head) * TC_HD + half * 64 + piece * 8) = o4;
         }
       }
     }
