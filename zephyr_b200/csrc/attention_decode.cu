@@ -243,6 +243,123 @@ __device__ __forceinline__ bool new_token_head(const __nv_bfloat16* src, const v
   return mine;
 }
 
+// Whether merge_many_parts finds room for `n_parts` splits where the consumers' parts lay.
+__device__ __forceinline__ bool merge_staging_fits(int n_parts, int g, int hd) {
+  const int n_vec = g * hd / 4;
+  return n_parts * g * 2 + g + 4 + (n_vec <= DEC_CONSUMERS * 16 ? n_vec * 4 : 0) <= DEC_CONSUMERS * g * hd;
+}
+
+// The last CTA of a (row, key/value head) pair to arrive merges the pair's more than a few splits;
+// called by the 128 consumer threads together.  A function of its own: inlined, its registers
+// changed the allocation of the kernel's main loop, which runs at the register limit.
+// All loads of a round are issued before the first is used: a merge costs a few round trips to the
+// L2, not one per split.  A thread takes whole vectors of four floats (16-byte loads), and where the
+// vectors leave half of the threads idle, two halves of the threads share a vector's splits (even
+// and odd ones) and add their sums at the end.  (Element by element the compiler strung a thread's
+// loads one behind the other: 0.28 us a split.)
+struct MergeJob {                        // what merge_many_parts needs of the launch and the item, by value
+  const float* part_o;
+  const float* part_ml;
+  __nv_bfloat16* out;                    // the pair's first output element
+  long long pair_start;
+  int n_parts, merge_first, per_range, split_size, g;
+  __device__ __forceinline__ int slot(int k) const {
+    return split_size > 0 ? merge_first + k : balanced_slot(pair_start, merge_first + k, per_range);
+  }
+};
+
+template <int HD>
+__device__ __noinline__ void merge_many_parts(const MergeJob job, float* merge_o) {
+  constexpr int BATCH = 8;
+  const int g = job.g;
+  const struct { int n_parts; } it = {job.n_parts};
+  const int ctid = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ml_s = merge_o;                 // [n_parts][g][2], where the consumers' parts lay (they are merged by now)
+  const int n_vec = g * HD / 4;          // the result as vectors of four floats
+  const int groups = n_vec <= DEC_CONSUMERS * 16 ? 2 : 1, per_group = DEC_CONSUMERS * 32 / groups;
+  const int grp = ctid / per_group, idx = ctid - grp * per_group;
+  float4* sums_s = reinterpret_cast<float4*>(
+      reinterpret_cast<uintptr_t>(merge_o + it.n_parts * g * 2 + g + 3) & ~static_cast<uintptr_t>(15));    // behind the weights
+    // This thread's first vector's shares of its first BATCH splits are asked for before the maxima
+    // are staged, so that both travel at the same time.
+    float4 first[BATCH];
+    {
+      const int h = idx * 4 / HD, d = idx * 4 - h * HD;
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int k = grp + u * groups;
+        first[u] = idx < n_vec && k < it.n_parts
+                       ? __ldcg(reinterpret_cast<const float4*>(&job.part_o[(static_cast<size_t>(job.slot(k)) * g + h) * HD + d]))
+                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    for (int e = ctid; e < it.n_parts * g * 2; e += DEC_CONSUMERS * 32) {
+      const int k = e / (g * 2), rest = e - k * g * 2;
+      ml_s[e] = __ldcg(&job.part_ml[static_cast<size_t>(job.slot(k)) * g * 2 + rest]);
+    }
+    consumer_barrier();
+    // One warp per head turns the maxima into the splits' weights, exp2(m_k - max), in place, and
+    // leaves the head's weighted sum of the l_k behind the list: the vectors below then cost a
+    // multiply-add per split and element.
+    for (int h = warp; h < g; h += DEC_CONSUMERS) {
+      float mx = -INFINITY;
+      for (int k = lane; k < it.n_parts; k += 32) mx = fmaxf(mx, ml_s[(k * g + h) * 2]);
+      mx = warp_max(mx);
+      float lsum = 0.0f;
+      for (int k = lane; k < it.n_parts; k += 32) {
+        const float f = exp2f(ml_s[(k * g + h) * 2] - mx);
+        lsum += ml_s[(k * g + h) * 2 + 1] * f;
+        ml_s[(k * g + h) * 2] = f;
+      }
+      lsum = warp_sum(lsum);
+      if (lane == 0) ml_s[it.n_parts * g * 2 + h] = lsum;
+    }
+    consumer_barrier();
+    for (int v0 = 0; v0 < n_vec; v0 += per_group) {         // the same number of turns for every thread: barriers inside
+      const int v = v0 + idx;
+      const bool mine = v < n_vec;
+      const int h = mine ? v * 4 / HD : 0, d = mine ? v * 4 - h * HD : 0;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int kb = grp; kb < it.n_parts; kb += groups * BATCH) {
+        float4 po[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+          const int k = kb + u * groups;
+          if (v0 == 0 && kb == grp) po[u] = first[u];
+          else
+            po[u] = mine && k < it.n_parts
+                        ? __ldcg(reinterpret_cast<const float4*>(&job.part_o[(static_cast<size_t>(job.slot(k)) * g + h) * HD + d]))
+                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {                      // a fixed order: the group's splits in the order of the context
+          const int k = kb + u * groups;
+          if (k < it.n_parts) {
+            const float f = ml_s[(k * g + h) * 2];
+            acc.x += po[u].x * f; acc.y += po[u].y * f; acc.z += po[u].z * f; acc.w += po[u].w * f;
+          }
+        }
+      }
+      if (groups == 2) {
+        if (grp == 1 && mine) sums_s[idx] = acc;
+        consumer_barrier();
+        if (grp == 0 && mine) {
+          const float4 other = sums_s[idx];
+          acc.x += other.x; acc.y += other.y; acc.z += other.z; acc.w += other.w;
+        }
+      }
+      if (grp == 0 && mine) {
+        const float l = ml_s[it.n_parts * g * 2 + h];
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(&job.out[v * 4]) = packed;
+      }
+      if (groups == 2 && v0 + per_group < n_vec) consumer_barrier();     // the sums' buffer is read before the next turn writes it
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 paged_decode_kernel(const DecodeArgs a) {
@@ -691,99 +808,52 @@ paged_decode_kernel(const DecodeArgs a) {
     if (!is_last) continue;
     // All loads of a round are issued before the first is used: a merge costs a few round trips to
     // the L2, not one per split.
-    constexpr int ROUND = 4, WIDE = 16;
-    float* ml_s = merge_o;                 // [n_parts][g][2], where the consumers' parts lay (they are merged by now)
-    const bool staged = it.n_parts > ROUND && it.n_parts * 2 + 1 <= DEC_CONSUMERS * HD;
-    // This thread's first two output elements' shares of the first WIDE splits, asked for before
-    // the maxima are staged so that both travel at the same time.
-    constexpr int AHEAD = 2;
-    float first_o[AHEAD][WIDE];
+    constexpr int ROUND = 4;
+    const bool staged = it.n_parts > ROUND && merge_staging_fits(it.n_parts, g, HD);
     if (staged) {
-#pragma unroll
-      for (int u = 0; u < AHEAD; ++u) {
-        const int e = ctid + u * DEC_CONSUMERS * 32;
-        if (e >= g * HD) break;
+      MergeJob job;
+      job.part_o = a.part_o; job.part_ml = a.part_ml; job.out = a.out + out_base;
+      job.pair_start = it.pair_start;
+      job.n_parts = it.n_parts; job.merge_first = it.merge_first; job.per_range = per_range; job.split_size = a.split_size; job.g = g;
+      merge_many_parts<HD>(job, merge_o);
+    } else {
+      for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
         const int h = e / HD, d = e - h * HD;
+        float acc = 0.0f, l = 0.0f;
+        if (it.n_parts <= ROUND) {
+          float pm[ROUND], pl[ROUND], po[ROUND];
 #pragma unroll
-        for (int k = 0; k < WIDE; ++k)
-          first_o[u][k] = k < it.n_parts
-                              ? __ldcg(&a.part_o[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * HD + d]) : 0.0f;
-      }
-      for (int e = ctid; e < it.n_parts * g * 2; e += DEC_CONSUMERS * 32) {
-        const int k = e / (g * 2), rest = e - k * g * 2;
-        ml_s[e] = __ldcg(&a.part_ml[static_cast<size_t>(part_slot(a, it, k, per_range)) * g * 2 + rest]);
-      }
-      consumer_barrier();
-      // One warp per head turns the maxima into the splits' weights, exp2(m_k - max), in place, and
-      // leaves the head's weighted sum of the l_k behind the list: the elements below then cost a
-      // multiply-add per split (with one warp per scheduler every instruction's latency shows).
-      for (int h = warp; h < g; h += DEC_CONSUMERS) {
-        float mx = -INFINITY;
-        for (int k = lane; k < it.n_parts; k += 32) mx = fmaxf(mx, ml_s[(k * g + h) * 2]);
-        mx = warp_max(mx);
-        float lsum = 0.0f;
-        for (int k = lane; k < it.n_parts; k += 32) {
-          const float f = exp2f(ml_s[(k * g + h) * 2] - mx);
-          lsum += ml_s[(k * g + h) * 2 + 1] * f;
-          ml_s[(k * g + h) * 2] = f;
-        }
-        lsum = warp_sum(lsum);
-        if (lane == 0) ml_s[it.n_parts * g * 2 + h] = lsum;
-      }
-      consumer_barrier();
-    }
-    for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
-      const int h = e / HD, d = e - h * HD;
-      float acc = 0.0f, l = 0.0f;
-      if (it.n_parts <= ROUND) {
-        float pm[ROUND], pl[ROUND], po[ROUND];
+          for (int k = 0; k < ROUND; ++k) {
+            pm[k] = -INFINITY; pl[k] = 0.0f; po[k] = 0.0f;
+            if (k < it.n_parts) {
+              const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
+              pm[k] = __ldcg(&a.part_ml[slot * 2]);
+              pl[k] = __ldcg(&a.part_ml[slot * 2 + 1]);
+              po[k] = __ldcg(&a.part_o[slot * HD + d]);
+            }
+          }
+          float mx = pm[0];
 #pragma unroll
-        for (int k = 0; k < ROUND; ++k) {
-          pm[k] = -INFINITY; pl[k] = 0.0f; po[k] = 0.0f;
-          if (k < it.n_parts) {
+          for (int k = 1; k < ROUND; ++k) mx = fmaxf(mx, pm[k]);
+#pragma unroll
+          for (int k = 0; k < ROUND; ++k) {                  // in the order of the context: a fixed order
+            const float f = k < it.n_parts ? exp2f(pm[k] - mx) : 0.0f;
+            acc += po[k] * f;
+            l += pl[k] * f;
+          }
+        } else {
+          float mx = -INFINITY;
+          for (int k = 0; k < it.n_parts; ++k)
+            mx = fmaxf(mx, __ldcg(&a.part_ml[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * 2]));
+          for (int k = 0; k < it.n_parts; ++k) {
             const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
-            pm[k] = __ldcg(&a.part_ml[slot * 2]);
-            pl[k] = __ldcg(&a.part_ml[slot * 2 + 1]);
-            po[k] = __ldcg(&a.part_o[slot * HD + d]);
+            const float f = exp2f(__ldcg(&a.part_ml[slot * 2]) - mx);
+            acc += __ldcg(&a.part_o[slot * HD + d]) * f;
+            l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
           }
         }
-        float mx = pm[0];
-#pragma unroll
-        for (int k = 1; k < ROUND; ++k) mx = fmaxf(mx, pm[k]);
-#pragma unroll
-        for (int k = 0; k < ROUND; ++k) {                  // in the order of the context: a fixed order
-          const float f = k < it.n_parts ? exp2f(pm[k] - mx) : 0.0f;
-          acc += po[k] * f;
-          l += pl[k] * f;
-        }
-      } else if (staged) {
-        for (int k0 = 0; k0 < it.n_parts; k0 += WIDE) {
-          float po[WIDE];
-#pragma unroll
-          for (int k = 0; k < WIDE; ++k) {
-            if (k0 == 0 && e == ctid) po[k] = first_o[0][k];
-            else if (k0 == 0 && e == ctid + DEC_CONSUMERS * 32) po[k] = first_o[1][k];
-            else
-              po[k] = k0 + k < it.n_parts
-                          ? __ldcg(&a.part_o[(static_cast<size_t>(part_slot(a, it, k0 + k, per_range)) * g + h) * HD + d]) : 0.0f;
-          }
-#pragma unroll
-          for (int k = 0; k < WIDE; ++k)                     // in the order of the context: a fixed order
-            if (k0 + k < it.n_parts) acc += po[k] * ml_s[((k0 + k) * g + h) * 2];
-        }
-        l = ml_s[it.n_parts * g * 2 + h];
-      } else {
-        float mx = -INFINITY;
-        for (int k = 0; k < it.n_parts; ++k)
-          mx = fmaxf(mx, __ldcg(&a.part_ml[(static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h) * 2]));
-        for (int k = 0; k < it.n_parts; ++k) {
-          const size_t slot = static_cast<size_t>(part_slot(a, it, k, per_range)) * g + h;
-          const float f = exp2f(__ldcg(&a.part_ml[slot * 2]) - mx);
-          acc += __ldcg(&a.part_o[slot * HD + d]) * f;
-          l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
-        }
+        a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
       }
-      a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
     }
     if (ctid == 0) a.counters[it.r * a.nkv + it.kvh] = 0;    // left as it was found, for the next call
   }

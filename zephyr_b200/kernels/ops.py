@@ -484,15 +484,15 @@ def _decode_workspace(device: torch.device, floats: int, counters: int) -> tuple
 
 
 def decode_split_size(n_rows: int, nkv: int, max_context: int) -> int:
-    """A size for fixed splits (``paged_decode(..., split_size=...)``): long items cost less per
-    position, short ones spread a small batch over all SMs.  The engine does not use fixed splits:
-    without a split size the kernel spreads the tiles of all rows evenly over its CTAs, so where a
-    row's context is cut, and with that the last bits of its result, depends on what else is decoded
-    beside it."""
-    split = 1024
-    while split > 128 and n_rows * nkv * math.ceil(max_context / split) < _sm_count() - 20:
-        split //= 2
-    return split
+    """A size for fixed splits (``paged_decode(..., split_size=...)``): as many splits of a row's
+    context as give every SM one item and none two (a second round of items would leave most SMs
+    idle), and no split shorter than 128 positions.  ``paged_decode`` takes fixed splits for a
+    handful of rows (4 * rows * key/value heads <= SMs); for more, the kernel spreads the tiles of
+    all rows evenly over its CTAs.  Either way, where a row's context is cut, and with that the last
+    bits of its result, depends on how many rows are decoded beside it."""
+    per_pair = max(1, _sm_count() // max(1, n_rows * nkv))     # splits of a (row, key/value head) pair: one item per SM
+    split = -(-max_context // per_pair)
+    return max(128, -(-split // 32) * 32)
 
 
 _SM_COUNT: dict[int, int] = {}
