@@ -189,6 +189,59 @@ def test_gemm_small_refuses(ops, cuda_device):
     assert ops.linear(x, w).shape == (65, 32)                            # the library product takes over
 
 
+# ------------------------------------------------------- seeded fill
+def philox_4x32_10(counter: int, key: int) -> list[int]:
+    """The published Philox 4x32 generator with ten rounds (Salmon et al. 2011), counter in the two low words."""
+    m0, m1, w0, w1, mask = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85, 0xFFFFFFFF
+    c = [counter & mask, (counter >> 32) & mask, 0, 0]
+    k = [key & mask, (key >> 32) & mask]
+    for _ in range(10):
+        p0, p1 = m0 * c[0], m1 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k[0], p1 & mask, (p0 >> 32) ^ c[3] ^ k[1], p0 & mask]
+        k = [(k[0] + w0) & mask, (k[1] + w1) & mask]
+    return c
+
+
+def ref_normals(n: int, key: int) -> torch.Tensor:
+    out = []
+    for i in range((n + 3) // 4):
+        w = philox_4x32_10(i, key)
+        for a, b in ((w[0], w[1]), (w[2], w[3])):
+            u1, u2 = ((a >> 8) + 1) / 16777216.0, (b >> 8) / 16777216.0
+            radius = math.sqrt(-2.0 * math.log(u1))
+            out += [radius * math.cos(2 * math.pi * u2), radius * math.sin(2 * math.pi * u2)]
+    return torch.tensor(out[:n], dtype=torch.float64)
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_fill_normal(ops, cuda_device, n):
+    key = 0x9E3779B97F4A7C15 ^ n
+    got = ops.fill_normal(torch.empty(n, dtype=torch.float32, device=cuda_device), key, 0.0, 1.0)
+    head = min(n, 2000)
+    assert (got[:head].double().cpu() - ref_normals(head, key)).abs().max() <= 2e-5      # float32 log, sqrt, sin and cos
+    # the same values scaled and shifted, rounded once to bfloat16; every element written, none beyond
+    wide = torch.full((n + 8,), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.fill_normal(wide[:n], key, 1.0, 0.02)
+    assert torch.equal(wide[:n], (got * 0.02 + 1.0).to(torch.bfloat16)) and bool((wide[n:] == 7.0).all())
+    # another key, other values; the same key, the same values
+    assert not torch.equal(ops.fill_normal(torch.empty_like(got), key + 1, 0.0, 1.0), got)
+    assert torch.equal(ops.fill_normal(torch.empty_like(got), key, 0.0, 1.0), got)
+    if n >= 4096:
+        assert abs(float(got.mean())) < 5.0 / math.sqrt(n) and abs(float(got.std()) - 1.0) < 5.0 / math.sqrt(n)
+
+
+def test_random_weights_on_the_device(cuda_device):
+    from zephyr_b200.weights.loader import ROLE_NORM, RandomWeights, WeightDecl
+    decls = {"a.weight": WeightDecl((40, 24)), "b.weight": WeightDecl((24,), ROLE_NORM), "c.weight": WeightDecl((40, 24))}
+    store = RandomWeights(decls, 3, torch.bfloat16, device=cuda_device)
+    a, b, c = (store.read(name) for name in decls)
+    assert a.shape == (40, 24) and a.dtype == torch.bfloat16 and a.is_cuda
+    assert not torch.equal(a, c) and abs(float(b.float().mean()) - 1.0) < 0.02 and float(a.float().std()) < 0.03
+    other_order = RandomWeights(dict(reversed(list(decls.items()))), 3, torch.bfloat16, device=cuda_device)
+    assert torch.equal(other_order.read("a.weight"), a)
+    assert not torch.equal(RandomWeights(decls, 4, torch.bfloat16, device=cuda_device).read("a.weight"), a)
+
+
 # ------------------------------------------------------- the tcgen05 product for many rows
 TC_GEMM_CASES = [(128, 256, 64, 0), (200, 264, 136, 0), (2048, 1024, 3072, 0), (333, 250, 1000, 128), (333, 250, 1000, 256),
                  (17, 1024, 2048, 128), (1000, 4096, 1024, 256), (129, 8, 8, 0), (2500, 1544, 520, 0),

@@ -84,6 +84,7 @@ _SIGNATURES = {
     "zb_gemm_small_supported": [c_int, c_int, c_int],
     "zb_gemm_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                       c_int, c_void_p],
+    "zb_fill_normal": [c_void_p, c_longlong, ctypes.c_ulonglong, c_float, c_float, c_int, c_void_p],
     "zb_gemm_tc_supported": [c_int, c_int, c_int, c_longlong, c_int, c_int],
     "zb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
@@ -229,6 +230,16 @@ def check_status(status: torch.Tensor, where: str = "step") -> None:
             buffer.zero_()
         raise KernelError(f"{where}: a kernel reported {STATUS_TEXT.get(code, f'error {code}')} "
                           f"(value {detail}, at element {index})")
+
+
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float) -> torch.Tensor:
+    """Fills a contiguous bfloat16 or float32 tensor with mean + std * z, z standard normal: element i
+    is a function of (key, i) alone (a counter-based generator; see random_fill.cu)."""
+    _cuda(out)
+    _require(out.is_contiguous() and out.dtype in DTYPE_CODE, "a contiguous bfloat16 or float32 tensor")
+    _check(library().zb_fill_normal(_ptr(out), out.numel(), int(key) & (2**64 - 1), float(mean), float(std),
+                                    DTYPE_CODE[out.dtype], _stream()), "fill_normal")
+    return out
 
 
 # --------------------------------------------------------------------------- elementwise

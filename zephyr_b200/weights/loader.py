@@ -105,12 +105,19 @@ def tensor_seed(seed: int, name: str) -> int:
 
 def random_tensor(seed: int, name: str, decl: WeightDecl, dtype: torch.dtype,
                   device: torch.device | str = "cpu") -> torch.Tensor:
-    """Seeded values for one tensor.  Each tensor has its own generator, so the value of a tensor
-    does not depend on which other tensors exist or in which order they are made.  Values are drawn
-    in float32 and then rounded to ``dtype``.  CPU and CUDA generators give different streams."""
+    """Seeded values for one tensor.  Each tensor has its own key, so the value of a tensor does not
+    depend on which other tensors exist or in which order they are made.  On a CUDA device this
+    package's counter-based fill kernel writes them straight in ``dtype`` (no float32 copy of the
+    tensor; the reference fills random models with a kernel of its own too,
+    deps/ttl/src/kernels/random/random.cu:83-125); on the CPU torch's generator draws them in float32
+    and they are rounded.  The two give different streams: a model folder holds whatever made it."""
     if decl.role not in _ROLE_INIT:
         raise WeightError(f"tensor '{name}' has the unknown role {decl.role!r}")
     mean, std = _ROLE_INIT[decl.role]
+    if torch.device(device).type == "cuda" and dtype in (torch.bfloat16, torch.float32):
+        from ..kernels import ops
+        with torch.cuda.device(device):
+            return ops.fill_normal(torch.empty(decl.shape, dtype=dtype, device=device), tensor_seed(seed, name), mean, std)
     generator = torch.Generator(device=device)
     generator.manual_seed(tensor_seed(seed, name))
     values = torch.randn(decl.shape, generator=generator, dtype=torch.float32, device=device)
