@@ -48,6 +48,14 @@ def test_norm_feed_forward_and_position(model_folders, cuda_device, name, dtype)
     got = block.feed_forward.forward(x)
     expected = plain_mlp(x64, weights, "model.layers.1.mlp")
     assert (got.double().cpu() - expected).abs().max() <= tol(dtype) * max(1.0, float(expected.abs().max()))
+    # As many rows as a long prompt portion brings (in bfloat16 the first product then runs on the
+    # tcgen05 kernel with the activation in its epilogue, at widths that end inside its tiles).
+    many = torch.randn(700, config["hidden_size"], generator=g).to(model.dtype).to(cuda_device)
+    before = ops.LAUNCH_COUNTS.get("gemm_tc", 0)
+    got = block.feed_forward.forward(many)
+    assert dtype == "float32" or ops.LAUNCH_COUNTS.get("gemm_tc", 0) == before + 1
+    expected = plain_mlp(many.double().cpu(), weights, "model.layers.1.mlp")
+    assert (got.double().cpu() - expected).abs().max() <= tol(dtype) * max(1.0, float(expected.abs().max()))
 
     position = block.mixer.position
     nh, hd = config["num_attention_heads"], block.mixer.hd
