@@ -444,6 +444,8 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
+    parser.add_argument("--own-products", action="store_true",
+                        help="with --only: no product on the vendor library (all on this package's tcgen05 kernel)")
     parser.add_argument("--only", choices=("prefill", "decode"), default=None,
                         help="time only the 2048-token prefill, or only the decode step, and print a short line "
                              "(the program a profiler is pointed at)")
@@ -454,6 +456,9 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     if args.only is not None and args.impl == "ours":
+        if args.own_products:
+            from zephyr_b200.kernels import ops
+            ops.USE_LIBRARY_PRODUCTS = False
         engine, config, _ = build_engine(args.shape, args.layers, args.batch, args.context, prefill_together=1)
         if args.only == "prefill":
             ms = device_prefill(engine, PREFILL_TOKENS, 3, args.steps)

@@ -289,6 +289,20 @@ def test_gemm_tc_fused_swiglu(ops, cuda_device, M, I, K, block_n):
     assert (few.double() - got[:8].double()).abs().max() <= 2.0 ** -7 * max(1.0, float(expected[:8].abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K,block_n", [(128, 256, 64, 0), (200, 250, 136, 0), (333, 151, 1000, 2), (40, 1001, 96, 0),
+                                          (1000, 4096, 1024, 2), (17, 517, 264, 128)])
+def test_gemm_tc_float_out(ops, cuda_device, M, N, K, block_n):
+    """The sums as they are (logits): float32 out, any width."""
+    x = rand((M, K), torch.bfloat16, cuda_device, 147)
+    w = rand((N, K), torch.bfloat16, cuda_device, 148, 0.1)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    got = ops.gemm_tc(x, w, block_n=block_n, status=status, out_dtype=torch.float32)
+    expected = x.double() @ w.double().T
+    assert status.tolist()[0] == 0 and got.dtype == torch.float32 and got.shape == (M, N) and got.is_contiguous()
+    assert (got.double() - expected).abs().max() <= 1e-3 * math.sqrt(K)
+    assert torch.equal(got.to(torch.bfloat16), ops.gemm_tc(x, w, block_n=block_n, status=status))       # the same sums, rounded
+
+
 def test_gemm_tc_refuses(ops, cuda_device):
     x = rand((200, 64), torch.bfloat16, cuda_device, 145)
     w = rand((32, 64), torch.bfloat16, cuda_device, 146)

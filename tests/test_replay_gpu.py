@@ -163,6 +163,32 @@ def test_a_step_of_more_than_a_thousand_rows(model_folders, cuda_device, name):
     assert first is None, f"{first}; worst {worst:.3e} at {where}"
 
 
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_without_the_vendor_library(model_folders, cuda_device, monkeypatch, name):
+    """With ``ops.USE_LIBRARY_PRODUCTS`` off no product of the step goes to the vendor library: every
+    bfloat16 product of more than a few rows runs on this package's tcgen05 kernel (the projections,
+    the feed-forward, the head's logits of many wanted rows), and the logits still are the plain
+    implementation's, whole prompts, portions and mixed steps alike."""
+    import torch
+
+    from zephyr_b200.kernels import ops
+    dtype = "bfloat16"
+    folder = model_folders(name, dtype)
+    requests = make_requests(name)
+    monkeypatch.setattr(ops, "USE_LIBRARY_PRODUCTS", False)
+
+    def no_library(*args, **kwargs):
+        raise AssertionError("a product went to the vendor library")
+    monkeypatch.setattr(torch, "mm", no_library)
+    before = ops.LAUNCH_COUNTS.get("gemm_tc", 0)
+    for mode in ("whole", "portions", "mixed"):
+        steps = TRACES[mode](requests)
+        rows = collect(steps, run_in_process(folder, dtype, steps, TINY[name]["page_size"]))
+        first, worst, where = first_mismatch(rows, requests, folder, dtype, f"{name} {mode}, own products")
+        assert first is None, f"{mode}: {first}; worst {worst:.3e} at {where}"
+    assert ops.LAUNCH_COUNTS.get("gemm_tc", 0) > before
+
+
 def test_first_tokens(model_folders, cuda_device):
     """The first tokens of a sequence, one at a time from the very start (position 0 has one key)."""
     for name in ("A", "B", "C"):

@@ -39,6 +39,7 @@ constexpr int GT_WAIT_LIMIT = 1 << 18;
 constexpr int GT_PAIR = 2;                 // as block_n: tiles of 256 x 256 on pairs of SMs
 constexpr int GT_EPI_PLAIN = 0;
 constexpr int GT_EPI_SWIGLU = 1;           // columns 16 j .. 16 j + 7 are gates, 16 j + 8 .. 16 j + 15 their ups
+constexpr int GT_EPI_FLOAT = 2;            // the sums as they are, float32 (logits)
 constexpr int GT_A_BYTES = GT_BM * GT_BK * 2;
 constexpr int GT_STAGING_BYTES = 32 * 128;  // an epilogue warp's 32 rows x 64 output columns on their way out; two a warp
 
@@ -104,11 +105,14 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 template <int BN, int EPI>
 __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigned tmem_row, int row0, int n0, int width,
                                                unsigned char* staging, int& stores, int lane) {
-  // A group = 64 output columns (128 bytes a row): two reads of 32 sums, four with the activation.
-  constexpr int READS = EPI == GT_EPI_SWIGLU ? 4 : 2, PIECES = 4 / (READS / 2);   // 16-byte pieces a read leaves
+  // A group = 128 bytes of a row's output: 64 bfloat16 columns from two reads of 32 sums (four reads with
+  // the activation, which halves them), or 32 float32 columns from one read.
+  constexpr int READS = EPI == GT_EPI_SWIGLU ? 4 : EPI == GT_EPI_FLOAT ? 1 : 2;
+  constexpr int PIECES = 8 / READS;                                  // 16-byte pieces a read leaves
+  constexpr int GROUP_COLUMNS = EPI == GT_EPI_FLOAT ? 32 : 64;       // output columns of a group
 #pragma unroll 1
   for (int group = 0; group < BN / (32 * READS); ++group) {
-    const int out_col = (EPI == GT_EPI_SWIGLU ? n0 / 2 : n0) + group * 64;
+    const int out_col = (EPI == GT_EPI_SWIGLU ? n0 / 2 : n0) + group * GROUP_COLUMNS;
     if (out_col >= width) break;                // the same for the whole warp
     unsigned char* buffer = staging + (stores & 1) * GT_STAGING_BYTES;
     if (stores >= 2) {                          // the store before last has read this buffer
@@ -122,23 +126,27 @@ __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigne
       tc_wait_ld();
 #pragma unroll
       for (int j = 0; j < PIECES; ++j) {
-        float o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (EPI == GT_EPI_SWIGLU) {
-            const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
-            o[i] = silu_fast(gate) * up;
-          } else {
-            o[i] = __uint_as_float(v[8 * j + i]);
-          }
-        }
         // piece q of row `lane` lies where the 128-byte swizzle of the store's map expects it
         const int q = r * PIECES + j;
         uint4 w;
-        w.x = pack_bf16(o[0], o[1]);
-        w.y = pack_bf16(o[2], o[3]);
-        w.z = pack_bf16(o[4], o[5]);
-        w.w = pack_bf16(o[6], o[7]);
+        if (EPI == GT_EPI_FLOAT) {
+          w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (EPI == GT_EPI_SWIGLU) {
+              const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
+              o[i] = silu_fast(gate) * up;
+            } else {
+              o[i] = __uint_as_float(v[8 * j + i]);
+            }
+          }
+          w.x = pack_bf16(o[0], o[1]);
+          w.y = pack_bf16(o[2], o[3]);
+          w.z = pack_bf16(o[4], o[5]);
+          w.w = pack_bf16(o[6], o[7]);
+        }
         *reinterpret_cast<uint4*>(buffer + lane * 128 + ((q ^ (lane & 7)) << 4)) = w;
       }
     }
@@ -470,14 +478,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GT_THREADS, 1) gemm_
   }
 }
 
-// A row-major bfloat16 matrix [rows][cols] with `ld` elements between rows, copied in boxes of 64
-// columns x box_rows rows with the 128-byte swizzle.  Maps are kept: weights come back every step,
+// A row-major matrix [rows][cols] of bfloat16 (or float32) with `ld` elements between rows, copied in
+// boxes of 128 bytes (64 or 32 columns) x box_rows rows with the 128-byte swizzle.  Maps are kept: weights come back every step,
 // and so do the activations of a captured step.
-bool matrix_tensor_map(const void* base, long long rows, int cols, long long ld, int box_rows, CUtensorMap* out) {
+bool matrix_tensor_map(const void* base, long long rows, int cols, long long ld, int box_rows, CUtensorMap* out,
+                       int element_bytes = 2) {
   static std::mutex mutex;
-  static std::map<std::tuple<const void*, long long, int, long long, int>, CUtensorMap> kept;
+  static std::map<std::tuple<const void*, long long, int, long long, int, int>, CUtensorMap> kept;
   std::lock_guard<std::mutex> lock(mutex);
-  const auto key = std::make_tuple(base, rows, cols, ld, box_rows);
+  const auto key = std::make_tuple(base, rows, cols, ld, box_rows, element_bytes);
   const auto found = kept.find(key);
   if (found != kept.end()) {
     *out = found->second;
@@ -486,10 +495,11 @@ bool matrix_tensor_map(const void* base, long long rows, int cols, long long ld,
   const EncodeTiled encode = tensor_map_encoder();
   if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {GT_BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * element_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / element_bytes), static_cast<cuuint32_t>(box_rows)};     // 128 bytes a row
   const cuuint32_t element_strides[2] = {1, 1};
-  if (encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+  if (encode(out, element_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+             const_cast<void*>(base), dims, strides, box, element_strides,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
@@ -536,12 +546,14 @@ using namespace zb;
 
 // 1 if zb_gemm_tc takes these sizes (x [M, K] with ldx elements between rows, w [N, K], y with ldy).
 ZB_API int zb_gemm_tc_supported(int M, int N, int K, long long ldx, int ldy, int epilogue) {
-  if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K || ldy % 8 != 0) return 0;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K || (epilogue != GT_EPI_FLOAT && ldy % 8 != 0)) return 0;
   if (epilogue == GT_EPI_SWIGLU) return N % 16 == 0 && ldy >= N / 2;
+  if (epilogue == GT_EPI_FLOAT) return ldy % 4 == 0 && ldy >= N;          // ldy counts float32 elements then
   return epilogue == GT_EPI_PLAIN && ldy >= N;
 }
 
-// y = epilogue(x w^T), bfloat16.  epilogue 0: y [M, N]; 1: y [M, N / 2] = silu(gate) * up for w's rows in
+// y = epilogue(x w^T), x and w bfloat16.  epilogue 0: y [M, N] bfloat16; 2: the same in float32;
+// 1: y [M, N / 2] = silu(gate) * up for w's rows in
 // blocks of 8 gate rows and their 8 up rows.  block_n is 256 or 128, or 2 for tiles of 256 x 256 on pairs of
 // SMs (0: chosen from the sizes).
 ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, int ldy, int epilogue,
@@ -566,10 +578,13 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   a.M = M; a.N = N; a.K = K;
   a.status = status;
   if (!matrix_tensor_map(x, M, K, ldx, GT_BM, &a.x_map)) return ERR_CUDA;
-  if (!matrix_tensor_map(y, M, epilogue == GT_EPI_SWIGLU ? N / 2 : N, ldy, 32, &a.y_map)) return ERR_CUDA;
+  if (!matrix_tensor_map(y, M, epilogue == GT_EPI_SWIGLU ? N / 2 : N, ldy, 32, &a.y_map, epilogue == GT_EPI_FLOAT ? 4 : 2)) return ERR_CUDA;
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (block_n == GT_PAIR)
-    return epilogue == GT_EPI_SWIGLU ? gemm_tc_pair_launch<GT_EPI_SWIGLU>(a, w, sms, s) : gemm_tc_pair_launch<GT_EPI_PLAIN>(a, w, sms, s);
+    return epilogue == GT_EPI_SWIGLU ? gemm_tc_pair_launch<GT_EPI_SWIGLU>(a, w, sms, s)
+           : epilogue == GT_EPI_FLOAT ? gemm_tc_pair_launch<GT_EPI_FLOAT>(a, w, sms, s) : gemm_tc_pair_launch<GT_EPI_PLAIN>(a, w, sms, s);
+  if (epilogue == GT_EPI_FLOAT)
+    return block_n == 256 ? gemm_tc_launch<256, GT_EPI_FLOAT>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_FLOAT>(a, w, sms, s);
   if (epilogue == GT_EPI_SWIGLU)
     return block_n == 256 ? gemm_tc_launch<256, GT_EPI_SWIGLU>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_SWIGLU>(a, w, sms, s);
   return block_n == 256 ? gemm_tc_launch<256, GT_EPI_PLAIN>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_PLAIN>(a, w, sms, s);

@@ -728,25 +728,28 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) ->
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int = 0,
-            status: torch.Tensor | None = None) -> torch.Tensor:
+            status: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed on tcgen05 tensor cores, bfloat16 with float32 sums in
-    tensor memory.  With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
+    tensor memory; the result in bfloat16, or with ``out_dtype=torch.float32`` the sums as they are.
+    With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
     rows, and the result is silu(gate) * up, [M, N / 2], taken from the float32 sums and rounded once.
     ``block_n`` is the width of an output tile (256, 128; 2: tiles of 256 x 256 on pairs of SMs; 0: chosen).  ``status`` (default: the
     device's status word) receives a report if a wait inside the kernel ran out."""
     _cuda(x, w)
     _require(gemm_tc_supported(x, w, swiglu), "gemm_tc takes bfloat16 x [M, K] and contiguous w [N, K], K a multiple of 8, "
              "16-byte aligned; with swiglu N a multiple of 16")
+    wide = out_dtype == torch.float32
+    _require(out_dtype in (None, torch.bfloat16, torch.float32) and not (wide and swiglu), "bfloat16 out, or float32 without the activation")
     M, K = x.shape
     N = w.shape[0]
     width = N // 2 if swiglu else N
-    ldy = (width + 7) // 8 * 8
-    out = torch.empty((M, ldy), dtype=torch.bfloat16, device=x.device)
+    ldy = (width + 3) // 4 * 4 if wide else (width + 7) // 8 * 8
+    out = torch.empty((M, ldy), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
     if status is None:
         status = device_status(x.device)
-    _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, int(swiglu), int(block_n),
-                                _ptr(status), _stream()), "gemm_tc")
-    return out if ldy == width else out[:, :width]
+    _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, 2 if wide else int(swiglu),
+                                int(block_n), _ptr(status), _stream()), "gemm_tc")
+    return out if ldy == width else out[:, :width].contiguous()
 
 
 # ------------------------------------------------------------------ chains of small products
@@ -869,16 +872,23 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
                                     _ptr(trace), _ptr(scratch) if longest else None, _stream()), "fused_chain")
 
 
+USE_LIBRARY_PRODUCTS = True     # off: every bfloat16 product of more than a few rows runs on this package's tcgen05 kernel
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """y = x w^T.  float32 runs on this package's CUDA-core kernel (no TF32 anywhere).  bfloat16
     with up to 64 rows (a decode step) runs on this package's weight-streaming kernel; larger
     bfloat16 products run on the vendor library's tensor-core product, as the reference's linear
-    layers do (src/layer/linear.cpp:22-24 -> cuBLASLt).  Accumulation is float32 everywhere."""
+    layers do (src/layer/linear.cpp:22-24 -> cuBLASLt), where that is the faster one; with
+    ``USE_LIBRARY_PRODUCTS`` off they run on this package's tcgen05 kernel (``gemm_tc``), so that no
+    library kernel is left on the path.  Accumulation is float32 everywhere."""
     _cuda(x, w)
     if x.dtype == torch.float32:
         return gemm_nt_simt(x, w, out_dtype)
     if x.shape[0] <= SMALL_GEMM_ROWS and gemm_small_supported(x, w):
         return gemm_small(x, w, out_dtype)
+    if not USE_LIBRARY_PRODUCTS and gemm_tc_supported(x, w):
+        return gemm_tc(x, w, out_dtype=out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -265,7 +265,7 @@ def products(args) -> dict:
         w_qkv, w_o, w_gu, w_down = layers[i % len(layers)]
         ops.linear(x, w_qkv)
         ops.linear(attn, w_o)
-        if T >= ops.GEMM_TC_MIN_ROWS and ops.gemm_tc_supported(x, w_gu, swiglu=True):
+        if (T >= ops.GEMM_TC_MIN_ROWS or not ops.USE_LIBRARY_PRODUCTS) and ops.gemm_tc_supported(x, w_gu, swiglu=True):
             ops.gemm_tc(x, w_gu, swiglu=True)
         else:
             ops.silu_mul(ops.linear(x, w_gu), blocked=True)
@@ -338,6 +338,7 @@ def main(argv=None) -> int:
                         help="block tables that walk the pool in order instead of a random permutation")
     parser.add_argument("--legacy-prefill", action="store_true", help="prompt attention on mma.sync even where tcgen05 applies")
     parser.add_argument("--library", action="store_true", help="gemm_tc: time the vendor library's product instead")
+    parser.add_argument("--own-products", action="store_true", help="products: none of them on the vendor library")
     parser.add_argument("--block-n", type=int, default=0, help="gemm_tc: width of an output tile (256, 128; 0: chosen)")
     parser.add_argument("--resident", action="store_true",
                         help="do not rotate operands: what fits in L2 is read from L2")
@@ -345,6 +346,7 @@ def main(argv=None) -> int:
     global RESIDENT, SEQUENTIAL_PAGES
     RESIDENT, SEQUENTIAL_PAGES = args.resident, args.sequential_pages
     ops.USE_TCGEN05_PREFILL = not args.legacy_prefill
+    ops.USE_LIBRARY_PRODUCTS = not args.own_products
     if not torch.cuda.is_available():
         print("a CUDA device is needed", file=sys.stderr)
         return 2

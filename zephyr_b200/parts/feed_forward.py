@@ -52,7 +52,8 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
             hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True)       # product and activation in one kernel
-        elif self.blocked and x.shape[0] >= ops.GEMM_TC_MIN_ROWS and ops.gemm_tc_supported(x, self.w_gate_up, swiglu=True):
+        elif (self.blocked and (x.shape[0] >= ops.GEMM_TC_MIN_ROWS or not ops.USE_LIBRARY_PRODUCTS)
+              and ops.gemm_tc_supported(x, self.w_gate_up, swiglu=True)):
             hidden = ops.gemm_tc(x, self.w_gate_up, swiglu=True)          # the same for a prompt's many rows, on tcgen05
         else:
             hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked)
