@@ -189,6 +189,19 @@ def test_gemm_small_refuses(ops, cuda_device):
     assert ops.linear(x, w).shape == (65, 32)                            # the library product takes over
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,N", [(1, 7), (13, 96), (300, 1000)])
+def test_add_bias(ops, cuda_device, dtype, T, N):
+    y = rand((T, N + 8), dtype, cuda_device, 160)
+    bias = rand((N,), torch.float32, cuda_device, 161)
+    expected = (y[:, :N].float() + bias[None, :]).to(dtype)
+    untouched = y[:, N:].clone()
+    ops.add_bias(y[:, :N], bias)                       # a slice of a wider buffer
+    assert torch.equal(y[:, :N], expected) and torch.equal(y[:, N:], untouched)
+    x, w = rand((T, 64), dtype, cuda_device, 162), rand((N, 64), dtype, cuda_device, 163, 0.1)
+    assert torch.equal(ops.linear(x, w, bias=bias.to(dtype)), ops.add_bias(ops.linear(x, w), bias.to(dtype)))
+
+
 # ------------------------------------------------------- seeded fill
 def philox_4x32_10(counter: int, key: int) -> list[int]:
     """The published Philox 4x32 generator with ten rounds (Salmon et al. 2011), counter in the two low words."""

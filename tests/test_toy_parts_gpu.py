@@ -31,6 +31,7 @@ def toy_classes():
     from zephyr_b200.kernels import ops
     from zephyr_b200.parts import NORMS, Block, FeedForward, InputPart, Mixer, OutputPart, PositionEncoding, lookup
     from zephyr_b200.weights import WeightDecl
+    from zephyr_b200.weights.loader import ROLE_NORM
 
     class NeighbourPairRope(PositionEncoding):
         """Rotates the pairs (2i, 2i + 1) of every head by position * theta^(-2i / head_dim).  It offers
@@ -128,15 +129,18 @@ def toy_classes():
             return self.cap * torch.tanh(logits * (self.scale / self.cap))
 
     class RunningMeanMixer(Mixer):
-        """y_t = W * mean(x_0 .. x_t).  The state is the running sum, one float32 vector per request."""
+        """y_t = W * mean(x_0 .. x_t) + b (a projection with a bias, which the one architecture has
+        not).  The state is the running sum, one float32 vector per request."""
 
         def __init__(self, spec, weights, dtype, device):
             self.weight = weights[spec.params["proj"]]
+            self.bias = weights[spec.params["proj_bias"]]
             self.hidden = spec.params["hidden_size"]
 
         @staticmethod
         def weight_decls(spec):
-            return {spec.params["proj"]: WeightDecl((spec.params["hidden_size"], spec.params["hidden_size"]))}
+            return {spec.params["proj"]: WeightDecl((spec.params["hidden_size"], spec.params["hidden_size"])),
+                    spec.params["proj_bias"]: WeightDecl((spec.params["hidden_size"],), ROLE_NORM)}
 
         @staticmethod
         def cache_spec(spec):
@@ -153,7 +157,7 @@ def toy_classes():
                 if call.writes_cache:
                     state[slot] = sums[-1]
                 start += n
-            return ops.linear(means.to(x.dtype), self.weight)
+            return ops.linear(means.to(x.dtype), self.weight, bias=self.bias)
 
     class ToyConfig:
         model_type, architecture = "toy_mix", "ToyMixForCausalLM"
@@ -189,7 +193,8 @@ def toy_classes():
             layers = []
             for index in range(3):
                 prefix = f"toy.layers.{index}"
-                mixer = (MixerSpec("running_mean", {"hidden_size": HIDDEN, "proj": f"{prefix}.mean.proj.weight"})
+                mixer = (MixerSpec("running_mean", {"hidden_size": HIDDEN, "proj": f"{prefix}.mean.proj.weight",
+                                                    "proj_bias": f"{prefix}.mean.proj.bias"})
                          if index == 1 else attention(f"{prefix}.attn"))
                 if index == 1:      # the stateful mixer, and the routed feed-forward
                     routed = FeedForwardSpec("toy_soft_experts", {
@@ -302,7 +307,7 @@ def plain_toy_logits(folder, tokens):
         prefix = f"toy.layers.{index}"
         h = plain_rmsnorm(x, w[f"{prefix}.norm1.weight"], EPS)
         means = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=F64)[:, None]
-        r = x + means @ w[f"{prefix}.mean.proj.weight"].T
+        r = x + means @ w[f"{prefix}.mean.proj.weight"].T + w[f"{prefix}.mean.proj.bias"]
         fed = plain_rmsnorm(r, w[f"{prefix}.norm2.weight"], EPS)
         share = torch.softmax(fed @ w[f"{prefix}.router.weight"].T * ROUTER_SHARPNESS, dim=-1)
         out = sum(share[:, e:e + 1] * plain_mlp(fed, w, f"{prefix}.experts.{e}") for e in range(EXPERTS))

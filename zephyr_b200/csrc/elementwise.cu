@@ -316,6 +316,20 @@ __global__ void silu_mul_blocked_rows_kernel(T* __restrict__ out, const T* __res
   }
 }
 
+// y[t, i] += b[i]: the bias of a projection, added in float32 and rounded once (no part of the one
+// architecture has a bias; a mixer or feed-forward of another one may).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, long long ldy, const void* __restrict__ bias, int b_dtype, int T_, int N) {
+  const long long total = static_cast<long long>(T_) * N;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = e / N;
+    const int i = static_cast<int>(e - t * N);
+    T* at = y + t * ldy + i;
+    *at = from_float<T>(to_float(*at) + load_scale(bias, b_dtype, i));
+  }
+}
+
 template <typename T> bool aligned16(const void* p, long long elems) {
   return reinterpret_cast<uintptr_t>(p) % 16 == 0 && elems % Vec<T>::N == 0;
 }
@@ -464,6 +478,18 @@ ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int b
   }
   return dtype == DTYPE_F32 ? silu_mul_launch<float>(out, gu, T, I, s)
                             : silu_mul_launch<__nv_bfloat16>(out, gu, T, I, s);
+}
+
+// y [T, N] (rows ldy apart) += bias [N], the bias bfloat16 or float32.
+ZB_API int zb_add_bias(void* y, long long ldy, const void* bias, int b_dtype, int T, int N, int dtype, void* stream) {
+  if (T < 0 || N < 0 || ldy < N) return ERR_BAD_ARGUMENT;
+  if (T == 0 || N == 0) return OK;
+  const long long total = static_cast<long long>(T) * N;
+  const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32) add_bias_kernel<float><<<blocks, 256, 0, s>>>((float*)y, ldy, bias, b_dtype, T, N);
+  else add_bias_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)y, ldy, bias, b_dtype, T, N);
+  return launch_result();
 }
 
 // The CUDA runtime's words for the last call of this library that failed (return code 2).

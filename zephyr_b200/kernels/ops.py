@@ -54,6 +54,7 @@ _SIGNATURES = {
                    c_void_p],
     "zb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "zb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_add_bias": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_void_p, c_void_p],
@@ -301,6 +302,17 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, ep
     _check(library().zb_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(w), _scale_code(w, H), float(eps),
                                     rows, H, DTYPE_CODE[residual.dtype], _stream()), "add_rmsnorm")
     return out
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y [T, N] += bias [N] in place (rows of y may be strided; the bias bfloat16 or float32)."""
+    _cuda(y, bias)
+    _require(y.dim() == 2 and y.stride(1) == 1 and y.dtype in DTYPE_CODE, "y must be [T, N] with unit inner stride")
+    _require(bias.dim() == 1 and bias.numel() == y.shape[1] and bias.is_contiguous() and bias.dtype in DTYPE_CODE,
+             "one bias value per column")
+    _check(library().zb_add_bias(_ptr(y), y.stride(0), _ptr(bias), DTYPE_CODE[bias.dtype], y.shape[0], y.shape[1],
+                                 DTYPE_CODE[y.dtype], _stream()), "add_bias")
+    return y
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bool = False) -> torch.Tensor:
@@ -875,13 +887,17 @@ def fused_chain(stages: Sequence[ChainStage], tokens: int, status: torch.Tensor,
 USE_LIBRARY_PRODUCTS = True     # off: every bfloat16 product of more than a few rows runs on this package's tcgen05 kernel
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+           bias: torch.Tensor | None = None) -> torch.Tensor:
     """y = x w^T.  float32 runs on this package's CUDA-core kernel (no TF32 anywhere).  bfloat16
     with up to 64 rows (a decode step) runs on this package's weight-streaming kernel; larger
     bfloat16 products run on the vendor library's tensor-core product, as the reference's linear
     layers do (src/layer/linear.cpp:22-24 -> cuBLASLt), where that is the faster one; with
     ``USE_LIBRARY_PRODUCTS`` off they run on this package's tcgen05 kernel (``gemm_tc``), so that no
-    library kernel is left on the path.  Accumulation is float32 everywhere."""
+    library kernel is left on the path.  Accumulation is float32 everywhere.  A ``bias`` [N] is
+    added to the product's (rounded) output by a kernel of its own."""
+    if bias is not None:
+        return add_bias(linear(x, w, out_dtype), bias)
     _cuda(x, w)
     if x.dtype == torch.float32:
         return gemm_nt_simt(x, w, out_dtype)
