@@ -433,8 +433,9 @@ def test_cache_write_reports_bad_page_and_position(ops, cuda_device):
 
 
 # --------------------------------------------------------------------- attention
-def ref_attention_row(q, K, V, ctx, q_len, window, nh, nkv):
-    """q [q_len, nh, hd]; K, V [ctx + q_len, nkv, hd] doubles; the new tokens sit at ctx..ctx+q_len-1."""
+def ref_attention_row(q, K, V, ctx, q_len, window, nh, nkv, slopes=None):
+    """q [q_len, nh, hd]; K, V [ctx + q_len, nkv, hd] doubles; the new tokens sit at ctx..ctx+q_len-1.
+    ``slopes`` [nh]: head h adds slopes[h] * (key position - query position) to its scores."""
     hd = q.shape[-1]
     g = nh // nkv
     out = torch.zeros_like(q)
@@ -443,6 +444,8 @@ def ref_attention_row(q, K, V, ctx, q_len, window, nh, nkv):
         lo = max(0, p - window + 1) if window > 0 else 0
         for h in range(nh):
             s = (K[lo:p + 1, h // g] @ q[i, h]) / math.sqrt(hd)
+            if slopes is not None:
+                s = s + float(slopes[h]) * (torch.arange(lo, p + 1, dtype=torch.float64) - p)
             out[i, h] = torch.softmax(s, 0) @ V[lo:p + 1, h // g]
     return out
 
@@ -518,6 +521,33 @@ def test_paged_attention_general(ops, cuda_device, dtype, nh, nkv, hd, page, win
         assert torch.isfinite(got[cursor:cursor + n]).all()
         assert error <= tol(dtype, 2.0), f"row {r}: {error}"
         cursor += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 16, 4, 0), (6, 3, 32, 8, 20), (16, 8, 128, 16, 0)])
+def test_paged_attention_with_a_bias_on_the_scores(ops, cuda_device, dtype, nh, nkv, hd, page, window):
+    """A slope per query head times the distance between key and query, added to the scores: steep
+    for some heads (they see little but the nearest keys), zero for one."""
+    q_lens, ctx = [1, 37, 2, 70], [130, 0, 63, 41]
+    q, cache, meta, Ks, Vs, qs = build_paged_case(cuda_device, dtype, nh, nkv, hd, page, q_lens, ctx, 101)
+    slopes = torch.tensor([0.0 if h == 1 else 2.0 ** -(h % 5) for h in range(nh)], dtype=torch.float32)
+    tile_tokens = ops.attention_tile_tokens(nh // nkv)
+    tile_row, tile_q0 = tiles_for(q_lens, tile_tokens, cuda_device)
+    status = ops.new_status(cuda_device)
+    out = ops.paged_attention(q, cache, meta["table"], tile_row, tile_q0, tile_tokens, meta["row_q_start"],
+                              meta["row_q_len"], meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status,
+                              head_slopes=slopes.to(cuda_device))
+    ops.check_status(status)
+    got = out.double().cpu().view(-1, nh, hd)
+    plain = ops.paged_attention(q, cache, meta["table"], tile_row, tile_q0, tile_tokens, meta["row_q_start"],
+                                meta["row_q_len"], meta["row_ctx"], nh, nkv, hd, window, 1 / math.sqrt(hd), status)
+    assert torch.equal(out.view(-1, nh, hd)[:, 1], plain.view(-1, nh, hd)[:, 1])          # the head without a slope
+    cursor = 0
+    for r, n in enumerate(q_lens):
+        expected = ref_attention_row(qs[r].double(), Ks[r].double(), Vs[r].double(), ctx[r], n, window, nh, nkv, slopes)
+        assert (got[cursor:cursor + n] - expected).abs().max() <= tol(dtype, 2.0), f"row {r}"
+        cursor += n
+    assert (out.float() - plain.float()).abs().max() > 0.05                                 # and the slopes do matter
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

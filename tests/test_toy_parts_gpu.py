@@ -14,12 +14,13 @@ import math
 import pytest
 import torch
 
-from plain_qwen3 import F64, plain_attention, plain_mlp, plain_rmsnorm
+from plain_qwen3 import F64, plain_mlp, plain_rmsnorm
 from replay_util import collect, random_tokens, trace_mixed, trace_portions, trace_tail, trace_whole
 
 pytestmark = pytest.mark.gpu
 
 HIDDEN, VOCAB, HEADS, KV_HEADS, HEAD_DIM, INTER, EPS, THETA, MAX_POS = 48, 101, 4, 2, 16, 80, 1e-5, 10000.0, 128
+SCORE_SLOPE = 0.25        # head h of the toy attention adds -SCORE_SLOPE / 2^h per position of distance to its scores
 EMBED_SCALE, LOGIT_SCALE, LOGIT_CAP = 3.0, 0.5, 2.0
 EXPERTS, EXPERT_INTER, ROUTER_SHARPNESS = 3, 24, 4.0
 
@@ -36,12 +37,18 @@ def toy_classes():
     class NeighbourPairRope(PositionEncoding):
         """Rotates the pairs (2i, 2i + 1) of every head by position * theta^(-2i / head_dim).  It offers
         no rotation tables, so the attention applies it through ``apply`` and runs its own norm and
-        cache-write kernels around it."""
+        cache-write kernels around it.  It is also a bias on the scores: query head h adds
+        -slope / 2^h for every position between the query and the key."""
 
         def __init__(self, spec, dtype, device):
             self.head_dim = spec.head_dim
             index = torch.arange(0, spec.head_dim, 2, dtype=torch.float32)
             self.inv_freq = (float(spec.params["theta"]) ** (-index / spec.head_dim)).to(device)
+            self.slopes = torch.tensor([float(spec.params["slope"]) / 2 ** h for h in range(int(spec.params["heads"]))],
+                                       dtype=torch.float32, device=device)
+
+        def as_score_slopes(self):
+            return self.slopes
 
         def apply(self, x, heads, positions, status):
             T = x.shape[0]
@@ -171,7 +178,7 @@ def toy_classes():
             return {"model_type": self.model_type, "architectures": [self.architecture]}
 
         def to_model_spec(self):
-            position = PositionSpec("toy_neighbour_rope", HEAD_DIM, MAX_POS, {"theta": THETA})
+            position = PositionSpec("toy_neighbour_rope", HEAD_DIM, MAX_POS, {"theta": THETA, "slope": SCORE_SLOPE, "heads": HEADS})
 
             def norm(name):
                 return NormSpec("rmsnorm", HIDDEN, EPS, name)
@@ -286,6 +293,15 @@ def plain_toy_logits(folder, tokens):
         v = (h @ w[f"{prefix}.v_proj.weight"].T).view(T, KV_HEADS, HEAD_DIM)
         return q, k, v
 
+    def sloped_attention(q, k, v):       # causal, grouped, with the encoding's bias on the scores
+        out = torch.zeros_like(q)
+        t, u = torch.arange(T)[:, None], torch.arange(T)[None, :]
+        for head in range(HEADS):
+            kv_head = head // (HEADS // KV_HEADS)
+            scores = (q[:, head, :] @ k[:, kv_head, :].T) / math.sqrt(HEAD_DIM) + (SCORE_SLOPE / 2 ** head) * (u - t).to(F64)
+            out[:, head, :] = torch.softmax(scores.masked_fill(u > t, float("-inf")), dim=-1) @ v[:, kv_head, :]
+        return out
+
     def finish(x, mixed, index):
         r = x + mixed
         return r + plain_mlp(plain_rmsnorm(r, w[f"toy.layers.{index}.norm2.weight"], EPS), w, f"toy.layers.{index}.mlp")
@@ -295,7 +311,7 @@ def plain_toy_logits(folder, tokens):
         q, k, v = qkv(h, f"toy.layers.{index}.attn")
         if kv is not None:
             k, v = kv
-        out = plain_attention(q, k, v).reshape(T, HEADS * HEAD_DIM) @ w[f"toy.layers.{index}.attn.o_proj.weight"].T
+        out = sloped_attention(q, k, v).reshape(T, HEADS * HEAD_DIM) @ w[f"toy.layers.{index}.attn.o_proj.weight"].T
         if index == 2:      # four norms: one more after each part
             prefix = f"toy.layers.{index}"
             r = x + plain_rmsnorm(out, w[f"{prefix}.norm1b.weight"], EPS)

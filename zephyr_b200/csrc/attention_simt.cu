@@ -7,7 +7,9 @@
 // uses key/value head j / g; s = scale * (q . k) with scale = 1/sqrt(hd); a query at absolute
 // position p sees the keys of its own sequence at positions <= p (and > p - window when the
 // layer has a window); softmax with a running maximum; o = sum softmax * v.  There is no epsilon
-// in the denominator and exp is expf.
+// in the denominator and exp is expf.  A position encoding that is a bias on the scores, linear
+// in the distance (a slope per query head), is added here; the one architecture has none, and
+// the faster kernels do not take one.
 //
 // One CTA serves one tile: a run of consecutive new tokens of one request, one key/value head,
 // and a chunk of that head's query heads.  The (token, head) pairs of the tile are dealt to the
@@ -34,6 +36,7 @@ struct AttentionArgs {
   int max_blocks, page_size, num_pages, num_rows;
   int nh, nkv, hd, window, tile_tokens, heads_per_chunk;
   float scale;
+  const float* head_slopes;  // null, or [nh]: query head h adds head_slopes[h] * (key position - query position) to its scores
   int* status;
 };
 
@@ -131,6 +134,8 @@ paged_attention_simt_kernel(const AttentionArgs a) {
       const int p = warp + i * ATT_WARPS;
       if (p >= n_pairs) continue;                       // uniform over the warp
       const int qpos = ctx + q0 + p / n_heads;
+      const float slope = a.head_slopes != nullptr
+                              ? a.head_slopes[kvh * g + chunk * a.heads_per_chunk + (p - p / n_heads * n_heads)] : 0.0f;
       const int first = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
       if (k0 > qpos || k0 + ATT_TILE <= first) continue;  // no key of this tile is visible
       const bool valid = kp <= qpos && kp >= first;
@@ -141,7 +146,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
         s = fmaf(qp[d], to_float(kr[d]), s);
         s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
       }
-      s = valid ? s * a.scale : -INFINITY;
+      s = valid ? fmaf(slope, static_cast<float>(kp - qpos), s * a.scale) : -INFINITY;
       const float new_m = fmaxf(m[i], warp_max(s));      // finite: the tile holds a visible key
       const float pr = valid ? expf(s - new_m) : 0.0f;
       const float corr = expf(m[i] - new_m);             // exp(-inf) = 0 on the first tile
@@ -221,7 +226,7 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
                                    int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
                                    const int* tile_q0, int n_tiles, int tile_tokens, const int* row_q_start,
                                    const int* row_q_len, const int* row_ctx, int nh, int nkv, int hd, int window,
-                                   float scale, int dtype, int* status, void* stream) {
+                                   float scale, const float* head_slopes, int dtype, int* status, void* stream) {
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0)
     return ERR_BAD_ARGUMENT;
   if (hd % 16 != 0 || hd > 256) return ERR_UNSUPPORTED;
@@ -236,7 +241,7 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
   a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window; a.tile_tokens = tile_tokens;
-  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.status = status;
+  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.head_slopes = head_slopes; a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   return dtype == DTYPE_F32 ? attention_simt_dispatch<float>(a, n_tiles, head_chunks, s)
                             : attention_simt_dispatch<__nv_bfloat16>(a, n_tiles, head_chunks, s);

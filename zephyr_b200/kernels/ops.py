@@ -65,7 +65,7 @@ _SIGNATURES = {
     "zb_attention_simt_tile_tokens": [c_int],
     "zb_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_float, c_int, c_void_p, c_void_p],
+                                c_float, c_void_p, c_int, c_void_p, c_void_p],
     "zb_paged_decode_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
@@ -438,9 +438,14 @@ def attention_tile_tokens(group: int) -> int:
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
                     tile_q0: torch.Tensor, tile_tokens: int, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
                     row_ctx: torch.Tensor, nh: int, nkv: int, hd: int, window: int, scale: float,
-                    status: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """The general kernel: causal attention of every new token over its request's pages."""
-    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status)
+                    status: torch.Tensor, out: torch.Tensor | None = None,
+                    head_slopes: torch.Tensor | None = None) -> torch.Tensor:
+    """The general kernel: causal attention of every new token over its request's pages.
+    ``head_slopes`` (float32 [nh]): query head h adds head_slopes[h] * (key position - query position)
+    to its scores, a position encoding that is a bias on the scores."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes)
+    _require(head_slopes is None or (head_slopes.dtype == torch.float32 and head_slopes.is_contiguous()
+                                     and head_slopes.numel() == nh), "one float32 slope per query head")
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype in DTYPE_CODE, "q shape")
     pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
@@ -450,8 +455,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
     _check(library().zb_paged_attention_simt(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), int(tile_tokens), _ptr(row_q_start),
-        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), DTYPE_CODE[q.dtype], _ptr(status),
-        _stream()), "paged_attention")
+        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), _ptr(head_slopes), DTYPE_CODE[q.dtype],
+        _ptr(status), _stream()), "paged_attention")
     return out
 
 

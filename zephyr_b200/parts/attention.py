@@ -62,15 +62,17 @@ class Attention(Mixer):
         tables = self.position.as_rotation_tables() if self.position is not None else (None, None)
         self.fused_position = tables is not None
         self.cos, self.sin = tables if tables is not None else (None, None)
+        # An encoding that is a bias on the scores: only the general kernel adds one.
+        self.score_slopes = self.position.as_score_slopes() if self.position is not None else None
         self.group = self.nh // self.nkv
         self.tile_tokens = ops.attention_tile_tokens(self.group)
-        self.fast_decode = ops.paged_decode_supported(self.nh, self.nkv, self.hd, dtype)
+        self.fast_decode = self.score_slopes is None and ops.paged_decode_supported(self.nh, self.nkv, self.hd, dtype)
         # Decode-only steps of this many requests or more: position encoding inside the attention kernel.
         # With few requests the kernel's own chain (the projection's arrival, a head's loads, its norm
         # and rotation, then the first tile) is as long as the separate kernel's: 4467 against 4620
         # tokens a second at 8 requests, 11305 against 11143 at 64.
         self.fuse_decode_rows = 32
-        self.fast_prefill = ops.paged_prefill_supported(self.nh, self.nkv, self.hd, dtype)
+        self.fast_prefill = self.score_slopes is None and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     @staticmethod
@@ -166,7 +168,7 @@ class Attention(Mixer):
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
-                                ctx.row_ctx, *common, out=out)
+                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes)
         return out
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:

@@ -113,6 +113,12 @@ class PositionEncoding(Part):
         as they are; None for anything else, which is then applied through ``apply``."""
         return None
 
+    def as_score_slopes(self) -> torch.Tensor | None:
+        """None, or float32 [heads] on the device for an encoding that is a bias on the attention
+        scores, linear in the distance: query head h adds slopes[h] * (key position - query position).
+        The attention part then takes the general kernel, the only one with that door."""
+        return None
+
 
 class Mixer(Part):
     def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
