@@ -189,6 +189,40 @@ def test_without_the_vendor_library(model_folders, cuda_device, monkeypatch, nam
     assert ops.LAUNCH_COUNTS.get("gemm_tc", 0) > before
 
 
+@pytest.mark.parametrize("seed", [1, 7])
+def test_random_configurations(cuda_device, tmp_path, seed):
+    """Configurations drawn at random (head sizes in steps of 16 up to 256, any head and group counts,
+    widths that are no multiple of 8, odd vocabularies, any page size), each replayed mixed, with a
+    batched tail and in portions, in both types, against the plain implementation."""
+    import random
+
+    import torch
+
+    from zephyr_b200.config import Qwen3Config
+    from zephyr_b200.weights import write_random_model
+
+    rng = random.Random(seed)
+    for case in range(4):
+        hd = rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 144, 256])
+        nkv = rng.choice([1, 2, 3, 4])
+        nh = nkv * (rng.choice([1, 2, 3, 4, 7]) if hd <= 128 else rng.choice([1, 2]))
+        vocab, page = rng.choice([97, 130, 257, 1003]), rng.choice([4, 8, 16, 32])
+        config = Qwen3Config(
+            vocab_size=vocab, hidden_size=rng.choice([40, 72, 100, 136, 264, 96]),
+            intermediate_size=rng.choice([56, 100, 136, 250, 328]), num_hidden_layers=rng.choice([1, 2, 3]),
+            num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, max_position_embeddings=320,
+            rms_norm_eps=rng.choice([1e-6, 1e-5, 3e-6]), rope_theta=rng.choice([1e4, 1e6, 5e5]),
+            tie_word_embeddings=rng.random() < 0.5)
+        requests = {f"r{i}": random_tokens(vocab, n, seed=100 * case + i) for i, n in enumerate((45, 120, 33, 200, 70))}
+        for dtype in ("bfloat16", "float32"):
+            folder = write_random_model(config, case, tmp_path / f"{seed}_{case}_{dtype}", dtype=getattr(torch, dtype))
+            for mode in ("mixed", "batched", "portions"):
+                steps = TRACES[mode](requests)
+                rows = collect(steps, run_in_process(folder, dtype, steps, page))
+                first, worst, where = first_mismatch(rows, requests, folder, dtype, f"random {seed}.{case} {mode}")
+                assert first is None, f"{config} page {page} {dtype} {mode}: {first}; worst {worst:.3e} at {where}"
+
+
 def test_first_tokens(model_folders, cuda_device):
     """The first tokens of a sequence, one at a time from the very start (position 0 has one key)."""
     for name in ("A", "B", "C"):
