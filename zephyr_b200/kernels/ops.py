@@ -185,9 +185,8 @@ def capture(graph: "torch.cuda.CUDAGraph", **kwargs):
     """``torch.cuda.graph`` with the garbage collector held still.  A collection that happens to run
     inside a capture may destroy an older CUDA graph (one of a runner that was dropped, kept alive
     until then by a reference cycle); the runtime forbids that while any stream captures and the
-    capture is lost ("operation failed due to a previous error during capture").  What is
-    unreachable is collected before the capture begins."""
-    gc.collect()
+    capture is lost ("operation failed due to a previous error during capture").  Such objects wait
+    for the first collection after the capture."""
     enabled = gc.isenabled()
     gc.disable()
     try:
